@@ -1,0 +1,160 @@
+#include "algo/select.h"
+
+#include <algorithm>
+#include <strings.h>
+
+namespace mnccl {
+namespace {
+
+bool nvls_type_ok(DType in, DType wire, DType out, RedOp op) {
+  if (op != RedOp::Sum && op != RedOp::Avg) return false;
+  auto f = [](DType t) { return t == DType::Float32 || t == DType::Float16 || t == DType::Bfloat16; };
+  if (in == wire && wire == out) return f(wire);
+  return wire == DType::Bfloat16 && ((in == DType::Float32 && (out == DType::Float32 || out == DType::Bfloat16)) ||
+                                    (in == DType::Bfloat16 && out == DType::Float32));
+}
+
+bool triple_ok(DType in, DType wire, DType out, RedOp op) {
+  if (in == wire && wire == out) return true;
+  return nvls_type_ok(in, wire, out, op);  // the mixed triples are the same set
+}
+
+uint64_t ceil_div(uint64_t a, uint64_t b) { return (a + b - 1) / b; }
+
+}  // namespace
+
+Algo parse_algo(const std::string& s) {
+  const char* c = s.c_str();
+  if (!strcasecmp(c, "ll")) return Algo::LL;
+  if (!strcasecmp(c, "oneshot")) return Algo::OneShot;
+  if (!strcasecmp(c, "twoshot")) return Algo::TwoShot;
+  if (!strcasecmp(c, "nvls")) return Algo::Nvls;
+  if (!strcasecmp(c, "ring")) return Algo::Ring;
+  return Algo::Auto;
+}
+
+Thresholds thresholds_for(int nranks, const Config& cfg) {
+  Thresholds t;
+  // Crossovers from the device-timed sweep (fp32 / bf16 sum).
+  if (nranks <= 2) {
+    t.ll_max = 64u << 10;
+    t.oneshot_max = 2u << 20;
+  } else if (nranks <= 4) {
+    t.ll_max = 32u << 10;
+    t.oneshot_max = 512u << 10;
+  } else {
+    t.ll_max = 16u << 10;
+    t.oneshot_max = 128u << 10;
+  }
+  t.nvls_min = t.oneshot_max + 1;
+  if (cfg.ll_max_bytes) t.ll_max = cfg.ll_max_bytes;
+  if (cfg.oneshot_max_bytes) t.oneshot_max = cfg.oneshot_max_bytes;
+  if (cfg.nvls_min_bytes) t.nvls_min = cfg.nvls_min_bytes;
+  return t;
+}
+
+size_t default_ll_slot_bytes(int nranks, const Config& cfg) {
+  size_t payload = std::max<size_t>(thresholds_for(nranks, cfg).ll_max, 64u << 10);
+  return 2 * payload;
+}
+
+size_t default_inbox_slot_bytes(int nranks, const Config& cfg) {
+  size_t cap = nranks <= 2 ? (4u << 20) : nranks <= 4 ? (2u << 20) : (1u << 20);
+  return std::max<size_t>(cap, thresholds_for(nranks, cfg).oneshot_max);
+}
+
+Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
+  Plan p;
+  const int N = caps.nranks;
+  const size_t wsz = dtype_size(in.wire), osz = dtype_size(in.out);
+  const uint64_t VW = 16 / wsz;
+  p.spec.mode = in.mode;
+  p.spec.in = in.in;
+  p.spec.wire = in.wire;
+  p.spec.out = in.out;
+  p.spec.op = in.op;
+  p.spec.nthreads = 512;
+  if (!triple_ok(in.in, in.wire, in.out, in.op)) {
+    p.reason = "unsupported (send, wire, recv) type combination for this operator";
+    return p;
+  }
+  const int max_blocks = cfg.max_blocks > 0 ? std::min(cfg.max_blocks, kMaxBlocks) : 0;
+
+  if (N == 1) {
+    if (in.mode != Mode::AllReduce && in.in != in.out) { p.reason = "type conversion needs AllReduce"; return p; }
+    p.spec.algo = Algo::Local;
+    const uint64_t vecs = ceil_div(in.count, std::min<uint64_t>(16 / dtype_size(in.in), 16 / osz));
+    p.spec.nblocks = static_cast<int>(std::clamp<uint64_t>(ceil_div(vecs, 512 * 4), 1, caps.sm_count * 4));
+    p.valid = true;
+    return p;
+  }
+
+  const uint64_t total_elems = in.mode == Mode::AllReduce ? in.count : in.count * uint64_t(N);
+  const uint64_t wire_bytes = total_elems * wsz;
+  const Thresholds th = thresholds_for(N, cfg);
+  Algo algo = in.forced;
+  const bool nvls_types = nvls_type_ok(in.in, in.wire, in.out, in.op);
+  // NVLS needs multicast views of whatever it touches: staging always has one
+  // when caps.nvls; symmetric user buffers only if their segment does.
+  const bool nvls_usable = caps.nvls && nvls_types && in.mode != Mode::AllGather &&
+                           (!in.in_symmetric || in.in_has_mc) && (!in.out_symmetric || in.out_has_mc);
+  if (in.mode != Mode::AllReduce) {
+    if (algo != Algo::TwoShot && algo != Algo::Nvls) algo = nvls_usable && in.mode == Mode::ReduceScatter && wire_bytes >= th.nvls_min ? Algo::Nvls : Algo::TwoShot;
+    if (algo == Algo::Nvls && !(nvls_usable && in.mode == Mode::ReduceScatter)) algo = Algo::TwoShot;
+  } else if (algo == Algo::Auto) {
+    if (wire_bytes <= th.ll_max && wire_bytes * 2 <= caps.ll_slot_bytes) algo = Algo::LL;
+    else if (wire_bytes <= th.oneshot_max && wire_bytes <= caps.inbox_slot_bytes) algo = Algo::OneShot;
+    else if (nvls_usable && wire_bytes >= th.nvls_min) algo = Algo::Nvls;
+    else algo = Algo::TwoShot;
+  }
+  // Forced choices that cannot be honoured degrade to the next general one.
+  if (algo == Algo::LL && ceil_div(wire_bytes, 8) * 16 > caps.ll_slot_bytes) algo = Algo::OneShot;
+  if (algo == Algo::OneShot && ceil_div(wire_bytes, 16) * 16 > caps.inbox_slot_bytes) algo = Algo::TwoShot;
+  if (algo == Algo::Nvls && !nvls_usable) algo = Algo::TwoShot;
+  if (algo == Algo::Ring || algo == Algo::Auto || algo == Algo::Local) algo = Algo::TwoShot;
+  p.spec.algo = algo;
+
+  if (algo == Algo::LL) {
+    const uint64_t units = ceil_div(wire_bytes, 8);
+    p.spec.nthreads = units <= 128 ? 128 : 256;
+    p.spec.nblocks = static_cast<int>(std::clamp<uint64_t>(ceil_div(units, p.spec.nthreads), 1, max_blocks ? max_blocks : 64));
+    p.valid = true;
+    return p;
+  }
+  if (algo == Algo::OneShot) {
+    const uint64_t vecs = ceil_div(wire_bytes, 16);
+    p.spec.nthreads = vecs <= 256 ? 256 : 512;
+    p.spec.nblocks = static_cast<int>(std::clamp<uint64_t>(ceil_div(vecs, p.spec.nthreads), 1, max_blocks ? max_blocks : 64));
+    p.valid = true;
+    return p;
+  }
+
+  // Two-shot / NVLS geometry.
+  uint64_t E;  // elements per shard
+  if (in.mode == Mode::AllReduce) E = ceil_div(ceil_div(in.count, VW), uint64_t(N)) * VW;
+  else E = in.count;
+  p.shard_elems = E;
+  const uint64_t shard_vecs = ceil_div(E, VW);
+  // Zero-copy needs 16-byte aligned shard starts inside the user buffers.
+  const bool shard_al_in = (E * dtype_size(in.in)) % 16 == 0;
+  const bool shard_al_out = (E * osz) % 16 == 0;
+  bool zc_in = in.in_symmetric && in.in == in.wire && shard_al_in;
+  bool zc_out = in.out_symmetric && shard_al_out;
+  if (in.mode == Mode::AllGather) zc_in = true;         // AllGather reads its own send buffer only
+  if (in.mode == Mode::ReduceScatter) zc_out = true;    // ReduceScatter writes its own recv buffer only
+  p.copy_in = !zc_in;
+  p.copy_out = !zc_out;
+  const uint64_t out_vb = VW * osz;
+  uint64_t sv = shard_vecs;
+  if (p.copy_in) sv = std::min<uint64_t>(sv, caps.stage_bytes / (uint64_t(N) * 16));
+  if (p.copy_out) sv = std::min<uint64_t>(sv, caps.stage_bytes / (uint64_t(N) * out_vb));
+  if (sv == 0) { p.reason = "staging buffer too small"; return p; }
+  p.chunk_shard_vecs = sv;
+  const uint64_t tiles = ceil_div(std::min(sv, shard_vecs), 512 * 4);
+  int cap = max_blocks ? max_blocks : (algo == Algo::Nvls ? 96 : 64);
+  p.spec.nblocks = static_cast<int>(std::clamp<uint64_t>(tiles, 1, cap));
+  p.valid = true;
+  return p;
+}
+
+}  // namespace mnccl

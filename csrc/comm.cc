@@ -1,0 +1,691 @@
+#include "comm.h"
+
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <chrono>
+#include <cstring>
+#include <functional>
+#include <random>
+#include <sstream>
+#include <thread>
+
+#include "bootstrap/fdpass.h"
+#include "bootstrap/hera.h"
+#include "bootstrap/store.h"
+#include "core/log.h"
+#include "mem/cuda_driver.h"
+#include "mem/symmetric.h"
+#include "net/ring.h"
+#include "net/transport.h"
+#include "watchdog/watchdog.h"
+
+namespace mnccl {
+namespace {
+
+#define RT_CHECK(call, what)                                                                   \
+  do {                                                                                         \
+    cudaError_t _e = (call);                                                                   \
+    if (_e != cudaSuccess) {                                                                   \
+      (void)cudaGetLastError();                                                                \
+      fail(Result::UnhandledCudaError, std::string(what) + ": " + cudaGetErrorString(_e));     \
+    }                                                                                          \
+  } while (0)
+
+struct PeerInfo {
+  uint64_t host_hash;
+  int32_t has_gpu;
+  int32_t device;
+  int32_t device_count;
+  int32_t pid;
+  char bus_id[32];
+};
+
+uint64_t host_hash() {
+  char name[256] = {0};
+  if (gethostname(name, sizeof(name) - 1) != 0) strcpy(name, "unknown");
+  // Containers on one machine may share a hostname but not /dev/shm or the
+  // abstract socket namespace; mix in the boot id and the network namespace.
+  std::string key = name;
+  char buf[128];
+  ssize_t n = readlink("/proc/self/ns/net", buf, sizeof(buf) - 1);
+  if (n > 0) key.append(buf, static_cast<size_t>(n));
+  return std::hash<std::string>{}(key);
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+constexpr size_t kShmBytes = 4096;
+constexpr int kProgressWords = 16;  // per local rank, 64 bytes
+
+enum class MemKind { Device, PinnedHost, PlainHost };
+
+MemKind classify(const void* p, bool has_gpu) {
+  if (!has_gpu) return MemKind::PlainHost;
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return MemKind::PlainHost;
+  }
+  switch (a.type) {
+    case cudaMemoryTypeDevice: return MemKind::Device;
+    case cudaMemoryTypeManaged: return MemKind::Device;
+    case cudaMemoryTypeHost: return MemKind::PinnedHost;
+    default: return MemKind::PlainHost;
+  }
+}
+
+}  // namespace
+
+Comm* Comm::create(int nranks, int rank, const char* ip) {
+  std::unique_ptr<Comm> c(new Comm());
+  c->init(nranks, rank, ip);
+  return c.release();
+}
+
+void Comm::init(int nranks, int rank, const char* ip) {
+  cfg_ = Config::get();
+  root_ip_ = ip ? ip : "127.0.0.1";
+  rank_ = rank;
+  size_ = nranks;
+  bool hera_mode = false;
+  if (rank == -1) {
+    // Hera auto-bootstrap: `ip` is the master; rank, world size and the root
+    // address come back from it (reference: src/api.cpp:38-51).
+    hera_mode = true;
+    log_always("Mini-NCCL", "Hera Mode Activated. Connecting to Master at %s...", root_ip_.c_str());
+    hera_.reset(new hera::Worker(root_ip_, cfg_.hera_port));
+    hera_->connect_and_register(cfg_.connect_retries, 250, cfg_.socket_timeout_ms);
+    rank_ = hera_->rank();
+    size_ = hera_->size();
+    root_ip_ = hera_->root_ip();
+    log_always("Mini-NCCL", "Auto-Assigned Rank: %d Size: %d Root-IP: %s", rank_, size_, root_ip_.c_str());
+    if (!cfg_.hera_keepalive) hera_->disconnect();  // the reference's worker lives for the registration only
+  }
+  if (size_ <= 0 || rank_ < 0 || rank_ >= size_) fail(Result::InvalidArgument, "rank out of range");
+  if (size_ > kMaxRanks && cfg_.transport != "soft" && cfg_.transport != "verbs")
+    MNCCL_INFO("Mini-NCCL", "more than %d ranks: the NVLink plane is not used", kMaxRanks);
+
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    ndev = 0;
+  }
+  has_gpu_ = ndev > 0;
+  if (has_gpu_) {
+    if (cfg_.cuda_device >= 0) RT_CHECK(cudaSetDevice(cfg_.cuda_device), "cudaSetDevice");
+    RT_CHECK(cudaGetDevice(&device_), "cudaGetDevice");
+  }
+
+  store_.reset(new BootstrapStore(rank_, size_, root_ip_, cfg_.bootstrap_port, cfg_.socket_timeout_ms,
+                                  cfg_.connect_retries));
+  store_->connect();
+
+  // Job namespace for host shared memory and unix sockets: a nonce from rank 0.
+  uint64_t nonce = 0;
+  if (rank_ == 0) {
+    std::random_device rd;
+    nonce = (static_cast<uint64_t>(rd()) << 32) ^ rd() ^ static_cast<uint64_t>(getpid());
+  }
+  store_->broadcast(&nonce, sizeof(nonce), 0);
+  {
+    char buf[64];
+    snprintf(buf, sizeof(buf), "%016llx", static_cast<unsigned long long>(nonce));
+    job_ns_ = cfg_.job_id.empty() ? std::string(buf) : cfg_.job_id + "-" + buf;
+  }
+
+  // Who is where.
+  PeerInfo me{};
+  me.host_hash = host_hash();
+  me.has_gpu = has_gpu_ ? 1 : 0;
+  me.device = device_;
+  me.device_count = ndev;
+  me.pid = static_cast<int32_t>(getpid());
+  if (has_gpu_) cudaDeviceGetPCIBusId(me.bus_id, sizeof(me.bus_id), device_);
+  std::vector<PeerInfo> all(size_);
+  store_->all_gather(&me, all.data(), sizeof(me));
+  local_rank_ = 0;
+  local_size_ = 0;
+  bool one_host = true, all_gpu = true;
+  for (int r = 0; r < size_; ++r) {
+    if (all[r].host_hash == me.host_hash) {
+      if (r < rank_) ++local_rank_;
+      ++local_size_;
+    } else {
+      one_host = false;
+    }
+    if (!all[r].has_gpu) all_gpu = false;
+  }
+
+  // Hera mode: ranks that were all started on the same device (the reference
+  // benchmark pins every rank to GPU 0, reference: tests/perf_test.cpp:46)
+  // spread over the host's GPUs by local rank.
+  if (hera_mode && cfg_.auto_device && has_gpu_ && cfg_.cuda_device < 0 && one_host && all_gpu && size_ > 1) {
+    bool shared = true;
+    for (int r = 0; r < size_; ++r) shared = shared && all[r].device == all[0].device;
+    if (shared && ndev >= local_size_) {
+      RT_CHECK(cudaSetDevice(local_rank_), "cudaSetDevice(local rank)");
+      device_ = local_rank_;
+      log_always("Mini-NCCL", "Rank %d: selected GPU %d from the local rank", rank_, device_);
+      me.device = device_;
+      cudaDeviceGetPCIBusId(me.bus_id, sizeof(me.bus_id), device_);
+      // fallthrough to the gather below
+    }
+    store_->all_gather(&me, all.data(), sizeof(me));
+  }
+
+  bool distinct = true;
+  for (int a = 0; a < size_ && distinct; ++a)
+    for (int b = a + 1; b < size_; ++b)
+      if (all[a].host_hash == all[b].host_hash && strncmp(all[a].bus_id, all[b].bus_id, sizeof(me.bus_id)) == 0) {
+        distinct = false;
+        break;
+      }
+  bool p2p_ok = has_gpu_;
+  if (has_gpu_ && one_host && all_gpu && distinct) {
+    for (int r = 0; r < size_ && p2p_ok; ++r) {
+      if (r == rank_) continue;
+      int peer_dev = -1, can = 0;
+      if (cudaDeviceGetByPCIBusId(&peer_dev, all[r].bus_id) != cudaSuccess) {
+        (void)cudaGetLastError();
+        continue;  // not visible in this process: the mapping step decides
+      }
+      if (cudaDeviceCanAccessPeer(&can, device_, peer_dev) != cudaSuccess || !can) {
+        (void)cudaGetLastError();
+        p2p_ok = false;
+      }
+    }
+  }
+  bool want_gpu_plane = size_ == 1 ? has_gpu_ : (one_host && all_gpu && distinct && p2p_ok && size_ <= kMaxRanks);
+  if (cfg_.transport == "soft" || cfg_.transport == "verbs") want_gpu_plane = false;
+  // Every rank must take the same plane.
+  uint8_t mine = want_gpu_plane ? 1 : 0;
+  std::vector<uint8_t> votes(size_);
+  store_->all_gather(&mine, votes.data(), 1);
+  gpu_plane_ = true;
+  for (uint8_t v : votes) gpu_plane_ = gpu_plane_ && v;
+  if (cfg_.transport == "nvlink" && !gpu_plane_)
+    fail(Result::SystemError, "MINI_NCCL_TRANSPORT=nvlink but the ranks do not share one NVLink-connected host");
+
+  setup_shared_host_segment();
+  if (gpu_plane_) init_gpu_plane();
+  else init_net_plane();
+
+  if (hera_ && cfg_.hera_keepalive) {
+    hera_->start_agent(200, [this](int origin, uint32_t reason) {
+      log_always("Mini-NCCL", "rank %d: GLOBAL_ABORT received (origin %d, reason %u)", rank_, origin, reason);
+      abort();
+    });
+  }
+  store_->barrier();
+  MNCCL_INFO("Mini-NCCL", "rank %d/%d ready: plane=%s device=%d local_rank=%d", rank_, size_,
+             gpu_plane_ ? "nvlink" : (transport_ ? transport_->name() : "none"), device_, local_rank_);
+}
+
+void Comm::setup_shared_host_segment() {
+  // One page per host: word 0 is the abort word, each local rank owns 16 words
+  // of progress.  Created by the host's first rank, unlinked once all mapped it.
+  std::string name = "/mnccl-" + job_ns_ + "-" + std::to_string(static_cast<unsigned long long>(host_hash() & 0xffffffffull));
+  int fd = -1;
+  if (local_rank_ == 0) {
+    fd = shm_open(name.c_str(), O_CREAT | O_EXCL | O_RDWR, 0600);
+    if (fd >= 0 && ftruncate(fd, kShmBytes) != 0) {
+      close(fd);
+      fd = -1;
+    }
+  }
+  store_->barrier();
+  if (local_rank_ != 0) fd = shm_open(name.c_str(), O_RDWR, 0600);
+  if (fd >= 0) {
+    void* m = mmap(nullptr, kShmBytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+    close(fd);
+    if (m != MAP_FAILED) {
+      shm_map_ = m;
+      shm_bytes_ = kShmBytes;
+    }
+  }
+  store_->barrier();
+  if (local_rank_ == 0) shm_unlink(name.c_str());
+  uint32_t* words = nullptr;
+  if (shm_map_ && (1 + local_rank_ + 1) * kProgressWords * 4 <= static_cast<int>(kShmBytes)) {
+    words = static_cast<uint32_t*>(shm_map_);
+    if (has_gpu_) {
+      if (cudaHostRegister(shm_map_, kShmBytes, cudaHostRegisterMapped | cudaHostRegisterPortable) == cudaSuccess) {
+        shm_registered_ = true;
+      } else {
+        (void)cudaGetLastError();
+        words = nullptr;
+        MNCCL_WARN("Mini-NCCL", "rank %d: cannot map the shared abort page into the GPU; abort stays local to this rank", rank_);
+      }
+    }
+  }
+  if (!words) {
+    if (has_gpu_) {
+      RT_CHECK(cudaHostAlloc(&private_host_, kShmBytes, cudaHostAllocMapped), "cudaHostAlloc(abort page)");
+    } else {
+      private_host_ = calloc(1, kShmBytes);
+      if (!private_host_) fail(Result::SystemError, "out of memory");
+    }
+    memset(private_host_, 0, kShmBytes);
+    words = static_cast<uint32_t*>(private_host_);
+    abort_host_ = words;
+    progress_host_ = words + kProgressWords;
+  } else {
+    abort_host_ = words;
+    progress_host_ = words + kProgressWords * (1 + local_rank_);
+    for (int i = 0; i < kProgressWords; ++i) progress_host_[i] = 0;
+  }
+}
+
+void Comm::init_gpu_plane() {
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device_);
+  caps_.nranks = size_;
+  caps_.sm_count = sms;
+  memset(&dev_, 0, sizeof(dev_));
+  dev_.rank = rank_;
+  dev_.nranks = size_;
+  dev_.spin_timeout_ns = static_cast<uint64_t>(cfg_.watchdog_timeout_ms) * 1500000ull;  // 1.5x the host bound
+  uint32_t* dptr = nullptr;
+  void* host_base = private_host_ ? private_host_ : shm_map_;
+  if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&dptr), host_base, 0) == cudaSuccess && dptr) {
+    const size_t prog_off = reinterpret_cast<const char*>(const_cast<const uint32_t*>(progress_host_)) - static_cast<const char*>(host_base);
+    dev_.abort_word = dptr;
+    dev_.host_progress = cfg_.watchdog_enable ? reinterpret_cast<volatile uint32_t*>(reinterpret_cast<char*>(dptr) + prog_off) : nullptr;
+  } else {
+    (void)cudaGetLastError();
+    dev_.abort_word = nullptr;
+    dev_.host_progress = nullptr;
+  }
+  if (size_ == 1) return;  // a single rank needs no symmetric memory
+
+  fds_.reset(new FdChannel(job_ns_, rank_));
+  fds_->open();
+  store_->barrier();
+  symm_.reset(new SymmetricMemory(rank_, size_, device_, store_.get(), fds_.get(), cfg_));
+
+  // Control segment layout.
+  caps_.ll_slot_bytes = align_up(default_ll_slot_bytes(size_, cfg_), 4096);
+  caps_.inbox_slot_bytes = align_up(default_inbox_slot_bytes(size_, cfg_), 4096);
+  caps_.stage_bytes = align_up(cfg_.staging_bytes, 4096);
+  size_t off = 0;
+  dev_.off_sig = off;
+  off += align_up(sizeof(uint32_t) * kMaxBlocks * kMaxRanks, 4096);
+  dev_.off_local = off;
+  off += align_up(sizeof(LocalState), 4096);
+  dev_.off_ll = off;
+  off += 2 * size_t(size_) * caps_.ll_slot_bytes;
+  dev_.off_inbox = off;
+  off += 2 * size_t(size_) * caps_.inbox_slot_bytes;
+  off = align_up(off, 1 << 16);
+  dev_.off_stage_a = off;
+  off += caps_.stage_bytes;
+  dev_.off_stage_b = off;
+  off += caps_.stage_bytes;
+  dev_.ll_slot_bytes = caps_.ll_slot_bytes;
+  dev_.inbox_slot_bytes = caps_.inbox_slot_bytes;
+  dev_.stage_bytes = caps_.stage_bytes;
+
+  ctrl_ = symm_->allocate(off, true);
+  for (int r = 0; r < size_; ++r) dev_.ctrl[r] = static_cast<char*>(ctrl_->peer[r]);
+  dev_.ctrl_mc = static_cast<char*>(ctrl_->mc);
+  caps_.nvls = ctrl_->mc != nullptr;
+
+  if (cfg_.watchdog_enable && dev_.host_progress) {
+    watchdog_.reset(new Watchdog(progress_host_, abort_host_, cfg_.watchdog_timeout_ms, rank_));
+    watchdog_->set_on_trip([this](uint32_t reason) {
+      if (hera_ && cfg_.hera_keepalive) {
+        try { hera_->send_global_abort(reason); } catch (...) {}
+      }
+    });
+    watchdog_->start();
+  }
+}
+
+void Comm::init_net_plane() {
+  std::string kind = cfg_.transport;
+  if (kind == "nvlink" || kind.empty()) kind = "auto";
+  transport_ = make_transport(kind, rank_, size_);
+  transport_->connect(*store_);
+  ring_.reset(new RingAllReduce(rank_, size_, transport_.get(), store_.get(), cfg_, abort_host_));
+}
+
+Comm::~Comm() {
+  if (hera_) hera_->stop_agent();
+  if (watchdog_) watchdog_->stop();
+  if (has_gpu_ && device_ >= 0) {
+    cudaSetDevice(device_);
+    cudaDeviceSynchronize();
+    (void)cudaGetLastError();
+  }
+  // Goodbye barrier, so that nobody unmaps memory a peer's kernel still uses.
+  // A dead peer must not hold destroy up for long: errors are swallowed.
+  if (store_ && !aborted_.load()) {
+    try { store_->barrier(); } catch (...) {}
+  }
+  ring_.reset();
+  transport_.reset();
+  {
+    std::lock_guard<std::mutex> lk(seg_mu_);
+    user_segments_.clear();
+  }
+  ctrl_.reset();
+  symm_.reset();
+  fds_.reset();
+  if (bounce_) {
+    if (has_gpu_) cudaFreeHost(bounce_); else free(bounce_);
+  }
+  if (shm_registered_) cudaHostUnregister(shm_map_);
+  if (shm_map_) munmap(shm_map_, shm_bytes_);
+  if (private_host_) {
+    if (has_gpu_) cudaFreeHost(private_host_); else free(private_host_);
+  }
+  (void)cudaGetLastError();
+}
+
+void Comm::check_usable() {
+  if (aborted_.load()) fail(Result::InternalError, "communicator was aborted");
+  if (abort_host_ && *abort_host_ != 0) {
+    aborted_.store(true);
+    fail(Result::InternalError, "NCCL Watchdog Timeout: Communication hang detected.");
+  }
+  if (progress_host_ && progress_host_[2] != 0) {
+    aborted_.store(true);
+    fail(Result::InternalError, "a collective kernel reported a failed wait (status " + std::to_string(progress_host_[2]) + ")");
+  }
+}
+
+std::shared_ptr<Segment> Comm::find_segment(const void* ptr, size_t bytes, size_t* offset) {
+  std::lock_guard<std::mutex> lk(seg_mu_);
+  const uintptr_t p = reinterpret_cast<uintptr_t>(ptr);
+  auto it = user_segments_.upper_bound(p);
+  if (it == user_segments_.begin()) return nullptr;
+  --it;
+  const uintptr_t base = it->first;
+  if (p >= base && p + bytes <= base + it->second->mapped_bytes) {
+    if (offset) *offset = p - base;
+    return it->second;
+  }
+  return nullptr;
+}
+
+void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType recv_t, DType wire_t, size_t count,
+                  RedOp op, double scale, Algo forced, cudaStream_t stream) {
+  const bool is_float = send_t == DType::Float16 || send_t == DType::Bfloat16 || send_t == DType::Float32 ||
+                        send_t == DType::Float64;
+  if (!is_float && scale != 1.0) fail(Result::InvalidArgument, "a scale factor needs a floating-point type");
+  const size_t in_elems = mode == Mode::ReduceScatter ? count * size_ : count;
+  const size_t out_elems = mode == Mode::AllGather ? count * size_ : count;
+  const size_t in_bytes = in_elems * dtype_size(send_t), out_bytes = out_elems * dtype_size(recv_t);
+  if (classify(send, true) == MemKind::PlainHost || classify(recv, true) == MemKind::PlainHost)
+    fail(Result::InvalidArgument, "buffers must be device memory or pinned host memory on the GPU data plane");
+
+  PlanInput pi;
+  pi.mode = mode;
+  pi.count = count;
+  pi.in = send_t;
+  pi.wire = wire_t;
+  pi.out = recv_t;
+  pi.op = op;
+  pi.forced = forced;
+  size_t in_off = 0, out_off = 0;
+  std::shared_ptr<Segment> in_seg, out_seg;
+  if (size_ > 1) {
+    in_seg = find_segment(send, in_bytes, &in_off);
+    out_seg = find_segment(recv, out_bytes, &out_off);
+    pi.in_symmetric = in_seg && (reinterpret_cast<uintptr_t>(send) & 15u) == 0;
+    pi.out_symmetric = out_seg && (reinterpret_cast<uintptr_t>(recv) & 15u) == 0;
+    pi.in_has_mc = in_seg && in_seg->mc;
+    pi.out_has_mc = out_seg && out_seg->mc;
+  }
+  Plan plan = make_plan(pi, caps_, cfg_);
+  if (!plan.valid) fail(Result::InvalidArgument, std::string("no kernel for this request: ") + plan.reason);
+  if (!kernel_exists(plan.spec)) fail(Result::InvalidArgument, "no kernel for this type / operator combination");
+
+  KParams kp;
+  memset(&kp, 0, sizeof(kp));
+  kp.comm = dev_;
+  CollArgs& a = kp.args;
+  a.send = send;
+  a.recv = recv;
+  a.count = count;
+  a.shard_elems = plan.shard_elems;
+  a.chunk_shard_vecs = plan.chunk_shard_vecs;
+  const double factor = scale * (op == RedOp::Avg ? 1.0 / static_cast<double>(size_) : 1.0);
+  a.scale_f = static_cast<float>(factor);
+  a.scale_d = factor;
+  a.int_div = (op == RedOp::Avg && !is_float) ? size_ : 0;
+  a.copy_in = plan.copy_in ? 1 : 0;
+  a.copy_out = plan.copy_out ? 1 : 0;
+  if (size_ > 1 && (plan.spec.algo == Algo::TwoShot || plan.spec.algo == Algo::Nvls)) {
+    const bool zc_in = !plan.copy_in && mode != Mode::AllGather;
+    const bool zc_out = !plan.copy_out && mode != Mode::ReduceScatter;
+    for (int r = 0; r < size_; ++r) {
+      a.in_peer[r] = zc_in ? static_cast<char*>(in_seg->peer[r]) + in_off : dev_.ctrl[r] + dev_.off_stage_a;
+      a.out_peer[r] = zc_out ? static_cast<char*>(out_seg->peer[r]) + out_off : dev_.ctrl[r] + dev_.off_stage_b;
+    }
+    a.in_mc = zc_in ? (in_seg->mc ? static_cast<char*>(in_seg->mc) + in_off : nullptr)
+                    : (dev_.ctrl_mc ? dev_.ctrl_mc + dev_.off_stage_a : nullptr);
+    a.out_mc = zc_out ? (out_seg->mc ? static_cast<char*>(out_seg->mc) + out_off : nullptr)
+                      : (dev_.ctrl_mc ? dev_.ctrl_mc + dev_.off_stage_b : nullptr);
+    if (zc_in) stats_.zero_copy_in++;
+    if (zc_out) stats_.zero_copy_out++;
+    if (plan.copy_in || plan.copy_out) stats_.staged_passes++;
+  }
+  if (size_ == 1 && mode == Mode::AllReduce && send == recv && send_t == recv_t && factor == 1.0) {
+    // Nothing to do; keep stream order semantics without a launch.
+  } else {
+    RT_CHECK(launch_collective(plan.spec, kp, stream), "kernel launch");
+  }
+  stats_.calls++;
+  stats_.bytes += in_bytes;
+  stats_.by_algo[static_cast<int>(plan.spec.algo)]++;
+}
+
+void Comm::wait_blocking(cudaStream_t stream) {
+  // Reference behaviour on request (MINI_NCCL_BLOCKING=1): return only when
+  // the stream has drained, report a watchdog trip as an error.
+  for (;;) {
+    cudaError_t q = cudaStreamQuery(stream);
+    if (q == cudaSuccess) break;
+    if (q != cudaErrorNotReady) {
+      (void)cudaGetLastError();
+      fail(Result::UnhandledCudaError, std::string("stream error: ") + cudaGetErrorString(q));
+    }
+    std::this_thread::sleep_for(std::chrono::microseconds(200));
+  }
+  check_usable();
+}
+
+void Comm::all_reduce(const void* send, DType send_t, void* recv, DType recv_t, DType wire_t, size_t count, RedOp op,
+                      double scale, Algo forced, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lk(call_mu_);
+  check_usable();
+  bool capturing = false;
+  if (has_gpu_) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cs) == cudaSuccess) capturing = cs == cudaStreamCaptureStatusActive;
+    else (void)cudaGetLastError();
+  }
+  if (capturing) {
+    stats_.graph_captures_seen++;
+    if (!capture_warned_.exchange(true)) {
+      if (gpu_plane_)
+        MNCCL_INFO("Mini-NCCL", "CUDA Graph capture detected: the collective is captured as one kernel node; flags and epochs are device-resident, so replays are safe.");
+      else
+        log_always("Mini-NCCL", "[Warning] CUDA Graph capture detected, but the network data plane is driven by the host and cannot be captured.");
+    }
+    if (!gpu_plane_) fail(Result::InvalidUsage, "the network data plane cannot run under CUDA Graph capture");
+  }
+  if (!gpu_plane_) {
+    if (send_t != recv_t || send_t != wire_t || scale != 1.0)
+      fail(Result::InvalidArgument, "the network data plane supports homogeneous types without a scale");
+    ring_all_reduce(send, recv, count, send_t, op, stream);
+    stats_.calls++;
+    stats_.bytes += count * dtype_size(send_t);
+    stats_.by_algo[static_cast<int>(Algo::Ring)]++;
+    return;
+  }
+  if (forced == Algo::Auto) forced = parse_algo(cfg_.algo);
+  if (forced == Algo::Ring) forced = Algo::Auto;
+  launch(Mode::AllReduce, send, send_t, recv, recv_t, wire_t, count, op, scale, forced, stream);
+  if (cfg_.blocking && !capturing) wait_blocking(stream);
+}
+
+void Comm::reduce_scatter(const void* send, void* recv, size_t recvcount, DType t, RedOp op, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lk(call_mu_);
+  check_usable();
+  if (!gpu_plane_) fail(Result::InvalidUsage, "ReduceScatter needs the GPU data plane");
+  if (size_ == 1) {
+    launch(Mode::AllReduce, send, t, recv, t, t, recvcount, op, 1.0, Algo::Auto, stream);
+    return;
+  }
+  launch(Mode::ReduceScatter, send, t, recv, t, t, recvcount, op, 1.0, parse_algo(cfg_.algo), stream);
+}
+
+void Comm::all_gather(const void* send, void* recv, size_t sendcount, DType t, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lk(call_mu_);
+  check_usable();
+  if (!gpu_plane_) fail(Result::InvalidUsage, "AllGather needs the GPU data plane");
+  if (size_ == 1) {
+    if (send != recv) RT_CHECK(cudaMemcpyAsync(recv, send, sendcount * dtype_size(t), cudaMemcpyDefault, stream), "cudaMemcpyAsync");
+    return;
+  }
+  launch(Mode::AllGather, send, t, recv, t, t, sendcount, RedOp::Sum, 1.0, Algo::TwoShot, stream);
+}
+
+void Comm::ring_all_reduce(const void* send, void* recv, size_t count, DType t, RedOp op, cudaStream_t stream) {
+  const size_t bytes = count * dtype_size(t);
+  if (has_gpu_) RT_CHECK(cudaStreamSynchronize(stream), "cudaStreamSynchronize");  // order after the caller's GPU work
+  const MemKind sk = classify(send, has_gpu_), rk = classify(recv, has_gpu_);
+  if (rk != MemKind::Device && sk != MemKind::Device) {
+    if (send != recv) memmove(recv, send, bytes);
+    ring_->run(recv, count, t, op);
+    return;
+  }
+  // Device memory: bounce through pinned host memory.
+  if (bounce_bytes_ < bytes) {
+    if (bounce_) cudaFreeHost(bounce_);
+    bounce_ = nullptr;
+    bounce_bytes_ = 0;
+    RT_CHECK(cudaHostAlloc(&bounce_, bytes, cudaHostAllocDefault), "cudaHostAlloc(bounce)");
+    bounce_bytes_ = bytes;
+  }
+  RT_CHECK(cudaMemcpy(bounce_, send, bytes, cudaMemcpyDefault), "cudaMemcpy(D2H)");
+  ring_->run(bounce_, count, t, op);
+  RT_CHECK(cudaMemcpy(recv, bounce_, bytes, cudaMemcpyDefault), "cudaMemcpy(H2D)");
+}
+
+void* Comm::mem_alloc(size_t bytes) {
+  if (!gpu_plane_) fail(Result::InvalidUsage, "symmetric allocations need the GPU data plane");
+  if (size_ == 1) {
+    void* p = nullptr;
+    RT_CHECK(cudaMalloc(&p, bytes), "cudaMalloc");
+    auto seg = std::make_shared<Segment>();
+    seg->bytes = bytes;
+    seg->mapped_bytes = bytes;
+    seg->local = p;
+    seg->peer.assign(1, p);
+    std::lock_guard<std::mutex> lk(seg_mu_);
+    user_segments_[reinterpret_cast<uintptr_t>(p)] = seg;
+    return p;
+  }
+  std::shared_ptr<Segment> seg = symm_->allocate(bytes, true);
+  std::lock_guard<std::mutex> lk(seg_mu_);
+  user_segments_[reinterpret_cast<uintptr_t>(seg->local)] = seg;
+  return seg->local;
+}
+
+void Comm::mem_free(void* ptr) {
+  std::shared_ptr<Segment> seg;
+  {
+    std::lock_guard<std::mutex> lk(seg_mu_);
+    auto it = user_segments_.find(reinterpret_cast<uintptr_t>(ptr));
+    if (it == user_segments_.end()) fail(Result::InvalidArgument, "pointer was not returned by mncclMemAlloc");
+    seg = it->second;
+    user_segments_.erase(it);
+  }
+  if (size_ == 1) {
+    cudaFree(ptr);
+    return;
+  }
+  symm_->release(seg);
+}
+
+void Comm::peer_pointers(void* ptr, void** peers, void** mc) {
+  size_t off = 0;
+  std::shared_ptr<Segment> seg = find_segment(ptr, 1, &off);
+  if (!seg) fail(Result::InvalidArgument, "pointer is not inside a symmetric allocation");
+  for (int r = 0; r < size_; ++r) peers[r] = static_cast<char*>(seg->peer[r]) + off;
+  if (mc) *mc = seg->mc ? static_cast<char*>(seg->mc) + off : nullptr;
+}
+
+void Comm::barrier() { store_->barrier(); }
+
+void Comm::abort() {
+  aborted_.store(true);
+  if (abort_host_) __atomic_store_n(const_cast<uint32_t*>(abort_host_), 1u, __ATOMIC_RELEASE);
+  if (transport_) transport_->abort();
+}
+
+Result Comm::async_error() {
+  if (aborted_.load()) return Result::InternalError;
+  if (abort_host_ && *abort_host_ != 0) return Result::InternalError;
+  if (progress_host_ && progress_host_[2] != 0) return Result::InternalError;
+  if (watchdog_ && watchdog_->tripped()) return Result::InternalError;
+  if (progress_host_ && progress_host_[0] != progress_host_[1]) return Result::InProgress;
+  return Result::Success;
+}
+
+Algo Comm::query_algo(size_t bytes, DType t, RedOp op, bool registered) {
+  if (!gpu_plane_) return Algo::Ring;
+  PlanInput pi;
+  pi.count = bytes / dtype_size(t);
+  pi.in = pi.wire = pi.out = t;
+  pi.op = op;
+  pi.in_symmetric = pi.out_symmetric = registered;
+  pi.in_has_mc = pi.out_has_mc = registered && caps_.nvls;
+  pi.forced = parse_algo(cfg_.algo);
+  if (pi.forced == Algo::Ring) pi.forced = Algo::Auto;
+  Plan p = make_plan(pi, caps_, cfg_);
+  return p.valid ? p.spec.algo : Algo::Auto;
+}
+
+std::string Comm::stats_json() {
+  std::ostringstream o;
+  o << "{\"rank\":" << rank_ << ",\"size\":" << size_ << ",\"plane\":\"" << (gpu_plane_ ? "nvlink" : (transport_ ? transport_->name() : "none"))
+    << "\",\"device\":" << device_ << ",\"symmetric_provider\":\"" << (symm_ ? symm_->provider() : "none") << "\",\"nvls\":"
+    << (caps_.nvls ? "true" : "false") << ",\"calls\":" << stats_.calls << ",\"bytes\":" << stats_.bytes << ",\"algo\":{";
+  const Algo algos[] = {Algo::LL, Algo::OneShot, Algo::TwoShot, Algo::Nvls, Algo::Ring, Algo::Local};
+  bool first = true;
+  for (Algo a : algos) {
+    if (!first) o << ",";
+    first = false;
+    o << "\"" << algo_name(a) << "\":" << stats_.by_algo[static_cast<int>(a)];
+  }
+  o << "},\"zero_copy_in\":" << stats_.zero_copy_in << ",\"zero_copy_out\":" << stats_.zero_copy_out
+    << ",\"staged_calls\":" << stats_.staged_passes << ",\"graph_captures_seen\":" << stats_.graph_captures_seen;
+  if (watchdog_) {
+    o << ",\"watchdog\":{\"polls\":" << watchdog_->stats().polls.load() << ",\"trips\":" << watchdog_->stats().trips.load()
+      << ",\"device_failures\":" << watchdog_->stats().device_failures.load() << ",\"remote_aborts\":"
+      << watchdog_->stats().remote_aborts.load() << "}";
+  }
+  if (progress_host_) o << ",\"progress\":{\"started\":" << progress_host_[0] << ",\"done\":" << progress_host_[1] << ",\"status\":" << progress_host_[2] << "}";
+  if (transport_) {
+    TransportStats& t = transport_->stats();
+    o << ",\"transport\":{\"writes\":" << t.writes.load() << ",\"flag_writes\":" << t.flag_writes.load() << ",\"bytes\":"
+      << t.bytes_written.load() << ",\"signaled\":" << t.signaled.load() << ",\"reg_hits\":" << t.reg_hits.load()
+      << ",\"reg_misses\":" << t.reg_misses.load() << ",\"completion_errors\":" << t.completion_errors.load() << "}";
+  }
+  if (ring_) {
+    const RingStats& r = ring_->stats();
+    o << ",\"ring\":{\"calls\":" << r.calls << ",\"slices_sent\":" << r.slices_sent << ",\"credit_stalls\":" << r.credit_stalls
+      << ",\"window_stalls\":" << r.window_stalls << ",\"slice_bytes\":" << ring_->slice_bytes() << ",\"slots\":" << ring_->slots() << "}";
+  }
+  o << ",\"aborted\":" << (aborted_.load() ? "true" : "false") << "}";
+  return o.str();
+}
+
+}  // namespace mnccl

@@ -1,0 +1,118 @@
+// The communicator: what the opaque ncclComm_t points at.  It owns the
+// bootstrap store, the data plane (NVLink symmetric memory + kernels, or the
+// network ring), the watchdog and the counters.  Plays the role of the
+// reference's Context + transport pair (reference: include/mini_nccl.h:71-111,
+// src/api.cpp:55-59) with two data planes instead of one.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "algo/select.h"
+#include "core/config.h"
+#include "core/dtype.h"
+#include "core/error.h"
+#include "kernels/comm_dev.h"
+#include "kernels/launch.h"
+
+namespace mnccl {
+
+class BootstrapStore;
+class FdChannel;
+class SymmetricMemory;
+struct Segment;
+class Watchdog;
+class OneSidedTransport;
+class RingAllReduce;
+namespace hera { class Worker; }
+
+struct CommStats {
+  uint64_t calls = 0, bytes = 0;
+  uint64_t by_algo[8] = {0};
+  uint64_t zero_copy_in = 0, zero_copy_out = 0, staged_passes = 0;
+  uint64_t graph_captures_seen = 0, errors = 0;
+};
+
+class Comm {
+ public:
+  // rank == -1: Hera auto-bootstrap, `ip` names the master.  Throws Error.
+  static Comm* create(int nranks, int rank, const char* ip);
+  ~Comm();
+
+  int rank() const { return rank_; }
+  int size() const { return size_; }
+  bool gpu_plane() const { return gpu_plane_; }
+
+  void all_reduce(const void* send, DType send_t, void* recv, DType recv_t, DType wire_t, size_t count, RedOp op,
+                  double scale, Algo forced, cudaStream_t stream);
+  void reduce_scatter(const void* send, void* recv, size_t recvcount, DType t, RedOp op, cudaStream_t stream);
+  void all_gather(const void* send, void* recv, size_t sendcount, DType t, cudaStream_t stream);
+
+  void* mem_alloc(size_t bytes);
+  void mem_free(void* ptr);
+  void peer_pointers(void* ptr, void** peers, void** mc);
+  void barrier();
+  void abort();
+  Result async_error();
+  std::string stats_json();
+  Algo query_algo(size_t bytes, DType t, RedOp op, bool registered);
+  const CommDev& device_handle() const { return dev_; }
+
+ private:
+  Comm() = default;
+  void init(int nranks, int rank, const char* ip);
+  void init_gpu_plane();
+  void init_net_plane();
+  void setup_shared_host_segment();
+  void check_usable();
+  void launch(Mode mode, const void* send, DType send_t, void* recv, DType recv_t, DType wire_t, size_t count,
+              RedOp op, double scale, Algo forced, cudaStream_t stream);
+  void ring_all_reduce(const void* send, void* recv, size_t count, DType t, RedOp op, cudaStream_t stream);
+  // Segment containing [ptr, ptr+bytes) on this rank; offset returned.
+  std::shared_ptr<Segment> find_segment(const void* ptr, size_t bytes, size_t* offset);
+  void wait_blocking(cudaStream_t stream);
+
+  int rank_ = 0, size_ = 1;
+  int local_rank_ = 0, local_size_ = 1;
+  int device_ = -1;
+  bool has_gpu_ = false, gpu_plane_ = false;
+  Config cfg_;
+  std::string root_ip_, job_ns_;
+
+  std::unique_ptr<hera::Worker> hera_;
+  std::unique_ptr<BootstrapStore> store_;
+  std::unique_ptr<FdChannel> fds_;
+  std::unique_ptr<SymmetricMemory> symm_;
+  std::shared_ptr<Segment> ctrl_;
+  std::mutex seg_mu_;
+  std::map<uintptr_t, std::shared_ptr<Segment>> user_segments_;  // keyed by local base address
+  CommDev dev_{};
+  CommCaps caps_{};
+
+  // host-mapped words shared by the ranks of this host
+  void* shm_map_ = nullptr;
+  size_t shm_bytes_ = 0;
+  bool shm_registered_ = false;
+  void* private_host_ = nullptr;  // fallback when the shared mapping cannot be registered
+  volatile uint32_t* abort_host_ = nullptr;
+  volatile uint32_t* progress_host_ = nullptr;
+  std::unique_ptr<Watchdog> watchdog_;
+
+  // network plane
+  std::unique_ptr<OneSidedTransport> transport_;
+  std::unique_ptr<RingAllReduce> ring_;
+  void* bounce_ = nullptr;
+  size_t bounce_bytes_ = 0;
+
+  std::atomic<bool> aborted_{false};
+  std::atomic<bool> capture_warned_{false};
+  std::mutex call_mu_;
+  CommStats stats_;
+};
+
+}  // namespace mnccl

@@ -1,0 +1,140 @@
+#include "core/config.h"
+
+#include <cerrno>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <strings.h>
+
+#include "core/error.h"
+#include "core/log.h"
+
+namespace mnccl {
+namespace {
+
+const char* env_getter(const char* name, void*) { return std::getenv(name); }
+
+long long parse_ll(const char* name, const char* s) {
+  errno = 0;
+  char* end = nullptr;
+  long long v = std::strtoll(s, &end, 10);
+  while (end && (*end == ' ' || *end == '\t' || *end == '\n')) ++end;
+  // Accept K/M/G suffixes (powers of two) as a convenience.
+  if (end && *end && !end[1]) {
+    if (*end == 'k' || *end == 'K') { v <<= 10; ++end; }
+    else if (*end == 'm' || *end == 'M') { v <<= 20; ++end; }
+    else if (*end == 'g' || *end == 'G') { v <<= 30; ++end; }
+  }
+  if (errno != 0 || end == s || (end && *end)) {
+    fail(Result::InvalidArgument, std::string("malformed value for ") + name + ": '" + s + "'");
+  }
+  return v;
+}
+
+bool parse_bool(const char* name, const char* s) {
+  if (!strcasecmp(s, "1") || !strcasecmp(s, "true") || !strcasecmp(s, "on") || !strcasecmp(s, "yes")) return true;
+  if (!strcasecmp(s, "0") || !strcasecmp(s, "false") || !strcasecmp(s, "off") || !strcasecmp(s, "no")) return false;
+  fail(Result::InvalidArgument, std::string("malformed boolean for ") + name + ": '" + s + "'");
+}
+
+struct Reader {
+  Config::Getter get;
+  void* ctx;
+  const char* raw(const char* n) const {
+    const char* v = get(n, ctx);
+    return (v && *v) ? v : nullptr;
+  }
+  template <typename T>
+  void num(const char* n, T& out) const {
+    if (const char* v = raw(n)) out = static_cast<T>(parse_ll(n, v));
+  }
+  void boolean(const char* n, bool& out) const {
+    if (const char* v = raw(n)) out = parse_bool(n, v);
+  }
+  void str(const char* n, std::string& out) const {
+    if (const char* v = raw(n)) out = v;
+  }
+};
+
+std::mutex g_mu;
+Config* g_cfg = nullptr;
+bool g_banner_printed = false;
+
+}  // namespace
+
+Config Config::from_getter(Getter get, void* ctx) {
+  Config c;
+  Reader r{get, ctx};
+  if (const char* v = r.raw("MINI_NCCL_SLICE_SIZE")) {
+    long long x = parse_ll("MINI_NCCL_SLICE_SIZE", v);
+    if (x < 0) fail(Result::InvalidArgument, "MINI_NCCL_SLICE_SIZE must be >= 0");
+    c.slice_size = static_cast<size_t>(x);
+  }
+  r.num("MINI_NCCL_WINDOW_SIZE", c.window_size);
+  r.num("MINI_NCCL_SIGNAL_BATCH", c.signal_batch);
+  if (c.slice_size == 0) c.slice_size = 1024;
+  if (c.window_size <= 0) c.window_size = 1;
+  if (c.signal_batch <= 0) c.signal_batch = 1;
+  r.boolean("MINI_NCCL_GDR_ENABLE", c.gdr_enable);
+  r.str("MINI_NCCL_NET_DEVICE", c.net_device);
+
+  r.num("MINI_NCCL_BOOTSTRAP_PORT", c.bootstrap_port);
+  r.num("MINI_NCCL_HERA_PORT", c.hera_port);
+  r.num("MINI_NCCL_WATCHDOG_TIMEOUT_MS", c.watchdog_timeout_ms);
+  r.boolean("MINI_NCCL_WATCHDOG", c.watchdog_enable);
+  r.num("MINI_NCCL_SOCKET_TIMEOUT_MS", c.socket_timeout_ms);
+  r.num("MINI_NCCL_CONNECT_RETRIES", c.connect_retries);
+  r.str("MINI_NCCL_TRANSPORT", c.transport);
+  r.str("MINI_NCCL_SYMM", c.symm_mode);
+  r.boolean("MINI_NCCL_NVLS_ENABLE", c.nvls_enable);
+  r.str("MINI_NCCL_ALGO", c.algo);
+  r.num("MINI_NCCL_LL_MAX_BYTES", c.ll_max_bytes);
+  r.num("MINI_NCCL_ONESHOT_MAX_BYTES", c.oneshot_max_bytes);
+  r.num("MINI_NCCL_NVLS_MIN_BYTES", c.nvls_min_bytes);
+  r.num("MINI_NCCL_STAGING_BYTES", c.staging_bytes);
+  r.num("MINI_NCCL_MAX_BLOCKS", c.max_blocks);
+  r.boolean("MINI_NCCL_NUMA_BIND", c.numa_bind);
+  r.num("MINI_NCCL_CUDA_DEVICE", c.cuda_device);
+  r.boolean("MINI_NCCL_HERA_KEEPALIVE", c.hera_keepalive);
+  r.str("MINI_NCCL_JOB_ID", c.job_id);
+  r.boolean("MINI_NCCL_BLOCKING", c.blocking);
+  r.boolean("MINI_NCCL_AUTO_DEVICE", c.auto_device);
+
+  if (c.bootstrap_port <= 0 || c.bootstrap_port > 65535) fail(Result::InvalidArgument, "MINI_NCCL_BOOTSTRAP_PORT out of range");
+  if (c.hera_port <= 0 || c.hera_port > 65535) fail(Result::InvalidArgument, "MINI_NCCL_HERA_PORT out of range");
+  if (c.watchdog_timeout_ms <= 0) c.watchdog_timeout_ms = 1;
+  if (c.socket_timeout_ms <= 0) c.socket_timeout_ms = 1;
+  if (c.connect_retries <= 0) c.connect_retries = 1;
+  if (c.staging_bytes < (1u << 20)) c.staging_bytes = 1u << 20;
+  c.staging_bytes = (c.staging_bytes + 4095) & ~size_t(4095);
+  return c;
+}
+
+Config Config::from_env() { return from_getter(env_getter, nullptr); }
+
+const Config& Config::get() {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_cfg) g_cfg = new Config(from_env());
+  if (!g_banner_printed) {
+    g_banner_printed = true;
+    log_always("Config", "%s", g_cfg->banner().c_str());
+  }
+  return *g_cfg;
+}
+
+const Config& Config::reload() {
+  std::lock_guard<std::mutex> lk(g_mu);
+  Config fresh = from_env();
+  if (!g_cfg) g_cfg = new Config(fresh);
+  else *g_cfg = fresh;
+  return *g_cfg;
+}
+
+std::string Config::banner() const {
+  char buf[160];
+  snprintf(buf, sizeof(buf), "Loaded: SLICE_SIZE=%zu B, WINDOW=%d, BATCH=%d", slice_size,
+           window_size, signal_batch);
+  return buf;
+}
+
+}  // namespace mnccl

@@ -1,0 +1,62 @@
+// Environment knobs.  The three reference knobs keep their names, defaults and
+// clamps (reference: include/Config.h:29-51): MINI_NCCL_SLICE_SIZE (bytes,
+// default 131072, 0 -> 1024), MINI_NCCL_WINDOW_SIZE (default 64, <=0 -> 1),
+// MINI_NCCL_SIGNAL_BATCH (default 16).  Unlike the reference, SIGNAL_BATCH is
+// validated (<=0 -> 1; the reference would compute `s % 0`) and malformed
+// numbers raise InvalidArgument instead of an uncaught std::invalid_argument.
+// The banner "[Config] Loaded: SLICE_SIZE=... B, WINDOW=..., BATCH=..." is
+// printed once per process.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <string>
+
+namespace mnccl {
+
+struct Config {
+  // --- reference knobs ---
+  size_t slice_size = 128 * 1024;
+  int window_size = 64;
+  int signal_batch = 16;
+  bool gdr_enable = false;  // reserved in the reference; MINI_NCCL_GDR_ENABLE here
+  std::string net_device;   // MINI_NCCL_NET_DEVICE (exact NIC name override)
+
+  // --- new knobs ---
+  int bootstrap_port = 8888;          // MINI_NCCL_BOOTSTRAP_PORT (reference: fixed 8888)
+  int hera_port = 9999;               // MINI_NCCL_HERA_PORT      (reference: fixed 9999)
+  int watchdog_timeout_ms = 10000;    // MINI_NCCL_WATCHDOG_TIMEOUT_MS (reference: fixed 10 s)
+  bool watchdog_enable = true;        // MINI_NCCL_WATCHDOG
+  int socket_timeout_ms = 30000;      // MINI_NCCL_SOCKET_TIMEOUT_MS (reference: unbounded)
+  int connect_retries = 20;           // MINI_NCCL_CONNECT_RETRIES (reference: 20 x 1 s)
+  std::string transport = "auto";     // MINI_NCCL_TRANSPORT = auto|nvlink|soft|verbs
+  std::string symm_mode = "auto";     // MINI_NCCL_SYMM = auto|vmm|ipc
+  bool nvls_enable = true;            // MINI_NCCL_NVLS_ENABLE
+  std::string algo = "auto";          // MINI_NCCL_ALGO = auto|ll|oneshot|twoshot|nvls|ring
+  size_t ll_max_bytes = 0;            // MINI_NCCL_LL_MAX_BYTES      (0 = built-in table)
+  size_t oneshot_max_bytes = 0;       // MINI_NCCL_ONESHOT_MAX_BYTES (0 = built-in table)
+  size_t nvls_min_bytes = 0;          // MINI_NCCL_NVLS_MIN_BYTES    (0 = built-in table)
+  size_t staging_bytes = 64u << 20;   // MINI_NCCL_STAGING_BYTES (per direction, per rank)
+  int max_blocks = 0;                 // MINI_NCCL_MAX_BLOCKS (0 = built-in)
+  bool numa_bind = true;              // MINI_NCCL_NUMA_BIND (verbs path only, calling thread)
+  int cuda_device = -1;               // MINI_NCCL_CUDA_DEVICE (-1 = current device)
+  bool hera_keepalive = false;        // MINI_NCCL_HERA_KEEPALIVE (heartbeat + global abort)
+  std::string job_id;                 // MINI_NCCL_JOB_ID (namespace for shm / unix sockets)
+  bool blocking = false;              // MINI_NCCL_BLOCKING: AllReduce returns only when the stream work is done (reference behaviour)
+  bool auto_device = true;            // MINI_NCCL_AUTO_DEVICE: in Hera mode pick GPU = local rank when ranks share a device
+
+  // Parse from the process environment.  Throws Error(InvalidArgument) on
+  // malformed numbers.  Does not print.
+  static Config from_env();
+  // Parse from an explicit lookup function (unit tests).
+  using Getter = const char* (*)(const char* name, void* ctx);
+  static Config from_getter(Getter get, void* ctx);
+
+  // Process-wide instance: parsed on first use, banner printed once.
+  static const Config& get();
+  // Re-read the environment (tests); prints no banner.
+  static const Config& reload();
+
+  std::string banner() const;
+};
+
+}  // namespace mnccl

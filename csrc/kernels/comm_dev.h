@@ -1,0 +1,81 @@
+// Device-visible description of a communicator, shared by the library's own
+// kernels and by user kernels that fuse a collective (obtained through
+// mncclCommDeviceHandle).  Plain C structs: no constructors, fixed layout.
+//
+// Every rank owns one "control segment" of symmetric memory that all peers map
+// (NVLink P2P).  Its layout, at the byte offsets stored below:
+//
+//   sig      [kMaxBlocks][kMaxRanks] u32   barrier signals written by peers
+//   local    LocalState                    this rank's private counters
+//   ll       [2][nranks][ll_slot_bytes]    one-shot "LL" inboxes (flag+data)
+//   inbox    [2][nranks][inbox_slot_bytes] one-shot inboxes (barrier flavour)
+//   stage_a  [stage_bytes]                 staged inputs  (wire type)
+//   stage_b  [stage_bytes]                 staged outputs (output type)
+//
+// The reference keeps its flags and scratch in host-pinned memory that the GPU
+// polls across PCIe and relaunches a one-thread wait kernel per slice
+// (reference: src/mini_nccl.cu:22-36, src/transport/RDMATransport.h:113-123);
+// here flags live in device memory of the rank that waits on them and every
+// wait happens inside the data kernel.
+#pragma once
+#include <stdint.h>
+
+namespace mnccl {
+
+constexpr int kMaxRanks = 16;
+constexpr int kMaxBlocks = 512;
+
+// Status codes a kernel can leave in LocalState::status / host_progress[2].
+enum DevStatus : uint32_t {
+  kDevOk = 0,
+  kDevTimeout = 1,   // a bounded wait ran out
+  kDevAborted = 2,   // the abort word was set while waiting
+};
+
+struct LocalState {
+  uint32_t epoch[kMaxBlocks];    // per-block barrier epoch (monotonic)
+  uint32_t ll_seq[kMaxBlocks];   // per-block LL sequence (flag value source)
+  uint32_t ticket;               // blocks finished in the running kernel
+  uint32_t started;              // collectives started on this rank
+  uint32_t done;                 // collectives finished on this rank
+  uint32_t status;               // first failure (DevStatus), sticky
+  uint32_t detail;               // (block << 16) | peer of the first failure
+  uint32_t pad[3];
+};
+
+struct CommDev {
+  int32_t rank;
+  int32_t nranks;
+  char* ctrl[kMaxRanks];          // control segment of every rank, as mapped here
+  char* ctrl_mc;                  // multicast mapping of the control segment (NVLS) or null
+  const volatile uint32_t* abort_word;  // host-mapped, shared by all local ranks; may be null
+  volatile uint32_t* host_progress;     // host-mapped {started, done, status, detail}; may be null
+  uint64_t spin_timeout_ns;       // budget of every device-side wait
+  uint64_t off_sig, off_local, off_ll, off_inbox, off_stage_a, off_stage_b;
+  uint64_t ll_slot_bytes, inbox_slot_bytes, stage_bytes;
+};
+
+// Arguments of one AllReduce / ReduceScatter / AllGather launch.
+struct CollArgs {
+  const void* send;
+  void* recv;
+  uint64_t count;            // AllReduce: elements; RS: recv elements per rank; AG: send elements per rank
+  uint64_t shard_elems;      // elements per rank-shard inside the kernel (AllReduce: multiple of the vector width)
+  uint64_t chunk_shard_vecs; // staged paths: vectors of one shard handled per staging pass
+  float scale_f;             // post-reduction factor for fp16 / bf16 / fp32 (includes 1/N for Avg)
+  int32_t int_div;           // integer Avg divisor (0 = none)
+  double scale_d;            // same for fp64
+  char* in_peer[kMaxRanks];  // input view on every rank: stage_a, or a symmetric user buffer (zero-copy)
+  char* out_peer[kMaxRanks]; // output view on every rank: stage_b, or a symmetric user buffer
+  char* in_mc;               // multicast views (NVLS) or null
+  char* out_mc;
+  int32_t copy_in;           // 1: inputs are first staged from `send`
+  int32_t copy_out;          // 1: outputs are copied from stage_b to `recv`
+};
+
+struct KParams {
+  CommDev comm;
+  CollArgs args;
+};
+
+}  // namespace mnccl

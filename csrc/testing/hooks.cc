@@ -1,0 +1,377 @@
+// C entry points that expose internal components to the Python test-suite
+// (ctypes).  They are thin: each one drives a component the way its users do
+// and reports what happened.  Nothing here is on a hot path.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <sstream>
+#include <unistd.h>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "algo/select.h"
+#include "bootstrap/fdpass.h"
+#include "bootstrap/hera.h"
+#include "bootstrap/store.h"
+#include "core/config.h"
+#include "core/error.h"
+#include "core/log.h"
+#include "net/nic_select.h"
+#include "net/reg_cache.h"
+#include "net/request_pool.h"
+#include "net/ring.h"
+#include "net/soft_transport.h"
+#include "net/spsc_queue.h"
+#include "ref/oracle.h"
+#include "watchdog/watchdog.h"
+
+using namespace mnccl;
+
+namespace {
+template <typename Fn>
+int guarded(Fn&& fn) {
+  try {
+    return fn();
+  } catch (const Error& e) {
+    return 100 + static_cast<int>(e.code());
+  } catch (const std::exception&) {
+    return 99;
+  }
+}
+void copy_out(const std::string& s, char* out, size_t len) {
+  if (!out || !len) return;
+  size_t n = s.size() < len - 1 ? s.size() : len - 1;
+  memcpy(out, s.data(), n);
+  out[n] = 0;
+}
+}  // namespace
+
+extern "C" {
+#define MNCCL_EXPORT __attribute__((visibility("default")))
+
+// ---- oracle ---------------------------------------------------------------
+MNCCL_EXPORT int mnccl_oracle_allreduce(int in_t, int wire_t, int out_t, int op, int nranks, const void* const* inputs,
+                                        void* out, size_t count, double scale) {
+  return guarded([&] {
+    oracle_allreduce(static_cast<DType>(in_t), static_cast<DType>(wire_t), static_cast<DType>(out_t),
+                     static_cast<RedOp>(op), nranks, inputs, out, count, scale);
+    return 0;
+  });
+}
+MNCCL_EXPORT int mnccl_verify_f32(const float* got, const float* want, size_t n, float atol, size_t* first_bad) {
+  return verify_f32_avx2(got, want, n, atol, first_bad) ? 0 : 1;
+}
+MNCCL_EXPORT int mnccl_verify_const_f32(const float* got, float want, size_t n, float atol, size_t* first_bad) {
+  return verify_const_f32_avx2(got, want, n, atol, first_bad) ? 0 : 1;
+}
+MNCCL_EXPORT void mnccl_sum_f32(const float* a, const float* b, float* out, size_t n) { sum_f32_avx2(a, b, out, n); }
+MNCCL_EXPORT int mnccl_cpu_has_avx2() { return cpu_has_avx2() ? 1 : 0; }
+MNCCL_EXPORT uint16_t mnccl_float_to_bf16(float f) { return float_to_bf16(f); }
+MNCCL_EXPORT uint16_t mnccl_float_to_half(float f) { return float_to_half(f); }
+MNCCL_EXPORT float mnccl_bf16_to_float(uint16_t h) { return bf16_to_float(h); }
+MNCCL_EXPORT float mnccl_half_to_float(uint16_t h) { return half_to_float(h); }
+
+// ---- config ---------------------------------------------------------------
+// env: "NAME=value;NAME=value".  out: JSON of the parsed knobs.
+MNCCL_EXPORT int mnccl_test_config(const char* env, char* out, size_t len) {
+  return guarded([&] {
+    std::map<std::string, std::string> kv;
+    std::stringstream ss(env ? env : "");
+    std::string item;
+    while (std::getline(ss, item, ';')) {
+      size_t eq = item.find('=');
+      if (eq != std::string::npos) kv[item.substr(0, eq)] = item.substr(eq + 1);
+    }
+    Config c = Config::from_getter(
+        [](const char* name, void* ctx) -> const char* {
+          auto* m = static_cast<std::map<std::string, std::string>*>(ctx);
+          auto it = m->find(name);
+          return it == m->end() ? nullptr : it->second.c_str();
+        },
+        &kv);
+    std::ostringstream o;
+    o << "{\"slice_size\":" << c.slice_size << ",\"window_size\":" << c.window_size << ",\"signal_batch\":" << c.signal_batch
+      << ",\"net_device\":\"" << c.net_device << "\",\"watchdog_timeout_ms\":" << c.watchdog_timeout_ms
+      << ",\"bootstrap_port\":" << c.bootstrap_port << ",\"hera_port\":" << c.hera_port << ",\"staging_bytes\":" << c.staging_bytes
+      << ",\"algo\":\"" << c.algo << "\",\"nvls_enable\":" << (c.nvls_enable ? "true" : "false") << ",\"banner\":\"" << c.banner() << "\"}";
+    copy_out(o.str(), out, len);
+    return 0;
+  });
+}
+
+// ---- SPSC queue -----------------------------------------------------------
+// One producer thread, one consumer thread, n items; checks order and loss.
+MNCCL_EXPORT int mnccl_test_spsc(int capacity, int n_items) {
+  SpscQueue<int> q(static_cast<size_t>(capacity));
+  if (!q.empty()) return 1;
+  // full / empty behaviour, single-threaded
+  int filled = 0;
+  while (q.push(filled)) ++filled;
+  if (filled < capacity) return 2;
+  int v = -1;
+  for (int i = 0; i < filled; ++i) {
+    if (!q.pop(&v) || v != i) return 3;
+  }
+  if (q.pop(&v)) return 4;
+  std::atomic<int> bad{0};
+  std::thread prod([&] {
+    for (int i = 0; i < n_items; ++i)
+      while (!q.push(i)) std::this_thread::yield();
+  });
+  std::thread cons([&] {
+    int x;
+    for (int i = 0; i < n_items; ++i) {
+      while (!q.pop(&x)) std::this_thread::yield();
+      if (x != i) bad++;
+    }
+  });
+  prod.join();
+  cons.join();
+  return bad.load() ? 5 : 0;
+}
+
+// ---- request pool ---------------------------------------------------------
+MNCCL_EXPORT int mnccl_test_request_pool(int n) {
+  RequestPool pool(static_cast<size_t>(n));
+  std::vector<Request*> held;
+  for (int i = 0; i < n; ++i) {
+    Request* r = pool.acquire(static_cast<uint64_t>(i));
+    if (!r || r->wr_id() != static_cast<uint64_t>(i) || r->completed()) return 1;
+    held.push_back(r);
+  }
+  if (pool.acquire(0) != nullptr) return 2;  // exhaustion is reported, not hidden
+  held[0]->complete(7);
+  if (!held[0]->completed() || held[0]->status() != 7) return 3;
+  pool.release(held[0]);
+  Request* again = pool.acquire(42);
+  if (!again || again->completed() || again->status() != 0 || again->wr_id() != 42) return 4;
+  pool.release(again);
+  for (size_t i = 1; i < held.size(); ++i) pool.release(held[i]);
+  return pool.available() == static_cast<size_t>(n) ? 0 : 5;
+}
+
+// ---- registration cache ---------------------------------------------------
+MNCCL_EXPORT int mnccl_test_reg_cache() {
+  struct H { int id; };
+  int made = 0;
+  RegistrationCache<H> cache(3);
+  auto make = [&](void*, size_t) { auto h = std::make_shared<H>(); h->id = ++made; return h; };
+  char* base = reinterpret_cast<char*>(0x100000);
+  auto a = cache.get(base, 4096, make);
+  if (made != 1) return 1;
+  if (cache.get(base, 1024, make)->id != a->id || made != 1) return 2;           // smaller request hits
+  if (cache.get(base + 512, 1024, make)->id != a->id || made != 1) return 3;     // interior pointer hits
+  if (cache.get(base, 8192, make)->id == a->id || made != 2) return 4;           // larger request re-registers
+  cache.get(base + 0x10000, 64, make);
+  cache.get(base + 0x20000, 64, make);
+  if (cache.size() != 3) return 5;
+  cache.get(base, 64, make);                 // touch: base is most recently used
+  cache.get(base + 0x30000, 64, make);       // evicts the least recently used (0x10000)
+  if (cache.size() != 3 || cache.evictions() != 1) return 6;
+  int before = made;
+  cache.get(base + 0x10000, 64, make);
+  if (made != before + 1) return 7;          // it was evicted, so this is a miss
+  if (cache.invalidate(base, 0) != 1) return 8;
+  before = made;
+  cache.get(base, 64, make);
+  if (made != before + 1) return 9;          // invalidated entries miss
+  if (cache.hits() < 3 || cache.misses() < 5) return 10;
+  return 0;
+}
+
+// ---- NIC / NUMA -----------------------------------------------------------
+MNCCL_EXPORT int mnccl_test_select_nic(const char* csv, const char* override_name, int* index) {
+  return guarded([&] {
+    std::vector<std::string> names;
+    std::stringstream ss(csv ? csv : "");
+    std::string n;
+    while (std::getline(ss, n, ',')) if (!n.empty()) names.push_back(n);
+    *index = select_nic(names, override_name ? override_name : "");
+    return 0;
+  });
+}
+MNCCL_EXPORT int mnccl_test_parse_cpu_list(const char* list, int* out, int max) {
+  std::vector<int> c = parse_cpu_list(list ? list : "");
+  for (int i = 0; i < static_cast<int>(c.size()) && i < max; ++i) out[i] = c[i];
+  return static_cast<int>(c.size());
+}
+MNCCL_EXPORT int mnccl_test_numa(const char* sysfs_root, const char* device, int* node, int* ncpus) {
+  *node = read_nic_numa_node(sysfs_root, device);
+  *ncpus = static_cast<int>(read_numa_cpus(sysfs_root, *node).size());
+  return 0;
+}
+
+// ---- planner --------------------------------------------------------------
+MNCCL_EXPORT int mnccl_test_plan(int nranks, int mode, uint64_t count, int in_t, int wire_t, int out_t, int op, int in_sym,
+                                 int out_sym, int nvls, int forced, uint64_t stage_bytes, int* algo, int* nblocks,
+                                 uint64_t* shard_elems, uint64_t* chunk_vecs, int* copy_in, int* copy_out) {
+  Config cfg;  // defaults, independent of the environment
+  CommCaps caps;
+  caps.nranks = nranks;
+  caps.nvls = nvls != 0;
+  caps.ll_slot_bytes = default_ll_slot_bytes(nranks, cfg);
+  caps.inbox_slot_bytes = default_inbox_slot_bytes(nranks, cfg);
+  caps.stage_bytes = stage_bytes ? stage_bytes : cfg.staging_bytes;
+  PlanInput pi;
+  pi.mode = static_cast<Mode>(mode);
+  pi.count = count;
+  pi.in = static_cast<DType>(in_t);
+  pi.wire = static_cast<DType>(wire_t);
+  pi.out = static_cast<DType>(out_t);
+  pi.op = static_cast<RedOp>(op);
+  pi.in_symmetric = in_sym;
+  pi.out_symmetric = out_sym;
+  pi.in_has_mc = in_sym && nvls;
+  pi.out_has_mc = out_sym && nvls;
+  pi.forced = static_cast<Algo>(forced);
+  Plan p = make_plan(pi, caps, cfg);
+  if (!p.valid) return 1;
+  *algo = static_cast<int>(p.spec.algo);
+  *nblocks = p.spec.nblocks;
+  *shard_elems = p.shard_elems;
+  *chunk_vecs = p.chunk_shard_vecs;
+  *copy_in = p.copy_in;
+  *copy_out = p.copy_out;
+  return 0;
+}
+
+// ---- watchdog -------------------------------------------------------------
+// Scenario 0: a collective that finishes in time; 1: one that never finishes;
+// 2: a kernel-reported failure.  Returns the abort word at the end (expected
+// 0, 1, 1) or a negative number on a logic error.
+MNCCL_EXPORT int mnccl_test_watchdog(int scenario, int timeout_ms) {
+  alignas(64) uint32_t words[32] = {0};
+  volatile uint32_t* abort_word = words;
+  volatile uint32_t* progress = words + 16;
+  Watchdog wd(progress, abort_word, timeout_ms, 0);
+  int trips = 0;
+  wd.set_on_trip([&](uint32_t) { ++trips; });
+  auto t0 = std::chrono::steady_clock::now();
+  auto at = [&](int ms) { return t0 + std::chrono::milliseconds(ms); };
+  wd.step(at(0));
+  progress[0] = 1;  // a collective started
+  wd.step(at(1));
+  if (scenario == 0) {
+    wd.step(at(timeout_ms / 2));
+    progress[1] = 1;  // ... and finished
+    wd.step(at(timeout_ms * 3));
+    progress[0] = 2;
+    wd.step(at(timeout_ms * 3 + 1));
+    progress[1] = 2;
+    wd.step(at(timeout_ms * 10));
+    if (wd.tripped() || trips) return -1;
+  } else if (scenario == 1) {
+    wd.step(at(timeout_ms / 2));
+    if (wd.tripped()) return -2;  // too early
+    wd.step(at(timeout_ms + 5));
+    if (!wd.tripped() || trips != 1) return -3;
+    wd.step(at(timeout_ms * 4));
+    if (trips != 1) return -4;  // trips once
+  } else {
+    progress[3] = 0x10002;
+    progress[2] = 1;
+    wd.step(at(2));
+    if (!wd.tripped() || trips != 1) return -5;
+  }
+  return static_cast<int>(*abort_word);
+}
+
+// ---- Hera -----------------------------------------------------------------
+MNCCL_EXPORT void* mnccl_hera_master_start(int world_size, int port, int heartbeat_timeout_ms) {
+  try {
+    auto* m = new hera::Master(world_size, port);
+    m->set_heartbeat_timeout_ms(heartbeat_timeout_ms);
+    m->start_background();
+    return m;
+  } catch (const std::exception& e) {
+    log_always("Hera-Master", "start failed: %s", e.what());
+    return nullptr;
+  }
+}
+MNCCL_EXPORT int mnccl_hera_master_port(void* m) { return static_cast<hera::Master*>(m)->port(); }
+MNCCL_EXPORT int mnccl_hera_master_registered(void* m) { return static_cast<int>(static_cast<hera::Master*>(m)->workers().size()); }
+MNCCL_EXPORT int mnccl_hera_master_abort_sent(void* m) { return static_cast<hera::Master*>(m)->abort_broadcast() ? 1 : 0; }
+MNCCL_EXPORT int mnccl_hera_master_worker(void* m, int idx, int* rank, int* pid, char* host, char* ip, int* alive) {
+  auto ws = static_cast<hera::Master*>(m)->workers();
+  if (idx < 0 || idx >= static_cast<int>(ws.size())) return 1;
+  *rank = ws[idx].rank;
+  *pid = ws[idx].pid;
+  copy_out(ws[idx].hostname, host, 64);
+  copy_out(ws[idx].ip, ip, 64);
+  *alive = ws[idx].alive ? 1 : 0;
+  return 0;
+}
+MNCCL_EXPORT void mnccl_hera_master_stop(void* m) {
+  auto* mm = static_cast<hera::Master*>(m);
+  mm->stop();
+  delete mm;
+}
+
+MNCCL_EXPORT void* mnccl_hera_worker_register(const char* ip, int port, int* rank, int* size, char* root_ip) {
+  try {
+    auto* w = new hera::Worker(ip, port);
+    w->connect_and_register(20, 100, 5000);
+    *rank = w->rank();
+    *size = w->size();
+    copy_out(w->root_ip(), root_ip, 64);
+    return w;
+  } catch (const std::exception& e) {
+    log_always("Hera-Worker", "register failed: %s", e.what());
+    return nullptr;
+  }
+}
+MNCCL_EXPORT int mnccl_hera_worker_topology(void* w, int* prev, int* next, char* next_ip) {
+  return guarded([&] {
+    hera::TopologyInfo t = static_cast<hera::Worker*>(w)->query_topology(3000);
+    *prev = t.prev_rank;
+    *next = t.next_rank;
+    copy_out(t.next_ip, next_ip, 64);
+    return 0;
+  });
+}
+static std::atomic<int> g_abort_seen[64];
+MNCCL_EXPORT int mnccl_hera_worker_start_agent(void* w, int period_ms, int slot) {
+  if (slot < 0 || slot >= 64) return 1;
+  g_abort_seen[slot].store(0);
+  static_cast<hera::Worker*>(w)->start_agent(period_ms, [slot](int origin, uint32_t reason) {
+    g_abort_seen[slot].store(1000 + (origin + 1) * 10 + static_cast<int>(reason));
+  });
+  return 0;
+}
+MNCCL_EXPORT int mnccl_hera_worker_abort_seen(int slot) { return g_abort_seen[slot].load(); }
+MNCCL_EXPORT int mnccl_hera_worker_send_abort(void* w, unsigned reason) {
+  return guarded([&] { static_cast<hera::Worker*>(w)->send_global_abort(reason); return 0; });
+}
+MNCCL_EXPORT void mnccl_hera_worker_set_state(void* w, unsigned s) { static_cast<hera::Worker*>(w)->set_local_state(s); }
+MNCCL_EXPORT void mnccl_hera_worker_free(void* w) { delete static_cast<hera::Worker*>(w); }
+
+// ---- fd passing -----------------------------------------------------------
+// Two channels in one process pass a pipe's write end; the receiver writes
+// through it and the sender reads the byte back.
+MNCCL_EXPORT int mnccl_test_fdpass(const char* ns) {
+  return guarded([&] {
+    FdChannel a(ns, 0), b(ns, 1);
+    a.open();
+    b.open();
+    int p[2];
+    if (pipe(p) != 0) return 1;
+    a.send_fd(1, p[1], 77, 2000);
+    int src = -1;
+    uint32_t tag = 0;
+    int got = b.recv_fd(&src, &tag, 2000);
+    if (src != 0 || tag != 77) return 2;
+    char c = 'x';
+    if (write(got, &c, 1) != 1) return 3;
+    char d = 0;
+    if (read(p[0], &d, 1) != 1 || d != 'x') return 4;
+    close(got);
+    close(p[0]);
+    close(p[1]);
+    return 0;
+  });
+}
+
+}  // extern "C"

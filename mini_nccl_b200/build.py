@@ -1,0 +1,173 @@
+"""In-tree native build of libmini_nccl.so and the command-line programs.
+
+Every CUDA translation unit is compiled for sm_100a only
+(``-gencode arch=compute_100a,code=sm_100a``); host files with g++.  Objects
+are cached under ``build/`` by source mtime, compilation runs in parallel.
+The shared library is written to ``mini_nccl_b200/lib/libmini_nccl.so`` and
+links the static CUDA runtime, so it loads on machines without a GPU driver
+(the network data plane and all host components work there).
+
+The reference builds with CMake and needs libibverbs and libnvToolsExt at
+configure time (reference: CMakeLists.txt:21-23); neither is required here:
+verbs support is compiled only when <infiniband/verbs.h> exists and NVTX is
+header-only.  A CMakeLists.txt at the repository root builds the same targets
+for C / C++ users.
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+CSRC = ROOT / "csrc"
+BUILD = ROOT / "build"
+LIBDIR = ROOT / "mini_nccl_b200" / "lib"
+BINDIR = ROOT / "mini_nccl_b200" / "bin"
+
+CUDA_HOME = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+NVCC = str(CUDA_HOME / "bin" / "nvcc")
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+
+HOST_SOURCES = [
+    "core/log.cc", "core/config.cc",
+    "bootstrap/socket.cc", "bootstrap/store.cc", "bootstrap/fdpass.cc", "bootstrap/hera.cc",
+    "net/soft_transport.cc", "net/nic_select.cc", "net/ring.cc", "net/factory.cc",
+    "mem/cuda_driver.cc", "mem/symmetric.cc",
+    "algo/select.cc", "watchdog/watchdog.cc", "ref/oracle.cc",
+    "comm.cc", "api.cc", "testing/hooks.cc",
+]
+CUDA_SOURCES = [
+    "kernels/k_small.cu", "kernels/k_twoshot.cu", "kernels/k_rsag.cu", "kernels/k_nvls.cu",
+    "kernels/launch.cu", "emu/emu_world.cu",
+]
+# Optional translation units: compiled when present (later build stages add them).
+OPTIONAL_CUDA = ["kernels/gemm_sm100.cu", "kernels/gemm_fused.cu", "kernels/noalloc.cu"]
+OPTIONAL_HOST = ["net/verbs_transport.cc"]
+
+PROGRAMS = {
+    # name -> (sources relative to ROOT, needs_cuda_runtime)
+    "hera_master": (["apps/hera_master.cpp"], False),
+    "hera_test": (["apps/hera_test.cpp"], False),
+    "app": (["apps/app.cpp"], True),
+    "perf_test": (["apps/perf_test.cpp"], True),
+}
+
+
+def _have_verbs() -> bool:
+    return any(Path(p, "infiniband", "verbs.h").exists() for p in ("/usr/include", "/usr/local/include"))
+
+
+def _common_includes() -> list[str]:
+    return ["-I", str(CSRC), "-I", str(ROOT / "include"), "-I", str(CUDA_HOME / "include")]
+
+
+def _obj_path(src: Path) -> Path:
+    tag = hashlib.sha1(str(src).encode()).hexdigest()[:8]
+    return BUILD / f"{src.stem}-{tag}.o"
+
+
+def _newest_header_mtime() -> float:
+    newest = 0.0
+    for pat in ("**/*.h", "**/*.cuh"):
+        for h in CSRC.glob(pat):
+            newest = max(newest, h.stat().st_mtime)
+    for h in (ROOT / "include").glob("*.h"):
+        newest = max(newest, h.stat().st_mtime)
+    return newest
+
+
+def _compile(src: Path, hdr_mtime: float, verbose: bool, extra: list[str]) -> Path:
+    obj = _obj_path(src)
+    if obj.exists() and obj.stat().st_mtime >= max(src.stat().st_mtime, hdr_mtime):
+        return obj
+    if src.suffix == ".cu":
+        cmd = [NVCC, "-std=c++17", "-O3", *ARCH, "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden",
+               *_common_includes(), *extra, "-c", str(src), "-o", str(obj)]
+    else:
+        cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-fvisibility=hidden", "-ffp-contract=off", "-Wall", "-Wextra",
+               "-pthread", *_common_includes(), *extra, "-c", str(src), "-o", str(obj)]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"compile failed: {src}\n{r.stdout}\n{r.stderr}")
+    if r.stderr.strip() and verbose:
+        print(r.stderr, file=sys.stderr)
+    return obj
+
+
+def lib_path() -> Path:
+    return LIBDIR / "libmini_nccl.so"
+
+
+def build(verbose: bool = False, programs: bool = True, jobs: int | None = None) -> Path:
+    """Build the shared library (and the programs).  Returns the library path."""
+    if not Path(NVCC).exists():
+        raise RuntimeError(f"nvcc not found at {NVCC}")
+    BUILD.mkdir(exist_ok=True)
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    BINDIR.mkdir(parents=True, exist_ok=True)
+    extra: list[str] = []
+    host = list(HOST_SOURCES)
+    cuda = list(CUDA_SOURCES)
+    for o in OPTIONAL_CUDA:
+        if (CSRC / o).exists():
+            cuda.append(o)
+    if _have_verbs() and (CSRC / "net/verbs_transport.cc").exists():
+        host.append("net/verbs_transport.cc")
+        extra.append("-DMNCCL_HAVE_VERBS=1")
+    srcs = [CSRC / s for s in host + cuda]
+    hdr = _newest_header_mtime()
+    jobs = jobs or max(1, (os.cpu_count() or 4))
+    with cf.ThreadPoolExecutor(max_workers=jobs) as ex:
+        objs = list(ex.map(lambda s: _compile(s, hdr, verbose, extra), srcs))
+    lib = lib_path()
+    newest_obj = max(o.stat().st_mtime for o in objs)
+    if not lib.exists() or lib.stat().st_mtime < newest_obj:
+        cmd = [NVCC, "-shared", *ARCH, "-cudart", "static", "-Xlinker", "-Bsymbolic-functions",
+               "-o", str(lib), *map(str, objs), "-lpthread", "-lrt", "-ldl"]
+        if "-DMNCCL_HAVE_VERBS=1" in extra:
+            cmd.append("-libverbs")
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed\n{r.stdout}\n{r.stderr}")
+    if programs:
+        for name, (sources, needs_cuda) in PROGRAMS.items():
+            paths = [ROOT / s for s in sources]
+            if not all(p.exists() for p in paths):
+                continue
+            out = BINDIR / name
+            newest = max([p.stat().st_mtime for p in paths] + [lib.stat().st_mtime, hdr])
+            if out.exists() and out.stat().st_mtime >= newest:
+                continue
+            cmd = ["g++", "-std=c++17", "-O2", "-mavx2", "-pthread", *_common_includes(), *map(str, paths),
+                   "-o", str(out), "-L", str(LIBDIR), "-lmini_nccl", f"-Wl,-rpath,$ORIGIN/../lib"]
+            if needs_cuda:
+                cmd += ["-L", str(CUDA_HOME / "lib64"), "-lcudart_static", "-ldl", "-lrt"]
+            if verbose:
+                print(" ".join(cmd), flush=True)
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError(f"program build failed: {name}\n{r.stdout}\n{r.stderr}")
+    return lib
+
+
+def clean() -> None:
+    shutil.rmtree(BUILD, ignore_errors=True)
+    for p in (lib_path(),):
+        if p.exists():
+            p.unlink()
+
+
+if __name__ == "__main__":
+    if len(sys.argv) > 1 and sys.argv[1] == "clean":
+        clean()
+    else:
+        print(build(verbose="-v" in sys.argv))
