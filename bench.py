@@ -1,0 +1,200 @@
+#!/usr/bin/env python
+"""Headline benchmark: AllReduce bus bandwidth (the metric BASELINE.json names).
+
+One "step" is one fp32 sum AllReduce of 256 MiB per rank through the library's
+public Python API (Communicator.all_reduce on a tensor from Communicator.empty),
+timed on the device with CUDA events, maximum over ranks.  The message is larger
+than the 126 MB L2, so iterations do not hit in cache.  `value` is the bus
+bandwidth algBW * 2(n-1)/n in GB/s (for one GPU, where that factor is zero, the
+algorithm bandwidth of the degenerate out-of-place call).  A sweep over message
+sizes (this library and NCCL side by side, fp32 and bf16) and the 8 KB latency
+are attached under "sweep".  The "e2e" number repeats the metric with, per step,
+the host-to-device copy of the input from pinned memory and the device-to-host
+read of the result inside the timed region.
+
+The reference library itself cannot run here (it needs libibverbs and an RDMA
+device at build and at run time); `--impl reference` reports that.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HEADLINE_BYTES = 256 << 20
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--bytes", type=int, default=HEADLINE_BYTES)
+    ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"])
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--sweep-max-bytes", type=int, default=1 << 30)
+    ap.add_argument("--unregistered", action="store_true", help="headline on ordinary torch tensors (staged path)")
+    return ap.parse_args()
+
+
+def reference_arm(args):
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "reference is a CMake/C++ project that needs libibverbs + libnvToolsExt at configure time and an "
+                       "RDMA device (rxe0/mlx5) at run time; neither exists on this image, and pip cannot install it "
+                       "(no setup.py / pyproject.toml)",
+    }))
+    return 0
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    torch.cuda.set_device(local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if "MINI_NCCL_BOOTSTRAP_PORT" not in os.environ:
+        os.environ["MINI_NCCL_BOOTSTRAP_PORT"] = str(int(os.environ.get("MASTER_PORT", "29500")) + 17)
+    os.environ.setdefault("MINI_NCCL_DEBUG", "WARN")
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    import mini_nccl_b200 as mn
+    from mini_nccl_b200.utils.timing import ClockSampler, bus_bandwidth_gbs, max_over_ranks
+
+    comm = mn.Communicator(world, rank, os.environ["MASTER_ADDR"])
+    dtype = torch.float32 if args.dtype == "fp32" else torch.bfloat16
+    esz = 4 if args.dtype == "fp32" else 2
+    count = args.bytes // esz
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    if args.unregistered or world == 1:
+        buf = torch.empty(count, dtype=dtype, device="cuda")
+    else:
+        buf = comm.empty(count, dtype)
+    buf.copy_(torch.randn(count, generator=gen, device="cuda", dtype=torch.float32).to(dtype))
+    out = torch.empty(count, dtype=dtype, device="cuda") if world == 1 else buf
+    stream = torch.cuda.current_stream()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def step():
+        # scale keeps the values bounded over many in-place iterations
+        comm.all_reduce(buf, "sum", out=out, scale=1.0 / world if world > 1 else 1.0)
+
+    # ---- headline: device-timed, K steps, max over ranks
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sync_all()
+    sampler = ClockSampler(torch.cuda.current_device()).start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    sync_all()
+    clocks = sampler.stop()
+    ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    alg, bus = bus_bandwidth_gbs(args.bytes, ms, world)
+    algo_used = comm.query_algo(args.bytes, dtype, "sum", registered=not (args.unregistered or world == 1))
+
+    # ---- end to end: pinned host input -> device -> AllReduce -> host, every step
+    host_in = torch.empty(count, dtype=dtype).pin_memory()
+    host_in.copy_(buf.cpu())
+    host_out = torch.empty(count, dtype=dtype).pin_memory()
+    def e2e_step():
+        buf.copy_(host_in, non_blocking=True)
+        comm.all_reduce(buf, "sum", out=out, scale=1.0 / world if world > 1 else 1.0)
+        host_out.copy_(out, non_blocking=True)
+    for _ in range(3):
+        e2e_step()
+    sync_all()
+    e2e_steps = max(3, min(args.steps, 20))
+    t0 = time.perf_counter()
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    e2e_ms = max_over_ranks(max(e0.elapsed_time(e1) / e2e_steps, wall_ms))
+    e2e_alg, e2e_bus = bus_bandwidth_gbs(args.bytes, e2e_ms, world)
+    sync_all()
+
+    # ---- sweep (ours vs NCCL), attached for context
+    sweep = None
+    if not args.no_sweep:
+        from benchmarks.sweep import run_sweep
+
+        sweep = run_sweep(comm, world, rank, max_bytes=args.sweep_max_bytes, quick=True)
+
+    stats = comm.stats()
+    if rank == 0:
+        line = {
+            "metric": "allreduce_busbw_GBps" if world > 1 else "allreduce_algbw_GBps_single_gpu",
+            "value": round(bus, 3),
+            "unit": "GB/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms, 5),
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": args.dtype,
+            "data": "synthetic: normal(0,1) seeded 1234+rank",
+            "impl": "ours",
+            "algbw_GBps": round(alg, 3),
+            "algorithm": algo_used,
+            "config": {
+                "model": "AllReduce sum, %d MiB per rank" % (args.bytes >> 20),
+                "global_batch": args.bytes * world,
+                "seq_len": count,
+                "parallelism": "allreduce x%d" % world,
+                "buffers": "ordinary device memory (staged)" if (args.unregistered or world == 1) else "symmetric memory (zero-copy)",
+                "l2": "message (%d MiB) larger than the 126 MB L2; no flush needed" % (args.bytes >> 20),
+                "timing": "CUDA events on the launching stream, max over ranks",
+                "nvls": bool(stats.get("nvls")),
+            },
+            "clocks": clocks,
+            "e2e": {
+                "value": round(e2e_bus, 3),
+                "unit": "GB/s",
+                "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": args.bytes,
+                "d2h_bytes_per_step": args.bytes,
+            },
+            "gpu_launches": args.steps,
+            "sweep": sweep,
+        }
+        print(json.dumps(line))
+        sys.stdout.flush()
+    if world > 1:
+        dist.barrier()
+    comm.destroy()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
