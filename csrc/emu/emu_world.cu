@@ -235,7 +235,8 @@ MNCCL_EXPORT int mncclEmuCollective(void* world, int mode, const void* const* se
     }
     const bool zc_in = !plan.copy_in && pi.mode != Mode::AllGather;
     const bool zc_out = !plan.copy_out && pi.mode != Mode::ReduceScatter;
-    for (int q = 0; q < N; ++q) {
+    const bool staged_algo = plan.spec.algo == Algo::TwoShot;
+    for (int q = 0; staged_algo && q < N; ++q) {
       a.in_peer[q] = zc_in ? w->segs[in_seg][q].first + in_off : w->ctrl[q] + w->dev[q].off_stage_a;
       a.out_peer[q] = zc_out ? w->segs[out_seg][q].first + out_off : w->ctrl[q] + w->dev[q].off_stage_b;
     }

@@ -45,7 +45,9 @@ bool kernel_exists(const LaunchSpec& spec) {
 }
 
 cudaError_t launch_collective(const LaunchSpec& spec, const KParams& p, cudaStream_t stream) {
-  if (spec.nblocks < 1 || spec.nblocks > kMaxBlocks || spec.nthreads < 32 || spec.nthreads > 512)
+  // Only kernels with per-block barrier state are bound by kMaxBlocks.
+  const int max_blocks = spec.algo == Algo::Local ? 65535 : kMaxBlocks;
+  if (spec.nblocks < 1 || spec.nblocks > max_blocks || spec.nthreads < 32 || spec.nthreads > 512)
     return cudaErrorInvalidConfiguration;
   dev::LaunchCtx x{&spec, &p, nullptr, 1, stream, nullptr};
   return route(x);

@@ -153,7 +153,7 @@ Request* SoftTransport::write_flag(int peer, RemoteBuffer remote_flags, uint32_t
     if (!req) fail(Result::InternalError, "request pool exhausted");
   }
   uint64_t nth = flag_posts_.fetch_add(1) + 1;
-  const bool drop = drop_at_.load() != 0 && nth == drop_at_.load();
+  const bool drop = drop_at_.load() != 0 && nth >= drop_at_.load();
   try {
     if (!drop) send_frame(peer, kFlag, remote_flags.rkey, value, remote_flags.addr + 4ull * index, nullptr, 4);
     else MNCCL_INFO("Mini-NCCL", "soft transport: dropping flag write #%llu (fault injection)", (unsigned long long)nth);

@@ -39,8 +39,10 @@ class SoftTransport : public OneSidedTransport {
   RemoteBuffer flags_remote() const override { return flags_remote_; }
   int max_outstanding() const override { return 1024; }
 
-  // Host-side fault injection for tests: the n-th flag write posted by this
-  // rank from now on (1-based) is dropped silently; 0 disables.
+  // Host-side fault injection for tests: from the n-th flag write posted by
+  // this rank on (1-based) every flag write is dropped silently, as if the
+  // link had gone quiet; 0 disables.  (A single lost flag would be healed by
+  // the next one: flags are monotonic counters.)
   void drop_flag_write_at(uint64_t n) { drop_at_.store(n); flag_posts_.store(0); }
   uint64_t remote_access_errors() const { return access_errors_.load(); }
 

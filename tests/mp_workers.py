@@ -1,0 +1,333 @@
+"""Worker bodies for the multi-process tests.  Each rank is its own Python process
+(`python tests/mp_workers.py <fn> <rank> <nranks> <json kwargs>`), prints one line
+`RESULT <json>` and exits 0; `run_ranks` starts them and collects the lines."""
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def run_ranks(fn: str, nranks: int, kwargs: dict | None = None, env: dict | None = None, timeout: float = 180.0,
+              per_rank_env: dict | None = None, expect_rc=None):
+    """Start `nranks` processes; return the list of result dicts ordered by rank."""
+    base = dict(os.environ)
+    base.update({k: str(v) for k, v in (env or {}).items()})
+    base["PYTHONPATH"] = str(ROOT) + os.pathsep + base.get("PYTHONPATH", "")
+    procs = []
+    for r in range(nranks):
+        e = dict(base)
+        for k, v in (per_rank_env or {}).get(r, {}).items():
+            e[k] = str(v)
+        procs.append(subprocess.Popen([sys.executable, str(Path(__file__)), fn, str(r), str(nranks), json.dumps(kwargs or {})],
+                                      env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    deadline = time.time() + timeout
+    outs = []
+    for r, p in enumerate(procs):
+        try:
+            o, err = p.communicate(timeout=max(1.0, deadline - time.time()))
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            o, err = p.communicate()
+            raise AssertionError(f"rank {r} timed out\nstdout:\n{o}\nstderr:\n{err[-4000:]}")
+        outs.append((p.returncode, o, err))
+    results = []
+    for r, (rc, o, err) in enumerate(outs):
+        want = 0 if expect_rc is None else expect_rc.get(r, 0)
+        line = [l for l in o.splitlines() if l.startswith("RESULT ")]
+        if rc != want or not line:
+            raise AssertionError(f"rank {r} exited {rc} (wanted {want})\nstdout:\n{o[-3000:]}\nstderr:\n{err[-6000:]}")
+        d = json.loads(line[-1][7:])
+        d["_stderr"] = err
+        results.append(d)
+    return results
+
+
+# --------------------------------------------------------------------------- helpers
+
+def _np_inputs(dtype, count, n, op, seed=1234):
+    from mini_nccl_b200.utils import oracle as O
+
+    return [O.make_input(dtype, count, r, seed=seed, op=op) for r in range(n)]
+
+
+def _bits_equal(a, b):
+    import numpy as np
+
+    return a.size == b.size and np.array_equal(a.view(np.uint8), b.view(np.uint8))
+
+
+# --------------------------------------------------------------------------- CPU: ring over the soft transport
+
+def cpu_ring(rank, n, kw):
+    """AllReduce through the C ABI on host buffers (no GPU): the network data plane."""
+    import ctypes as C
+
+    import numpy as np
+
+    import mini_nccl_b200 as mn
+    from mini_nccl_b200 import _lib
+    from mini_nccl_b200.utils import oracle as O
+
+    init_rank = -1 if kw.get("hera") else rank
+    comm = mn.Communicator(n, init_rank, kw.get("ip", "127.0.0.1"))
+    rank = comm.rank
+    n = comm.size
+    res = {"rank": rank, "size": n, "cases": 0, "max_err": 0.0}
+    for case in kw["cases"]:
+        dtype, op, count = case["dtype"], case["op"], case["count"]
+        ins = _np_inputs(dtype, count, n, op, seed=case.get("seed", 1234))
+        x = ins[rank].copy()
+        if case.get("in_place"):
+            out = x
+        else:
+            out = np.zeros_like(x)
+        for _ in range(case.get("repeat", 1)):
+            if case.get("in_place"):
+                x[:] = ins[rank]
+            rc = mn.lib().ncclAllReduce(x.ctypes.data, out.ctypes.data, count, dtype, op, comm.handle, None)
+            assert rc == 0, f"ncclAllReduce returned {rc}"
+        want = O.oracle_allreduce(ins, dtype, op)
+        if dtype == _lib.FLOAT32 and op == _lib.SUM:
+            bad = C.c_size_t()
+            ok = mn.lib().mnccl_verify_f32(out.ctypes.data, want.ctypes.data, count, 1e-5, C.byref(bad))
+            assert ok == 0, f"AVX2 verifier: mismatch at {bad.value}: {out[bad.value]} vs {want[bad.value]}"
+        if dtype in O.FLOAT_TYPES:
+            # The ring adds in ring order, the oracle in rank order: compare with a tolerance.
+            err = float(np.abs(O.to_float64(out, dtype) - O.to_float64(want, dtype)).max()) if count else 0.0
+            tol = {_lib.FLOAT32: 1e-5, _lib.FLOAT64: 1e-12, _lib.FLOAT16: 0.02, _lib.BFLOAT16: 0.1}[dtype] * (4 if op == _lib.PROD else 1)
+            assert err <= tol, f"{O.DTYPE_NAMES[dtype]} {O.OP_NAMES[op]} count {count}: err {err}"
+            res["max_err"] = max(res["max_err"], err)
+        else:
+            assert _bits_equal(out, want), f"{O.DTYPE_NAMES[dtype]} {O.OP_NAMES[op]} count {count}: integer mismatch"
+        res["cases"] += 1
+    res["stats"] = comm.stats()
+    comm.destroy()
+    return res
+
+
+def cpu_ring_fault(rank, n, kw):
+    """A dropped flag write (host-side fault) must end in a bounded error, not a hang."""
+    import numpy as np
+
+    import mini_nccl_b200 as mn
+    from mini_nccl_b200 import _lib
+
+    comm = mn.Communicator(n, rank, "127.0.0.1")
+    x = np.ones(1 << 16, np.float32)
+    t0 = time.time()
+    rc = mn.lib().ncclAllReduce(x.ctypes.data, x.ctypes.data, x.size, _lib.FLOAT32, _lib.SUM, comm.handle, None)
+    dt = time.time() - t0
+    err = comm.async_error() if rc != 0 else 0
+    # after a failure the communicator stays failed (sticky), and destroy does not hang
+    rc2 = mn.lib().ncclAllReduce(x.ctypes.data, x.ctypes.data, x.size, _lib.FLOAT32, _lib.SUM, comm.handle, None) if rc != 0 else 0
+    comm.abort()
+    comm.destroy()
+    return {"rank": rank, "rc": rc, "rc2": rc2, "seconds": dt, "async": err}
+
+
+# --------------------------------------------------------------------------- GPU: real multi-process data plane
+
+def gpu_battery(rank, n, kw):
+    import ctypes as C
+
+    import numpy as np
+    import torch
+
+    import mini_nccl_b200 as mn
+    from mini_nccl_b200 import _lib
+    from mini_nccl_b200.utils import oracle as O
+
+    torch.cuda.set_device(rank % torch.cuda.device_count())
+    init_rank = -1 if kw.get("hera") else rank
+    comm = mn.Communicator(n, init_rank, "127.0.0.1")
+    rank, n = comm.rank, comm.size
+    stats0 = comm.stats()
+    res = {"rank": rank, "nvls": bool(stats0["nvls"]), "provider": stats0["symmetric_provider"], "plane": stats0["plane"],
+           "cases": 0, "algos": {}}
+    assert stats0["plane"] == "nvlink", stats0
+
+    def T(np_arr):
+        return torch.from_numpy(np_arr.view(np.uint8).copy()).cuda()
+
+    tdt = {_lib.FLOAT32: torch.float32, _lib.BFLOAT16: torch.bfloat16, _lib.FLOAT16: torch.float16, _lib.FLOAT64: torch.float64,
+           _lib.INT32: torch.int32, _lib.INT64: torch.int64, _lib.INT8: torch.int8, _lib.UINT8: torch.uint8}
+    algos = ["ll", "oneshot", "twoshot", "auto"] + (["nvls"] if res["nvls"] else [])
+    sym_cap = 8 << 20
+    sym = comm.empty(sym_cap, torch.uint8)
+    for algo in algos:
+        for dtype, op, count in [(_lib.FLOAT32, _lib.SUM, 2048), (_lib.FLOAT32, _lib.SUM, 100003), (_lib.BFLOAT16, _lib.SUM, 65536 + 8),
+                                 (_lib.BFLOAT16, _lib.AVG, 1 << 20), (_lib.FLOAT32, _lib.MAX, 5000), (_lib.INT32, _lib.SUM, 4097),
+                                 (_lib.FLOAT16, _lib.SUM, 12345), (_lib.FLOAT64, _lib.PROD, 999), (_lib.INT8, _lib.MIN, 333)]:
+            esz = _lib.DTYPE_SIZES[dtype]
+            if algo == "ll" and count * esz > 64 * 1024:
+                continue
+            nvls_ok = dtype in (_lib.FLOAT32, _lib.BFLOAT16, _lib.FLOAT16) and op in (_lib.SUM, _lib.AVG)
+            ins = _np_inputs(dtype, count, n, op)
+            want = O.oracle_allreduce(ins, dtype, op)
+            for where in ("plain", "symmetric"):
+                if where == "plain":
+                    buf = T(ins[rank])
+                    out = torch.zeros_like(buf)
+                else:
+                    buf = sym[:count * esz]
+                    buf.copy_(T(ins[rank]))
+                    out = buf
+                rc = mn.lib().mncclAllReduceEx(buf.data_ptr(), dtype, out.data_ptr(), dtype, dtype, count, op, 1.0,
+                                               {"auto": 0, "ll": 1, "oneshot": 2, "twoshot": 3, "nvls": 4}[algo], comm.handle,
+                                               torch.cuda.current_stream().cuda_stream)
+                assert rc == 0, f"{algo} {O.DTYPE_NAMES[dtype]} {O.OP_NAMES[op]} {count} {where}: rc {rc}"
+                torch.cuda.synchronize()
+                got = out.cpu().numpy().view(O.NP_DTYPES[dtype])
+                if algo in ("nvls", "auto") and nvls_ok and res["nvls"]:
+                    # the switch defines the summation order: tolerance instead of bits
+                    err = float(np.abs(O.to_float64(got, dtype) - O.to_float64(want, dtype)).max())
+                    assert err <= O.tolerance(dtype, n), f"{algo} {O.DTYPE_NAMES[dtype]} {count} {where}: err {err}"
+                else:
+                    assert _bits_equal(got, want), f"{algo} {O.DTYPE_NAMES[dtype]} {O.OP_NAMES[op]} {count} {where}: mismatch"
+                res["cases"] += 1
+                comm.barrier()
+    # NVLS on exactly representable data is bit-exact whatever the order
+    if res["nvls"]:
+        count = 1 << 18
+        x = torch.full((count,), float(rank + 1), device="cuda")
+        s = comm.empty(count, torch.float32)
+        s.copy_(x)
+        comm.all_reduce(s, "sum", algo="nvls")
+        torch.cuda.synchronize()
+        assert torch.all(s == float(n * (n + 1) // 2)).item()
+        comm.free(s)
+    # fused cast + scale
+    count = 300001
+    ins = _np_inputs(_lib.FLOAT32, count, n, _lib.SUM)
+    want = O.oracle_allreduce(ins, _lib.FLOAT32, _lib.SUM, wire_dtype=_lib.BFLOAT16, out_dtype=_lib.FLOAT32, scale=0.5)
+    src = torch.from_numpy(ins[rank]).cuda()
+    dst = torch.zeros(count, device="cuda")
+    comm.all_reduce(src, "sum", out=dst, scale=0.5, wire_dtype=torch.bfloat16, algo="twoshot")
+    torch.cuda.synchronize()
+    assert np.array_equal(dst.cpu().numpy(), want), "fused fp32->bf16->fp32 mismatch"
+    # reduce-scatter / all-gather
+    per = 50003
+    ins = _np_inputs(_lib.FLOAT32, per * n, n, _lib.SUM)
+    want = O.oracle_allreduce(ins, _lib.FLOAT32, _lib.SUM)
+    src = torch.from_numpy(ins[rank]).cuda()
+    rs = torch.zeros(per, device="cuda")
+    comm.reduce_scatter(src, rs)
+    torch.cuda.synchronize()
+    assert np.array_equal(rs.cpu().numpy(), want[rank * per:(rank + 1) * per]), "reduce_scatter mismatch"
+    ag = torch.zeros(per * n, device="cuda")
+    comm.all_gather(rs, ag)
+    torch.cuda.synchronize()
+    assert np.array_equal(ag.cpu().numpy(), want), "all_gather mismatch"
+    # pinned host buffers, as the reference's programs use
+    hx = torch.from_numpy(_np_inputs(_lib.FLOAT32, 1 << 20, n, _lib.SUM)[rank]).pin_memory()
+    hy = torch.zeros(1 << 20).pin_memory()
+    rc = mn.lib().mncclAllReduce(hx.data_ptr(), hy.data_ptr(), 1 << 20, _lib.FLOAT32, _lib.SUM, comm.handle, None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    want = O.oracle_allreduce(_np_inputs(_lib.FLOAT32, 1 << 20, n, _lib.SUM), _lib.FLOAT32, _lib.SUM)
+    if res["nvls"]:
+        assert float(np.abs(hy.numpy() - want).max()) <= 1e-5 * n
+    else:
+        assert np.array_equal(hy.numpy(), want), "pinned host buffers mismatch"
+    # CUDA graph: capture 50 AllReduces of 64 KB bf16, replay 20 times
+    g_in = comm.empty(32768, torch.bfloat16)
+    ones = torch.ones(32768, dtype=torch.bfloat16, device="cuda")
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        g_in.copy_(ones)
+        comm.all_reduce(g_in, "avg")
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=s):
+            for _ in range(50):
+                comm.all_reduce(g_in, "avg")
+    torch.cuda.current_stream().wait_stream(s)
+    for _ in range(20):
+        g.replay()
+    torch.cuda.synchronize()
+    assert torch.all(g_in == 1.0).item(), "graph replay changed the average of ones"
+    assert comm.async_error() == 0
+    res["stats"] = comm.stats()
+    res["algo_8k"] = comm.query_algo(8192)
+    res["algo_1m"] = comm.query_algo(1 << 20)
+    res["algo_256m"] = comm.query_algo(256 << 20, registered=True)
+    del g
+    comm.free(g_in)
+    comm.free(sym)
+    comm.destroy()
+    return res
+
+
+def gpu_stall(rank, n, kw):
+    """1000 AllReduces of 64 KB bf16 in CUDA graphs; one rank stops launching at iteration
+    `stall_at` (a host-made stall).  Every rank must see an error within the bound."""
+    import torch
+
+    import mini_nccl_b200 as mn
+
+    torch.cuda.set_device(rank % torch.cuda.device_count())
+    init_rank = -1 if kw.get("hera") else rank
+    comm = mn.Communicator(n, init_rank, "127.0.0.1")
+    rank = comm.rank
+    buf = comm.empty(32768, torch.bfloat16)
+    buf.fill_(1.0)
+    per_graph = 10
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        comm.all_reduce(buf, "avg")
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=s):
+            for _ in range(per_graph):
+                comm.all_reduce(buf, "avg")
+    torch.cuda.synchronize()
+    comm.barrier()
+    stall_at, victim = kw["stall_at"], kw["victim"]
+    t_fail, it_fail = None, None
+    t0 = time.time()
+    for it in range(0, kw["iters"], per_graph):
+        if rank == victim and it == stall_at:
+            # the stalled rank simply stops launching; it polls the error state instead
+            while comm.async_error() == 0 and time.time() - t0 < 60:
+                time.sleep(0.01)
+        if comm.async_error() not in (0, 7):
+            t_fail, it_fail = time.time(), it
+            break
+        with torch.cuda.stream(s):
+            g.replay()
+        if it % 100 == 0:
+            s.synchronize()
+    if t_fail is None:
+        s.synchronize()
+        if comm.async_error() not in (0, 7):
+            t_fail, it_fail = time.time(), kw["iters"]
+    torch.cuda.synchronize()  # every kernel has returned: nothing is left spinning
+    t_sync = time.time()
+    err = comm.async_error()
+    rc = 0
+    try:
+        comm.all_reduce(buf, "avg")
+    except mn.MiniNcclError as e:
+        rc = e.code
+    stats = comm.stats()
+    comm.destroy()
+    return {"rank": rank, "async": err, "rc_after": rc, "it_fail": it_fail, "sync_seconds": t_sync - t0, "stats": stats}
+
+
+FUNCS = {f.__name__: f for f in (cpu_ring, cpu_ring_fault, gpu_battery, gpu_stall)}
+
+if __name__ == "__main__":
+    fn, rank, n, kw = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), json.loads(sys.argv[4])
+    out = FUNCS[fn](rank, n, kw)
+    print("RESULT " + json.dumps(out))
+    sys.stdout.flush()

@@ -1,0 +1,71 @@
+"""The NVLink data plane with one process per GPU (needs >= 2 GPUs).
+
+`gpu_battery` checks every algorithm (LL, one-shot, two-shot, NVLS when the box
+offers multicast, auto) on ordinary and on symmetric buffers against the host
+oracle, the fused cast, ReduceScatter / AllGather, pinned host buffers and CUDA
+graph capture + replay.  `gpu_stall` is the bounded-failure scenario: a rank stops
+launching (a stall made on the host, between steps); the peers' kernels wait, the
+watchdog sets the shared abort word after the configured bound, every kernel
+returns, and every rank reports an error.  NVLS is off in the stall tests: a rank
+that leaves while its memory is bound to a multicast object can fault its peers.
+"""
+import pytest
+
+from mini_nccl_b200 import _lib
+from tests.mp_workers import run_ranks
+
+
+def _ngpus():
+    import torch
+
+    return torch.cuda.device_count()
+
+
+@pytest.mark.multigpu(2)
+def test_battery_two_ranks(free_port):
+    res = run_ranks("gpu_battery", 2, {}, {"MINI_NCCL_BOOTSTRAP_PORT": free_port}, timeout=600)
+    for r in res:
+        assert r["cases"] > 40 and r["plane"] == "nvlink"
+        assert r["algo_8k"] == "ll" and r["algo_1m"] == "oneshot"
+        assert r["stats"]["progress"]["status"] == 0
+
+
+@pytest.mark.multigpu(2)
+def test_battery_ipc_provider_without_nvls(free_port):
+    # The fallback provider: cudaMalloc + CUDA IPC handles, no multicast.
+    env = {"MINI_NCCL_BOOTSTRAP_PORT": free_port, "MINI_NCCL_SYMM": "ipc"}
+    res = run_ranks("gpu_battery", 2, {}, env, timeout=600)
+    for r in res:
+        assert r["provider"] == "ipc" and not r["nvls"]
+
+
+@pytest.mark.multigpu(4)
+def test_battery_all_gpus(free_port):
+    n = min(_ngpus(), 8)
+    res = run_ranks("gpu_battery", n, {}, {"MINI_NCCL_BOOTSTRAP_PORT": free_port}, timeout=900)
+    assert len(res) == n
+
+
+@pytest.mark.multigpu(2)
+def test_hera_bootstrap_and_stall_bounded_failure(free_port, lib):
+    # rank = -1 for every process; 1000 AllReduces of 64 KB bf16 in CUDA graphs; the victim
+    # stops launching at iteration 500.  Bound: watchdog 1.5 s.
+    n = min(_ngpus(), 8)
+    hera_port = free_port
+    m = lib.mnccl_hera_master_start(n, hera_port, 0)
+    assert m
+    try:
+        env = {"MINI_NCCL_BOOTSTRAP_PORT": hera_port + 211, "MINI_NCCL_HERA_PORT": hera_port,
+               "MINI_NCCL_WATCHDOG_TIMEOUT_MS": 1500, "MINI_NCCL_NVLS_ENABLE": 0, "NCCL_NVLS_ENABLE": 0}
+        res = run_ranks("gpu_stall", n, {"hera": True, "iters": 1000, "stall_at": 500, "victim": 1}, env, timeout=300)
+    finally:
+        lib.mnccl_hera_master_stop(m)
+    assert sorted(r["rank"] for r in res) == list(range(n))
+    for r in res:
+        assert r["async"] == _lib.INTERNAL_ERROR, r
+        assert r["rc_after"] == _lib.INTERNAL_ERROR, "the communicator stays failed"
+        assert r["sync_seconds"] < 30, "every kernel returned within the bound"
+        assert not r["stats"]["nvls"]
+    tripped = sum(r["stats"]["watchdog"]["trips"] + r["stats"]["watchdog"]["device_failures"] for r in res)
+    assert tripped >= 1, "at least one watchdog saw the hang"
+    assert any("TIMEOUT DETECTED" in r["_stderr"] or "reported status" in r["_stderr"] for r in res)
