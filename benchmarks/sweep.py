@@ -90,8 +90,9 @@ def run_sweep(comm, world, rank, max_bytes=1 << 30, min_bytes=8 << 10, quick=Fal
                         row[key + "_sym_err"] = str(e)[:80]
                 p = plain[:n]
                 p.copy_(init[:n] if n <= init.numel() else init.repeat((n + init.numel() - 1) // init.numel())[:n])
+                p_out = p if world > 1 else torch.empty_like(p)  # one rank: out of place, so that a kernel runs
                 try:
-                    ms = _time_loop(lambda: comm.all_reduce(p, "sum", scale=scale, algo=algo), iters, warm, world)
+                    ms = _time_loop(lambda: comm.all_reduce(p, "sum", out=p_out, scale=scale, algo=algo), iters, warm, world)
                     row[key + "_us"] = round(ms * 1e3, 2)
                     row[key + "_busbw"] = round(bus_bandwidth_gbs(nbytes, ms, world)[1], 2)
                     if algo == "auto":
@@ -122,6 +123,23 @@ def run_sweep(comm, world, rank, max_bytes=1 << 30, min_bytes=8 << 10, quick=Fal
                 ms = _time_loop(lambda: dist.all_reduce(q), iters, warm, world)
                 row["nccl_us"] = round(ms * 1e3, 2)
                 row["nccl_busbw"] = round(bus_bandwidth_gbs(nbytes, ms, world)[1], 2)
+                if graphs and nbytes <= (1 << 20):
+                    try:
+                        g = torch.cuda.CUDAGraph()
+                        s = torch.cuda.Stream()
+                        s.wait_stream(torch.cuda.current_stream())
+                        with torch.cuda.stream(s):
+                            dist.all_reduce(q)
+                            torch.cuda.synchronize()
+                            with torch.cuda.graph(g, stream=s):
+                                for _ in range(20):
+                                    dist.all_reduce(q)
+                        torch.cuda.current_stream().wait_stream(s)
+                        ms = _time_loop(lambda: g.replay(), max(3, iters // 10), 2, world) / 20
+                        row["nccl_graph_us"] = round(ms * 1e3, 2)
+                        del g
+                    except Exception as e:
+                        row["nccl_graph_err"] = str(e)[:80]
                 q.zero_()
             rows.append(row)
         del plain

@@ -150,7 +150,8 @@ Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
   if (p.copy_out) sv = std::min<uint64_t>(sv, caps.stage_bytes / (uint64_t(N) * out_vb));
   if (sv == 0) { p.reason = "staging buffer too small"; return p; }
   p.chunk_shard_vecs = sv;
-  const uint64_t tiles = ceil_div(std::min(sv, shard_vecs), 512 * 4);
+  p.spec.unroll = (algo == Algo::Nvls && in.mode == Mode::AllReduce && cfg.unroll == 8) ? 8 : 4;
+  const uint64_t tiles = ceil_div(std::min(sv, shard_vecs), 512 * uint64_t(p.spec.unroll));
   int cap = max_blocks ? max_blocks : (algo == Algo::Nvls ? 96 : 64);
   p.spec.nblocks = static_cast<int>(std::clamp<uint64_t>(tiles, 1, cap));
   p.valid = true;

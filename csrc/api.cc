@@ -197,6 +197,11 @@ MNCCL_EXPORT ncclResult_t mncclCommDeviceHandle(ncclComm_t comm, void* out, size
   return ncclSuccess;
 }
 
+MNCCL_EXPORT ncclResult_t mncclCommSetTuning(ncclComm_t comm, int max_blocks, int unroll) {
+  if (!comm || max_blocks < 0 || max_blocks > mnccl::kMaxBlocks || (unroll != 0 && unroll != 4 && unroll != 8)) return ncclInvalidArgument;
+  return firewall("SetTuning", ncclInternalError, [&] { unwrap(comm)->set_tuning(max_blocks, unroll); });
+}
+
 MNCCL_EXPORT unsigned mncclVersion(void) { return 100; }
 
 // ---- reference-compatible names -------------------------------------------

@@ -419,9 +419,6 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
   const size_t in_elems = mode == Mode::ReduceScatter ? count * size_ : count;
   const size_t out_elems = mode == Mode::AllGather ? count * size_ : count;
   const size_t in_bytes = in_elems * dtype_size(send_t), out_bytes = out_elems * dtype_size(recv_t);
-  if (classify(send, true) == MemKind::PlainHost || classify(recv, true) == MemKind::PlainHost)
-    fail(Result::InvalidArgument, "buffers must be device memory or pinned host memory on the GPU data plane");
-
   PlanInput pi;
   pi.mode = mode;
   pi.count = count;
@@ -440,6 +437,9 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
     pi.in_has_mc = in_seg && in_seg->mc;
     pi.out_has_mc = out_seg && out_seg->mc;
   }
+  // Kernels dereference these pointers: pageable host memory would fault.
+  if ((!in_seg && classify(send, true) == MemKind::PlainHost) || (!out_seg && send != recv && classify(recv, true) == MemKind::PlainHost))
+    fail(Result::InvalidArgument, "buffers must be device memory or pinned host memory on the GPU data plane");
   Plan plan = make_plan(pi, caps_, cfg_);
   if (!plan.valid) fail(Result::InvalidArgument, std::string("no kernel for this request: ") + plan.reason);
   if (!kernel_exists(plan.spec)) fail(Result::InvalidArgument, "no kernel for this type / operator combination");

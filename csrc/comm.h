@@ -62,6 +62,11 @@ class Comm {
   std::string stats_json();
   Algo query_algo(size_t bytes, DType t, RedOp op, bool registered);
   const CommDev& device_handle() const { return dev_; }
+  void set_tuning(int max_blocks, int unroll) {
+    std::lock_guard<std::mutex> lk(call_mu_);
+    cfg_.max_blocks = max_blocks;
+    cfg_.unroll = unroll;
+  }
 
  private:
   Comm() = default;

@@ -93,6 +93,7 @@ Config Config::from_getter(Getter get, void* ctx) {
   r.num("MINI_NCCL_NVLS_MIN_BYTES", c.nvls_min_bytes);
   r.num("MINI_NCCL_STAGING_BYTES", c.staging_bytes);
   r.num("MINI_NCCL_MAX_BLOCKS", c.max_blocks);
+  r.num("MINI_NCCL_UNROLL", c.unroll);
   r.boolean("MINI_NCCL_NUMA_BIND", c.numa_bind);
   r.num("MINI_NCCL_CUDA_DEVICE", c.cuda_device);
   r.boolean("MINI_NCCL_HERA_KEEPALIVE", c.hera_keepalive);

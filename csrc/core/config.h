@@ -37,6 +37,7 @@ struct Config {
   size_t nvls_min_bytes = 0;          // MINI_NCCL_NVLS_MIN_BYTES    (0 = built-in table)
   size_t staging_bytes = 64u << 20;   // MINI_NCCL_STAGING_BYTES (per direction, per rank)
   int max_blocks = 0;                 // MINI_NCCL_MAX_BLOCKS (0 = built-in)
+  int unroll = 0;                     // MINI_NCCL_UNROLL (NVLS vectors in flight per thread: 4 or 8; 0 = built-in)
   bool numa_bind = true;              // MINI_NCCL_NUMA_BIND (verbs path only, calling thread)
   int cuda_device = -1;               // MINI_NCCL_CUDA_DEVICE (-1 = current device)
   bool hera_keepalive = false;        // MINI_NCCL_HERA_KEEPALIVE (heartbeat + global abort)

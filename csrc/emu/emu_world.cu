@@ -154,8 +154,9 @@ MNCCL_EXPORT int mncclEmuSetTimeoutNs(void* world, uint64_t ns) {
   return 0;
 }
 
-// A deaf rank behaves as if it were alone: it neither signals nor waits, so
-// its peers' bounded waits run out.  Host-made failure for tests.
+// A deaf rank takes no part in the collective (its kernel sees zero ranks and
+// zero elements): it neither signals nor waits, so its peers' bounded waits
+// run out.  Host-made failure for tests.
 MNCCL_EXPORT int mncclEmuSetDeaf(void* world, int rank, int on) {
   auto* w = static_cast<EmuWorld*>(world);
   if (!w || rank < 0 || rank >= w->n) return 4;
@@ -229,7 +230,7 @@ MNCCL_EXPORT int mncclEmuCollective(void* world, int mode, const void* const* se
     a.copy_in = plan.copy_in;
     a.copy_out = plan.copy_out;
     if (w->deaf[r]) {  // takes no part: moves nothing, signals nobody
-      kp.comm.nranks = 1;
+      kp.comm.nranks = 0;
       a.count = 0;
       a.shard_elems = 0;
     }

@@ -32,8 +32,6 @@
 namespace mnccl {
 namespace dev {
 
-constexpr int kUnroll = 4;
-
 enum CollMode : int { kAllReduce = 0, kReduceScatter = 1, kAllGather = 2 };
 
 // -------------------------------------------------------------------- N == 1
@@ -185,7 +183,7 @@ __device__ __forceinline__ void oneshot_body(const KParams& P, int blk, int nblk
 // `v0` of the shard.  Shard j covers elements [j*E, (j+1)*E) of the logical
 // message; its vector i sits at element j*E + i*VW of user buffers and at
 // vector (j*SV + i) of a staging buffer (SV = capacity per shard).
-template <typename InT, typename WireT, typename OutT, int OP, bool NVLS, int MODE>
+template <typename InT, typename WireT, typename OutT, int OP, bool NVLS, int MODE, int kUnroll = 4>
 __device__ __forceinline__ void twoshot_body(const KParams& P, int blk, int nblk, BlockCtl& ctl) {
   const CommDev& c = P.comm;
   const CollArgs& a = P.args;

@@ -26,6 +26,7 @@ struct LaunchSpec {
   RedOp op = RedOp::Sum;  // Avg is launched as Sum; the factor travels in CollArgs
   int nblocks = 1;
   int nthreads = 512;
+  int unroll = 4;  // vectors in flight per thread in the NVLS kernels (4 or 8)
 };
 
 // True when a kernel exists for this combination of algorithm, mode, types

@@ -151,6 +151,10 @@ ncclResult_t mncclCommQueryAlgo(ncclComm_t comm, size_t bytes, ncclDataType_t da
  * `len` bytes; returns the full size in *needed. */
 ncclResult_t mncclCommDeviceHandle(ncclComm_t comm, void* out, size_t len, size_t* needed);
 
+/* Launch tuning for the calls that follow (0 keeps the built-in value).  Every
+ * rank must use the same values.  Meant for benchmarking sweeps. */
+ncclResult_t mncclCommSetTuning(ncclComm_t comm, int max_blocks, int unroll);
+
 unsigned mncclVersion(void);
 
 #ifdef __cplusplus

@@ -75,6 +75,7 @@ def lib() -> C.CDLL:
     sig("mncclCommStats", i32, vp, C.c_char_p, sz)
     sig("mncclCommQueryAlgo", i32, vp, sz, i32, i32, i32, P(i32))
     sig("mncclCommDeviceHandle", i32, vp, vp, sz, P(sz))
+    sig("mncclCommSetTuning", i32, vp, i32, i32)
     sig("mncclVersion", C.c_uint)
     # reference-compatible names (exported for C users; typed here for the ABI tests)
     sig("ncclGetErrorString", C.c_char_p, i32)

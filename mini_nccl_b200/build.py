@@ -49,10 +49,13 @@ CUDA_SOURCES = [
 OPTIONAL_CUDA = ["kernels/gemm_sm100.cu", "kernels/gemm_fused.cu", "kernels/noalloc.cu"]
 OPTIONAL_HOST = ["net/verbs_transport.cc"]
 
+_HERA_SRCS = ["csrc/bootstrap/hera.cc", "csrc/bootstrap/socket.cc", "csrc/core/log.cc"]
 PROGRAMS = {
-    # name -> (sources relative to ROOT, needs_cuda_runtime)
-    "hera_master": (["apps/hera_master.cpp"], False),
-    "hera_test": (["apps/hera_test.cpp"], False),
+    # name -> (sources relative to ROOT, links libmini_nccl + CUDA runtime)
+    # The Hera programs are self-contained (no CUDA, no shared library), like the
+    # reference's header-only control plane.
+    "hera_master": (["apps/hera_master.cpp", *_HERA_SRCS], False),
+    "hera_test": (["apps/hera_test.cpp", *_HERA_SRCS], False),
     "app": (["apps/app.cpp"], True),
     "perf_test": (["apps/perf_test.cpp"], True),
 }
@@ -148,9 +151,10 @@ def build(verbose: bool = False, programs: bool = True, jobs: int | None = None)
             if out.exists() and out.stat().st_mtime >= newest:
                 continue
             cmd = ["g++", "-std=c++17", "-O2", "-mavx2", "-pthread", *_common_includes(), *map(str, paths),
-                   "-o", str(out), "-L", str(LIBDIR), "-lmini_nccl", f"-Wl,-rpath,$ORIGIN/../lib"]
+                   "-o", str(out)]
             if needs_cuda:
-                cmd += ["-L", str(CUDA_HOME / "lib64"), "-lcudart_static", "-ldl", "-lrt"]
+                cmd += ["-L", str(LIBDIR), "-lmini_nccl", "-Wl,-rpath,$ORIGIN/../lib",
+                        "-L", str(CUDA_HOME / "lib64"), "-lcudart_static", "-ldl", "-lrt"]
             if verbose:
                 print(" ".join(cmd), flush=True)
             r = subprocess.run(cmd, capture_output=True, text=True)

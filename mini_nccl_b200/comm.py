@@ -23,7 +23,13 @@ except Exception:  # pragma: no cover
     torch = None
 
 
+_DTYPE_TABLE: dict = {}
+
+
 def _torch_dtype_code(dt) -> int:
+    code = _DTYPE_TABLE.get(dt)
+    if code is not None:
+        return code
     table = {
         torch.int8: _lib.INT8, torch.uint8: _lib.UINT8, torch.int32: _lib.INT32, torch.int64: _lib.INT64,
         torch.float16: _lib.FLOAT16, torch.float32: _lib.FLOAT32, torch.float64: _lib.FLOAT64,
@@ -34,6 +40,7 @@ def _torch_dtype_code(dt) -> int:
             table[getattr(torch, name)] = code
     if dt not in table:
         raise TypeError(f"unsupported dtype {dt}")
+    _DTYPE_TABLE.update(table)
     return table[dt]
 
 
@@ -177,6 +184,10 @@ class Communicator:
         buf = C.create_string_buffer(4096)
         check(lib().mncclCommStats(self._h, buf, len(buf)), "mncclCommStats")
         return json.loads(buf.value.decode())
+
+    def set_tuning(self, max_blocks: int = 0, unroll: int = 0) -> None:
+        """Grid cap and NVLS unroll for the calls that follow (0 = built-in).  Same values on every rank."""
+        check(lib().mncclCommSetTuning(self._h, max_blocks, unroll), "mncclCommSetTuning")
 
     def query_algo(self, nbytes: int, dtype=None, op: str = "sum", registered: bool = False) -> str:
         a = C.c_int()

@@ -1,0 +1,147 @@
+"""Host components one by one: config knobs, SPSC queue, request pool, registration cache,
+NIC choice, NUMA parsing, descriptor passing, watchdog logic, the launch planner."""
+import ctypes as C
+import json
+
+import pytest
+
+from mini_nccl_b200 import _lib
+
+
+def cfg(lib, env):
+    out = C.create_string_buffer(2048)
+    rc = lib.mnccl_test_config(env.encode(), out, 2048)
+    return rc, (json.loads(out.value.decode()) if rc == 0 else None)
+
+
+def test_config_defaults_and_banner(lib):
+    rc, c = cfg(lib, "")
+    assert rc == 0
+    assert c["slice_size"] == 131072 and c["window_size"] == 64 and c["signal_batch"] == 16
+    assert c["watchdog_timeout_ms"] == 10000 and c["bootstrap_port"] == 8888 and c["hera_port"] == 9999
+    assert c["banner"] == "Loaded: SLICE_SIZE=131072 B, WINDOW=64, BATCH=16"
+
+
+def test_config_clamps(lib):
+    rc, c = cfg(lib, "MINI_NCCL_SLICE_SIZE=0;MINI_NCCL_WINDOW_SIZE=-3;MINI_NCCL_SIGNAL_BATCH=0")
+    assert rc == 0
+    assert c["slice_size"] == 1024   # 0 -> 1024
+    assert c["window_size"] == 1     # <= 0 -> 1
+    assert c["signal_batch"] == 1    # 0 would be a modulo by zero in the slice loop
+
+
+def test_config_values_and_suffixes(lib):
+    rc, c = cfg(lib, "MINI_NCCL_SLICE_SIZE=64K;MINI_NCCL_WINDOW_SIZE=8;MINI_NCCL_SIGNAL_BATCH=4;MINI_NCCL_NET_DEVICE=mlx5_1;"
+                     "MINI_NCCL_WATCHDOG_TIMEOUT_MS=250;MINI_NCCL_ALGO=nvls;MINI_NCCL_NVLS_ENABLE=0")
+    assert rc == 0
+    assert c["slice_size"] == 65536 and c["window_size"] == 8 and c["signal_batch"] == 4
+    assert c["net_device"] == "mlx5_1" and c["watchdog_timeout_ms"] == 250 and c["algo"] == "nvls" and c["nvls_enable"] is False
+
+
+@pytest.mark.parametrize("bad", ["MINI_NCCL_SLICE_SIZE=abc", "MINI_NCCL_WINDOW_SIZE=1.5x", "MINI_NCCL_NVLS_ENABLE=maybe",
+                                 "MINI_NCCL_BOOTSTRAP_PORT=70000", "MINI_NCCL_SLICE_SIZE=-5"])
+def test_config_malformed_is_invalid_argument(lib, bad):
+    rc, _ = cfg(lib, bad)
+    assert rc == 100 + _lib.INVALID_ARGUMENT
+
+
+def test_spsc_queue(lib):
+    assert lib.mnccl_test_spsc(1, 1000) == 0
+    assert lib.mnccl_test_spsc(7, 200000) == 0
+    assert lib.mnccl_test_spsc(4096, 500000) == 0
+
+
+def test_request_pool(lib):
+    assert lib.mnccl_test_request_pool(4096) == 0
+    assert lib.mnccl_test_request_pool(3) == 0
+
+
+def test_registration_cache(lib):
+    assert lib.mnccl_test_reg_cache() == 0
+
+
+def test_nic_selection_policy(lib):
+    idx = C.c_int(-1)
+    assert lib.mnccl_test_select_nic(b"mlx5_0,rxe0,mlx5_1", b"", C.byref(idx)) == 0 and idx.value == 1   # rxe0 first
+    assert lib.mnccl_test_select_nic(b"eth_rdma,mlx5_0,mlx5_1", b"", C.byref(idx)) == 0 and idx.value == 1  # then mlx5
+    assert lib.mnccl_test_select_nic(b"hfi1_0,bnxt_re0", b"", C.byref(idx)) == 0 and idx.value == 0        # else first
+    assert lib.mnccl_test_select_nic(b"mlx5_0,rxe0,mlx5_1", b"mlx5_1", C.byref(idx)) == 0 and idx.value == 2  # override
+    assert lib.mnccl_test_select_nic(b"mlx5_0,rxe0", b"nope0", C.byref(idx)) == 100 + _lib.SYSTEM_ERROR     # no match: error
+    assert lib.mnccl_test_select_nic(b"", b"", C.byref(idx)) == 100 + _lib.SYSTEM_ERROR                     # no devices
+
+
+def test_cpu_list_parser(lib):
+    out = (C.c_int * 64)()
+    n = lib.mnccl_test_parse_cpu_list(b"0-3,8,10-11\n", out, 64)
+    assert list(out[:n]) == [0, 1, 2, 3, 8, 10, 11]
+    assert lib.mnccl_test_parse_cpu_list(b"", out, 64) == 0
+    n = lib.mnccl_test_parse_cpu_list(b"5", out, 64)
+    assert list(out[:n]) == [5]
+    n = lib.mnccl_test_parse_cpu_list(b"x,2-1,7", out, 64)
+    assert list(out[:n]) == [7]
+
+
+def test_numa_lookup_on_fake_sysfs(lib, tmp_path):
+    dev = tmp_path / "class" / "infiniband" / "mlx5_0" / "device"
+    dev.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    node = tmp_path / "devices" / "system" / "node" / "node1"
+    node.mkdir(parents=True)
+    (node / "cpulist").write_text("16-31,48-63\n")
+    nd, ncpu = C.c_int(), C.c_int()
+    lib.mnccl_test_numa(str(tmp_path).encode(), b"mlx5_0", C.byref(nd), C.byref(ncpu))
+    assert nd.value == 1 and ncpu.value == 32
+    lib.mnccl_test_numa(str(tmp_path).encode(), b"absent0", C.byref(nd), C.byref(ncpu))
+    assert nd.value == -1 and ncpu.value == 0
+    (dev / "numa_node").write_text("-1\n")
+    lib.mnccl_test_numa(str(tmp_path).encode(), b"mlx5_0", C.byref(nd), C.byref(ncpu))
+    assert nd.value == -1 and ncpu.value == 0
+
+
+def test_descriptor_passing(lib):
+    import os
+
+    assert lib.mnccl_test_fdpass(f"t{os.getpid()}".encode()) == 0
+
+
+def test_watchdog_logic(lib):
+    assert lib.mnccl_test_watchdog(0, 100) == 0   # finishes in time: no abort
+    assert lib.mnccl_test_watchdog(1, 100) == 1   # stuck past the bound: abort word set, one trip
+    assert lib.mnccl_test_watchdog(2, 100) == 1   # a kernel reported a failed wait: abort at once
+
+
+def plan(lib, n, count, dtype=_lib.FLOAT32, op=_lib.SUM, mode=0, in_sym=0, out_sym=0, nvls=0, forced=0, stage=0, wire=None, out=None):
+    algo, nb, cin, cout = C.c_int(), C.c_int(), C.c_int(), C.c_int()
+    se, cv = C.c_uint64(), C.c_uint64()
+    rc = lib.mnccl_test_plan(n, mode, count, dtype, dtype if wire is None else wire, dtype if out is None else out, op, in_sym,
+                             out_sym, nvls, forced, stage, C.byref(algo), C.byref(nb), C.byref(se), C.byref(cv), C.byref(cin), C.byref(cout))
+    if rc:
+        return None
+    return dict(algo=_lib.ALGO_NAMES[algo.value], nblocks=nb.value, shard=se.value, chunk=cv.value, copy_in=cin.value, copy_out=cout.value)
+
+
+def test_planner_picks_by_size(lib):
+    assert plan(lib, 8, 2048)["algo"] == "ll"                      # 8 KB
+    assert plan(lib, 8, 16384)["algo"] == "oneshot"                # 64 KB
+    assert plan(lib, 8, 1 << 20)["algo"] == "twoshot"              # 4 MB, no multicast
+    assert plan(lib, 8, 1 << 20, nvls=1)["algo"] == "nvls"
+    assert plan(lib, 8, 1 << 20, nvls=1, op=_lib.MAX)["algo"] == "twoshot"      # the switch only adds
+    assert plan(lib, 8, 1 << 20, nvls=1, dtype=_lib.INT32)["algo"] == "twoshot"
+    assert plan(lib, 1, 12345)["algo"] == "local"
+    assert plan(lib, 8, 1 << 26, forced=_lib.ALGO_LL)["algo"] == "twoshot"      # forced but impossible: degrade
+
+
+def test_planner_geometry(lib):
+    p = plan(lib, 8, 1000003)
+    assert p["shard"] % 4 == 0 and p["shard"] * 8 >= 1000003 and (p["shard"] - 4) * 8 < 1000003 + 32
+    assert p["copy_in"] == 1 and p["copy_out"] == 1
+    z = plan(lib, 8, 1 << 24, in_sym=1, out_sym=1, nvls=1)
+    assert z["algo"] == "nvls" and z["copy_in"] == 0 and z["copy_out"] == 0 and z["chunk"] * 4 == z["shard"]
+    s = plan(lib, 4, 1 << 26, stage=1 << 20)           # 256 MB through 1 MB of staging: many passes
+    assert s["chunk"] == (1 << 20) // (4 * 16)
+    assert 1 <= s["nblocks"] <= 512
+    assert plan(lib, 4, 1000, dtype=_lib.FLOAT32, wire=_lib.INT32) is None   # no such cast
+    rs = plan(lib, 4, 1001, mode=1)
+    assert rs["algo"] == "twoshot" and rs["shard"] == 1001 and rs["copy_out"] == 0
+    ag = plan(lib, 4, 1001, mode=2)
+    assert ag["algo"] == "twoshot" and ag["copy_in"] == 0 and ag["copy_out"] == 1
