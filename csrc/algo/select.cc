@@ -35,16 +35,19 @@ Algo parse_algo(const std::string& s) {
 
 Thresholds thresholds_for(int nranks, const Config& cfg) {
   Thresholds t;
-  // Crossovers from the device-timed sweep (fp32 / bf16 sum).
+  // Crossovers from the device-timed sweep on 8xB200 (benchmarks/tune.py, fp32
+  // sum, symmetric buffers).  N=2: one-shot moves no more bytes than two-shot
+  // and wins up to 4 MB.  N=4: one-shot wins up to 512 KB.  N=8: LL and
+  // one-shot tie up to 64 KB, NVLS wins from 256 KB on.
   if (nranks <= 2) {
     t.ll_max = 64u << 10;
-    t.oneshot_max = 2u << 20;
+    t.oneshot_max = 4u << 20;
   } else if (nranks <= 4) {
-    t.ll_max = 32u << 10;
+    t.ll_max = 64u << 10;
     t.oneshot_max = 512u << 10;
   } else {
-    t.ll_max = 16u << 10;
-    t.oneshot_max = 128u << 10;
+    t.ll_max = 64u << 10;
+    t.oneshot_max = 192u << 10;
   }
   t.nvls_min = t.oneshot_max + 1;
   if (cfg.ll_max_bytes) t.ll_max = cfg.ll_max_bytes;
@@ -96,7 +99,9 @@ Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
   const bool nvls_types = nvls_type_ok(in.in, in.wire, in.out, in.op);
   // NVLS needs multicast views of whatever it touches: staging always has one
   // when caps.nvls; symmetric user buffers only if their segment does.
-  const bool nvls_usable = caps.nvls && nvls_types && in.mode != Mode::AllGather &&
+  // With two ranks the switch cannot win: both phases move S bytes per link
+  // direction one after the other, while P2P moves S/2 each way at once.
+  const bool nvls_usable = caps.nvls && N > 2 && nvls_types && in.mode != Mode::AllGather &&
                            (!in.in_symmetric || in.in_has_mc) && (!in.out_symmetric || in.out_has_mc);
   if (in.mode != Mode::AllReduce) {
     if (algo != Algo::TwoShot && algo != Algo::Nvls) algo = nvls_usable && in.mode == Mode::ReduceScatter && wire_bytes >= th.nvls_min ? Algo::Nvls : Algo::TwoShot;
@@ -152,7 +157,9 @@ Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
   p.chunk_shard_vecs = sv;
   p.spec.unroll = (algo == Algo::Nvls && in.mode == Mode::AllReduce && cfg.unroll == 8) ? 8 : 4;
   const uint64_t tiles = ceil_div(std::min(sv, shard_vecs), 512 * uint64_t(p.spec.unroll));
-  int cap = max_blocks ? max_blocks : (algo == Algo::Nvls ? 96 : 64);
+  // Measured: the switch path peaks with ~32 CTAs (more only add contention),
+  // the P2P path wants ~96.
+  int cap = max_blocks ? max_blocks : (algo == Algo::Nvls ? 32 : 96);
   p.spec.nblocks = static_cast<int>(std::clamp<uint64_t>(tiles, 1, cap));
   p.valid = true;
   return p;

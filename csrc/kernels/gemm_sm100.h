@@ -1,0 +1,105 @@
+// Shared definitions of the sm_100a bf16 GEMM (tile shape, arguments, the
+// epilogue interface) used by gemm_sm100.cu and the fused kernels.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+namespace mnccl {
+namespace gemm {
+
+constexpr int kBM = 128;          // tile rows  (UMMA M; TMEM lanes)
+constexpr int kBN = 256;          // tile cols  (UMMA N; TMEM columns per accumulator)
+constexpr int kBK = 64;           // k-block: 64 bf16 = one 128-byte swizzle row
+constexpr int kUmmaK = 16;        // K of one tcgen05.mma for 16-bit types
+constexpr int kStages = 4;
+constexpr int kTileABytes = kBM * kBK * 2;           // 16 KB
+constexpr int kTileBBytes = kBN * kBK * 2;           // 32 KB
+constexpr int kStageBytes = kTileABytes + kTileBBytes;
+constexpr int kTmemCols = 512;    // two fp32 accumulators of 256 columns
+constexpr int kEpilogueWarps = 4;
+constexpr int kThreads = 32 * (2 + kEpilogueWarps);
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct GemmArgs {
+  int M, N, K;
+  void* c;                 // output (StoreEpilogue)
+  int ldc;
+  int group_m;             // tile rasterisation: group of m-tiles that share B tiles in L2
+  uint32_t* err;           // device error word (first failed wait)
+  uint64_t wait_budget_ns;
+  // all-gather -> GEMM: chunk c of A's rows is valid once a_ready[c] >= a_epoch
+  const uint32_t* a_ready;
+  uint32_t a_epoch;
+  int rows_per_chunk;
+  int m_tile_rotate;       // first m-tile to compute (so that local rows go first)
+};
+
+// Tile index -> (tm, tn).  m-tiles are visited in groups of `group_m` so that a
+// wave of CTAs reuses the same B tiles from L2; `m_tile_rotate` rotates the
+// m order (fused all-gather: rows that are already local first).
+__device__ __forceinline__ void tile_coords(const GemmArgs& g, int t, int tiles_m, int tiles_n, int* tm, int* tn) {
+  const int gm = g.group_m > 0 ? g.group_m : 1;
+  const int per_group = gm * tiles_n;
+  const int group = t / per_group;
+  const int first_m = group * gm;
+  const int rows_in_group = (tiles_m - first_m) < gm ? (tiles_m - first_m) : gm;
+  const int in_group = t % per_group;
+  int m = first_m + in_group % rows_in_group;
+  *tn = in_group / rows_in_group;
+  m += g.m_tile_rotate;
+  if (m >= tiles_m) m -= tiles_m;
+  *tm = m;
+}
+
+// Plain epilogue: convert and store the accumulator tile to C.
+template <bool OUT_F32>
+struct StoreEpilogue {
+  // Thread holds row `row`, columns [col, col+32) as fp32 bit patterns.
+  __device__ __forceinline__ void store(const GemmArgs& g, int row, int col, const uint32_t (&r)[32], int, int) const {
+    if (row >= g.M || col >= g.N) return;
+    if constexpr (OUT_F32) {
+      float* dst = static_cast<float*>(g.c) + static_cast<size_t>(row) * g.ldc + col;
+      if (col + 32 <= g.N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          reinterpret_cast<uint4*>(dst)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+      } else {
+        for (int j = 0; j < 32 && col + j < g.N; ++j) dst[j] = __uint_as_float(r[j]);
+      }
+    } else {
+      __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.c) + static_cast<size_t>(row) * g.ldc + col;
+      if (col + 32 <= g.N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 v;
+          uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * k]), __uint_as_float(r[8 * j + 2 * k + 1]));
+            w[k] = *reinterpret_cast<uint32_t*>(&p);
+          }
+          reinterpret_cast<uint4*>(dst)[j] = v;
+        }
+      } else {
+        for (int j = 0; j < 32 && col + j < g.N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+      }
+    }
+  }
+  __device__ __forceinline__ void tile_done(const GemmArgs&, int, int, int, int) const {}
+};
+
+bool make_tensor_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_elems,
+                          uint32_t box_rows, uint32_t box_cols, std::string* why);
+uint32_t* error_word();
+int sm_count();
+
+template <typename Epilogue>
+cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const Epilogue& epi, int grid,
+                   cudaStream_t stream);
+
+}  // namespace gemm
+}  // namespace mnccl

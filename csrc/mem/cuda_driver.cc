@@ -52,6 +52,7 @@ const CudaDriver* CudaDriver::get() {
                        resolve("cuMulticastUnbind", &d->MulticastUnbind) &
                        resolve("cuMulticastGetGranularity", &d->MulticastGetGranularity);
     resolve("cuStreamWriteValue32", &d->StreamWriteValue32);
+    resolve("cuTensorMapEncodeTiled", &d->TensorMapEncodeTiled);
     drv = d;
   });
   return drv;

@@ -84,6 +84,10 @@ def lib() -> C.CDLL:
     sig("ncclCommUserRank", i32, vp, P(i32))
     sig("ncclCommCount", i32, vp, P(i32))
     sig("ncclAllReduce", i32, vp, vp, sz, i32, i32, vp, vp)
+    # sm_100a GEMM (optional translation unit)
+    if hasattr(L, "mncclGemmBf16"):
+        sig("mncclGemmBf16", i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp)
+        sig("mncclGemmStatus", i32, P(u32))
     # emulation + probes
     sig("mncclEmuCreate", i32, i32, sz, P(vp))
     sig("mncclEmuDestroy", i32, vp)

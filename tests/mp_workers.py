@@ -222,11 +222,21 @@ def gpu_battery(rank, n, kw):
     rs = torch.zeros(per, device="cuda")
     comm.reduce_scatter(src, rs)
     torch.cuda.synchronize()
-    assert np.array_equal(rs.cpu().numpy(), want[rank * per:(rank + 1) * per]), "reduce_scatter mismatch"
+    got_rs = rs.cpu().numpy()
+    if res["nvls"]:  # large ReduceScatter may go through the switch, which picks the summation order
+        assert float(np.abs(got_rs - want[rank * per:(rank + 1) * per]).max()) <= 1e-5 * n, "reduce_scatter mismatch"
+    else:
+        assert np.array_equal(got_rs, want[rank * per:(rank + 1) * per]), "reduce_scatter mismatch"
     ag = torch.zeros(per * n, device="cuda")
     comm.all_gather(rs, ag)
     torch.cuda.synchronize()
-    assert np.array_equal(ag.cpu().numpy(), want), "all_gather mismatch"
+    # AllGather moves bits: every rank must hold exactly what each owner computed
+    assert np.array_equal(ag.cpu().numpy()[rank * per:(rank + 1) * per], got_rs), "all_gather: own shard changed"
+    assert float(np.abs(ag.cpu().numpy() - want).max()) <= 1e-5 * n, "all_gather mismatch"
+    chk = ag.clone()
+    comm.all_reduce(chk, "max")
+    torch.cuda.synchronize()
+    assert torch.equal(chk, ag), "all_gather results differ between ranks"
     # pinned host buffers, as the reference's programs use
     hx = torch.from_numpy(_np_inputs(_lib.FLOAT32, 1 << 20, n, _lib.SUM)[rank]).pin_memory()
     hy = torch.zeros(1 << 20).pin_memory()
@@ -298,7 +308,7 @@ def gpu_stall(rank, n, kw):
     for it in range(0, kw["iters"], per_graph):
         if rank == victim and it == stall_at:
             # the stalled rank simply stops launching; it polls the error state instead
-            while comm.async_error() == 0 and time.time() - t0 < 60:
+            while comm.async_error() in (0, 7) and time.time() - t0 < 60:  # 7: its own earlier kernels still run
                 time.sleep(0.01)
         if comm.async_error() not in (0, 7):
             t_fail, it_fail = time.time(), it

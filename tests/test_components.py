@@ -122,7 +122,8 @@ def plan(lib, n, count, dtype=_lib.FLOAT32, op=_lib.SUM, mode=0, in_sym=0, out_s
 
 def test_planner_picks_by_size(lib):
     assert plan(lib, 8, 2048)["algo"] == "ll"                      # 8 KB
-    assert plan(lib, 8, 16384)["algo"] == "oneshot"                # 64 KB
+    assert plan(lib, 8, 16384)["algo"] == "ll"                     # 64 KB
+    assert plan(lib, 8, 40000)["algo"] == "oneshot"                # 160 KB
     assert plan(lib, 8, 1 << 20)["algo"] == "twoshot"              # 4 MB, no multicast
     assert plan(lib, 8, 1 << 20, nvls=1)["algo"] == "nvls"
     assert plan(lib, 8, 1 << 20, nvls=1, op=_lib.MAX)["algo"] == "twoshot"      # the switch only adds

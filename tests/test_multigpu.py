@@ -26,7 +26,7 @@ def test_battery_two_ranks(free_port):
     res = run_ranks("gpu_battery", 2, {}, {"MINI_NCCL_BOOTSTRAP_PORT": free_port}, timeout=600)
     for r in res:
         assert r["cases"] > 40 and r["plane"] == "nvlink"
-        assert r["algo_8k"] == "ll" and r["algo_1m"] == "oneshot"
+        assert r["algo_8k"] == "ll" and r["algo_1m"] == "oneshot" and r["algo_256m"] == "twoshot"
         assert r["stats"]["progress"]["status"] == 0
 
 
