@@ -1,0 +1,381 @@
+// Tensor-parallel fusions of the sm_100a GEMM with its collective, each ONE kernel:
+//
+//   GEMM -> reduce-scatter.  Every rank multiplies its K-slice: P_r = A_r * B_r^T, [M, N];
+//   the result row block i belongs to rank i.  The epilogue converts each 128 x 256
+//   accumulator tile to bf16 and stores it straight into the OWNER's staging slot for
+//   this source rank over NVLink (plain peer stores), then raises a per-tile flag
+//   there (st.release.sys).  Tiles are visited owner by owner starting with the next
+//   rank, the local rows last, so the transfers overlap the remaining math.  When a
+//   CTA has no tiles left, its epilogue warps turn to the rows this rank owns: they
+//   wait (bounded) for the flags of all ranks, add the partial tiles in rank order in
+//   fp32 and write the bf16 result.  Deterministic; nothing is reduced in the switch.
+//
+//   all-gather -> GEMM.  X is sharded by rows; every rank needs all of X times its own
+//   weight slice.  The local shard already sits at its place inside the gather buffer.
+//   A few CTAs of the grid do no math: after a cross-rank barrier they push the local
+//   shard into every peer's gather buffer (peer stores), chunk of 128 rows by chunk,
+//   and count each finished chunk into the peer's ready counters (red.release.sys).
+//   The GEMM CTAs start on the local rows at once; their TMA producer waits (bounded)
+//   for a chunk's counter before loading tiles of those rows -- always from local
+//   memory, never from a peer.
+//
+// Call counters (epochs) are device-resident, flags and counters only grow, staging
+// alternates between two halves: no clearing between calls and a captured launch can
+// be replayed.  The reference has neither tensor parallelism nor a GEMM; these kernels
+// are what "AllReduce fused with the adjacent compute" means for this library.
+#include <cstdio>
+
+#include "kernels/gemm_kernel.cuh"
+
+namespace mnccl {
+namespace gemm {
+
+constexpr int kMaxTpRanks = 8;
+
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void epilogue_warps_sync() {
+  // the four epilogue warps (128 threads) on named barrier 1
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+// Bounded wait for *p >= target (wrap-safe) with system-scope acquire.
+__device__ __forceinline__ bool wait_flag_sys(const uint32_t* p, uint32_t target, volatile uint32_t* abort_flag,
+                                              uint64_t budget_ns) {
+  if (static_cast<int32_t>(ld_acquire_sys_u32(p) - target) >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (static_cast<int32_t>(ld_acquire_sys_u32(p) - target) >= 0) return true;
+    if ((it & 255u) == 0u) {
+      if (*abort_flag != 0u) return false;
+      if (globaltimer_ns() - t0 > budget_ns) {
+        *abort_flag = 3u;
+        return false;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ GEMM -> reduce-scatter
+
+struct RsEpilogue {
+  int rank, nranks;
+  int rows_per_rank;                 // M / nranks, a multiple of 128
+  char* stage[kMaxTpRanks];          // every rank's staging: [2][nranks][rows_per_rank][N] bf16
+  uint32_t* flags[kMaxTpRanks];      // every rank's flags:   [nranks][tiles_m_local * tiles_n]
+  __nv_bfloat16* out;                // [rows_per_rank, N] on this rank
+  int ldo;
+
+  __device__ __forceinline__ size_t slot_elems(const GemmArgs& g) const {
+    return static_cast<size_t>(rows_per_rank) * g.N;
+  }
+
+  // Peer stores want long contiguous runs: a warp's 32 rows x 32 columns piece would be 32
+  // separate 16-byte writes per instruction.  So two pieces (64 columns = 128 bytes per row) are
+  // first laid out row-major in shared memory, then written with 8 lanes per row: every store
+  // instruction of the warp covers four full 128-byte lines of the owner's memory.
+  __device__ __forceinline__ void store(const GemmArgs& g, uint32_t epoch, int row, int col, const uint32_t (&r)[32],
+                                        int chunk, uint8_t* warp_smem, int lane) const {
+    uint8_t* mine = warp_smem + lane * kEpiRowBytes + (chunk & 1) * 64;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 v;
+      uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * k]), __uint_as_float(r[8 * j + 2 * k + 1]));
+        w[k] = *reinterpret_cast<uint32_t*>(&p);
+      }
+      *reinterpret_cast<uint4*>(mine + j * 16) = v;
+    }
+    if ((chunk & 1) == 0) return;
+    __syncwarp();
+    const int row_base = row - lane;        // first row of this warp's 32
+    const int col_base = col - 32;          // first of the 64 columns
+    const int owner = row_base / rows_per_rank;   // a 128-row tile never straddles owners
+    __nv_bfloat16* slot = reinterpret_cast<__nv_bfloat16*>(stage[owner]) +
+                          (static_cast<size_t>(epoch & 1u) * nranks + rank) * slot_elems(g);
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int rr = it * 4 + (lane >> 3);  // 4 rows per instruction
+      const int seg = lane & 7;             // 8 x 16 bytes per row
+      const int grow = row_base + rr;
+      const int gcol = col_base + seg * 8;
+      if (grow < g.M && gcol < g.N) {
+        const uint4 v = *reinterpret_cast<const uint4*>(warp_smem + rr * kEpiRowBytes + seg * 16);
+        *reinterpret_cast<uint4*>(slot + static_cast<size_t>(grow - owner * rows_per_rank) * g.N + gcol) = v;
+      }
+    }
+    __syncwarp();  // the scratch is reused by the next pair of pieces
+  }
+
+  // All four epilogue warps call this after the last store of a tile.
+  __device__ __forceinline__ void tile_done(const GemmArgs& g, uint32_t epoch, int tm, int tn, int q, int lane) const {
+    epilogue_warps_sync();  // every store of the tile precedes the flag
+    if (q == 0 && lane == 0) {
+      const int tiles_n = (g.N + kBN - 1) / kBN;
+      const int tiles_m_local = rows_per_rank / kBM;
+      const int owner = (tm * kBM) / rows_per_rank;
+      const int ltm = tm - owner * tiles_m_local;
+      st_release_sys_u32(flags[owner] + (static_cast<size_t>(rank) * tiles_m_local + ltm) * tiles_n + tn, epoch);
+    }
+  }
+
+  // Reduction of the rows this rank owns, by the epilogue warps of every CTA.
+  __device__ __forceinline__ void after_tiles(const GemmArgs& g, uint32_t epoch, int cta, int n_cta, int q, int lane,
+                                              volatile uint32_t* abort_flag) const {
+    const int tiles_n = (g.N + kBN - 1) / kBN;
+    const int tiles_m_local = rows_per_rank / kBM;
+    const int items = tiles_m_local * tiles_n * 4;  // a tile quarter: 32 rows x 256 columns
+    const int tid = ((q + 2) & 3) * 32 + lane;      // 0..127 over warps 2,3,4,5 in launch order
+    const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(stage[rank]) +
+                                static_cast<size_t>(epoch & 1u) * nranks * slot_elems(g);
+    for (int item = cta; item < items; item += n_cta) {
+      const int tile = item >> 2, quarter = item & 3;
+      const int ltm = tile / tiles_n, tn = tile - ltm * tiles_n;
+      if (tid < nranks) {
+        wait_flag_sys(flags[rank] + (static_cast<size_t>(tid) * tiles_m_local + ltm) * tiles_n + tn, epoch, abort_flag,
+                      g.wait_budget_ns);
+      }
+      epilogue_warps_sync();
+      if (*abort_flag != 0u) return;
+      const int row0 = ltm * kBM + quarter * 32;
+      const int col0 = tn * kBN;
+      const int ncols = min(kBN, g.N - col0);
+      const int vec_per_row = ncols / 8;  // 8 bf16 = 16 bytes (N is a multiple of 8)
+      for (int v = tid; v < 32 * vec_per_row; v += 128) {
+        const int rr = row0 + v / vec_per_row;
+        const int cc = col0 + (v % vec_per_row) * 8;
+        if (rr >= rows_per_rank) continue;
+        float acc[8];
+        for (int src = 0; src < nranks; ++src) {
+          const uint4 x = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(src) * slot_elems(g) +
+                                                          static_cast<size_t>(rr) * g.N + cc);
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 f = __bfloat1622float2(h[k]);
+            acc[2 * k] = src == 0 ? f.x : acc[2 * k] + f.x;
+            acc[2 * k + 1] = src == 0 ? f.y : acc[2 * k + 1] + f.y;
+          }
+        }
+        uint4 y;
+        __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&y);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+        *reinterpret_cast<uint4*>(out + static_cast<size_t>(rr) * ldo + cc) = y;
+      }
+      epilogue_warps_sync();
+    }
+  }
+
+  __device__ __forceinline__ void comm_cta(const GemmArgs&, uint32_t, int, int, volatile uint32_t*) const {}
+};
+
+// ------------------------------------------------------------------ all-gather -> GEMM
+
+struct AgEpilogue {
+  int rank, nranks;
+  int rows_per_rank;                 // M / nranks, a multiple of 128
+  int lda;                           // row stride of the gather buffers, elements
+  char* xg[kMaxTpRanks];             // every rank's gather buffer [M, K] bf16
+  uint32_t* ready[kMaxTpRanks];      // every rank's chunk counters [M / 128]
+  uint32_t* bar[kMaxTpRanks];        // every rank's barrier words [n_comm][nranks]
+  StoreEpilogue<false> plain;
+
+  __device__ __forceinline__ void store(const GemmArgs& g, uint32_t epoch, int row, int col, const uint32_t (&r)[32],
+                                        int chunk, uint8_t* warp_smem, int lane) const {
+    plain.store(g, epoch, row, col, r, chunk, warp_smem, lane);
+  }
+  __device__ __forceinline__ void tile_done(const GemmArgs&, uint32_t, int, int, int, int) const {}
+  __device__ __forceinline__ void after_tiles(const GemmArgs&, uint32_t, int, int, int, int, volatile uint32_t*) const {}
+
+  // A communication CTA: barrier with the same CTA of every peer (everyone has left
+  // the previous use of the gather buffers), then push the local shard to every peer.
+  __device__ __forceinline__ void comm_cta(const GemmArgs& g, uint32_t epoch, int cta, int n_comm,
+                                           volatile uint32_t* abort_flag) const {
+    const int t = threadIdx.x;
+    if (t < nranks && t != rank) {
+      st_release_sys_u32(bar[t] + cta * nranks + rank, epoch);
+      wait_flag_sys(bar[rank] + cta * nranks + t, epoch, abort_flag, g.wait_budget_ns);
+    }
+    __syncthreads();
+    if (*abort_flag != 0u) return;
+    const int chunks = rows_per_rank / kBM;
+    const int vec_per_row = g.K / 8;                       // 16-byte vectors in a row
+    const int vecs = kBM * vec_per_row;                    // per chunk
+    const int stride = n_comm * static_cast<int>(blockDim.x);
+    for (int s = 1; s < nranks; ++s) {
+      const int peer = (rank - s + nranks) % nranks;       // the peer that wants this shard soonest first
+      for (int c = 0; c < chunks; ++c) {
+        const int row0 = rank * rows_per_rank + c * kBM;
+        for (int v0 = cta * static_cast<int>(blockDim.x) + t; v0 < vecs; v0 += 4 * stride) {
+          uint4 x[4];
+          size_t off[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int v = v0 + u * stride;
+            off[u] = (static_cast<size_t>(row0 + v / vec_per_row) * lda + static_cast<size_t>(v % vec_per_row) * 8) * 2;
+            if (v < vecs) x[u] = *reinterpret_cast<const uint4*>(xg[rank] + off[u]);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int v = v0 + u * stride;
+            if (v < vecs) *reinterpret_cast<uint4*>(xg[peer] + off[u]) = x[u];
+          }
+        }
+        __syncthreads();  // every store of this CTA's part of the chunk precedes the count
+        if (t == 0) red_release_sys_add(ready[peer] + (row0 / kBM), 1u);
+      }
+    }
+  }
+};
+
+namespace {
+
+bool check_common(int M, int N, int K, int rank, int nranks, const char* who) {
+  if (M <= 0 || N <= 0 || K <= 0 || nranks < 1 || nranks > kMaxTpRanks || rank < 0 || rank >= nranks) {
+    fprintf(stderr, "[Mini-NCCL] %s: bad shape or rank\n", who);
+    return false;
+  }
+  if (M % nranks != 0 || (M / nranks) % kBM != 0 || N % 8 != 0 || K % 8 != 0) {
+    fprintf(stderr, "[Mini-NCCL] %s: needs M / nranks to be a multiple of %d and N, K multiples of 8\n", who, kBM);
+    return false;
+  }
+  return true;
+}
+
+}  // namespace
+}  // namespace gemm
+}  // namespace mnccl
+
+using namespace mnccl;
+using namespace mnccl::gemm;
+
+extern "C" {
+#define MNCCL_EXPORT __attribute__((visibility("default")))
+
+// Bytes / words a caller must provide (in symmetric memory, zero-filled once).
+MNCCL_EXPORT size_t mncclGemmRsStageBytes(int M, int N, int /*nranks*/) {
+  return size_t(2) * M * N * 2;  // two halves x nranks slots x (M / nranks) rows x N bf16
+}
+MNCCL_EXPORT size_t mncclGemmRsFlagWords(int M, int N, int nranks) {
+  return size_t(nranks) * (M / nranks / kBM) * ((N + kBN - 1) / kBN);
+}
+MNCCL_EXPORT size_t mncclAgGemmReadyWords(int M) { return size_t(M) / kBM; }
+MNCCL_EXPORT size_t mncclAgGemmBarWords(int nranks, int n_comm) { return size_t(nranks) * n_comm; }
+
+// out[M/nranks, N] (rows of this rank) = sum over ranks of A_r[M, K] * B_r[N, K]^T, bf16.
+// stage_peers / flag_peers: the staging / flag buffers of EVERY rank as mapped here
+// (Communicator.peer_pointers); state: two zero-initialised device words of this rank.
+MNCCL_EXPORT int mncclGemmReduceScatterBf16(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb,
+                                            int ldo, int rank, int nranks, void* const* stage_peers,
+                                            void* const* flag_peers, uint32_t* state, cudaStream_t stream) {
+  if (!A || !B || !out || !stage_peers || !flag_peers || !state) return -1;
+  if (!check_common(M, N, K, rank, nranks, "GEMM->reduce-scatter")) return -2;
+  if (lda == 0) lda = K;
+  if (ldb == 0) ldb = K;
+  if (ldo == 0) ldo = N;
+  CUtensorMap ta, tb;
+  std::string why;
+  if (!make_tensor_map_bf16(&ta, A, M, K, lda, kBM, kBK, &why) || !make_tensor_map_bf16(&tb, B, N, K, ldb, kBN, kBK, &why)) {
+    fprintf(stderr, "[Mini-NCCL] GEMM->reduce-scatter: %s\n", why.c_str());
+    return -3;
+  }
+  RsEpilogue epi{};
+  epi.rank = rank;
+  epi.nranks = nranks;
+  epi.rows_per_rank = M / nranks;
+  epi.out = static_cast<__nv_bfloat16*>(out);
+  epi.ldo = ldo;
+  for (int r = 0; r < nranks; ++r) {
+    epi.stage[r] = static_cast<char*>(stage_peers[r]);
+    epi.flags[r] = static_cast<uint32_t*>(flag_peers[r]);
+  }
+  GemmArgs g{};
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.err = error_word();
+  g.wait_budget_ns = 2000000000ull;
+  const int tiles_m_local = epi.rows_per_rank / kBM;
+  g.group_m = tiles_m_local;
+  g.m_tile_rotate = ((rank + 1) % nranks) * tiles_m_local;  // next rank's rows first, own rows last
+  g.epoch_ptr = state;
+  g.ticket_ptr = state + 1;
+  const int tiles = (M / kBM) * ((N + kBN - 1) / kBN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  cudaError_t e = launch(ta, tb, g, epi, grid, stream);
+  return e == cudaSuccess ? 0 : static_cast<int>(e) + 1000;
+}
+
+// C[M, N] = X[M, K] * B[N, K]^T where X is the row-wise concatenation of every rank's shard.
+// xg_peers: the gather buffer [M, K] of EVERY rank as mapped here; this rank's shard must
+// already be at rows [rank * M/nranks, ...) of its own buffer.  ready_peers / bar_peers: counter
+// and barrier words of every rank; state: two zero-initialised device words of this rank.
+// n_comm_ctas CTAs of the grid move data instead of computing (0 = default).
+MNCCL_EXPORT int mncclAllGatherGemmBf16(void* const* xg_peers, const void* B, void* C, int M, int N, int K, int lda, int ldb,
+                                        int ldc, int rank, int nranks, void* const* ready_peers, void* const* bar_peers,
+                                        uint32_t* state, int n_comm_ctas, cudaStream_t stream) {
+  if (!xg_peers || !B || !C || !state) return -1;
+  if (!check_common(M, N, K, rank, nranks, "all-gather->GEMM")) return -2;
+  if (nranks > 1 && (!ready_peers || !bar_peers)) return -1;
+  if (lda == 0) lda = K;
+  if (ldb == 0) ldb = K;
+  if (ldc == 0) ldc = N;
+  CUtensorMap ta, tb;
+  std::string why;
+  // The A operand is this rank's own gather buffer: TMA only ever reads local memory.
+  if (!make_tensor_map_bf16(&ta, xg_peers[rank], M, K, lda, kBM, kBK, &why) ||
+      !make_tensor_map_bf16(&tb, B, N, K, ldb, kBN, kBK, &why)) {
+    fprintf(stderr, "[Mini-NCCL] all-gather->GEMM: %s\n", why.c_str());
+    return -3;
+  }
+  const int sms = sm_count();
+  int n_comm = nranks > 1 ? (n_comm_ctas > 0 ? n_comm_ctas : 16) : 0;
+  if (n_comm > sms / 2) n_comm = sms / 2;
+  AgEpilogue epi{};
+  epi.rank = rank;
+  epi.nranks = nranks;
+  epi.rows_per_rank = M / nranks;
+  epi.lda = lda;
+  for (int r = 0; r < nranks; ++r) {
+    epi.xg[r] = static_cast<char*>(xg_peers[r]);
+    epi.ready[r] = nranks > 1 ? static_cast<uint32_t*>(ready_peers[r]) : nullptr;
+    epi.bar[r] = nranks > 1 ? static_cast<uint32_t*>(bar_peers[r]) : nullptr;
+  }
+  GemmArgs g{};
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.c = C;
+  g.ldc = ldc;
+  g.err = error_word();
+  g.wait_budget_ns = 2000000000ull;
+  const int tiles_m_local = epi.rows_per_rank / kBM;
+  g.group_m = tiles_m_local;
+  g.m_tile_rotate = rank * tiles_m_local;  // local rows first, then the shards in arrival order
+  g.epoch_ptr = state;
+  g.ticket_ptr = state + 1;
+  if (nranks > 1) {
+    g.a_ready = epi.ready[rank];
+    g.a_ready_mult = static_cast<uint32_t>(n_comm);
+    g.rows_per_chunk = kBM;
+    g.a_local_first = rank * tiles_m_local;
+    g.a_local_count = tiles_m_local;
+  }
+  const int tiles = (M / kBM) * ((N + kBN - 1) / kBN);
+  int n_gemm = sms - n_comm;
+  if (tiles < n_gemm) n_gemm = tiles;
+  g.n_gemm_ctas = n_gemm;
+  // Every CTA must be resident at once (communication CTAs wait for peers while GEMM CTAs
+  // wait for data): the grid never exceeds one CTA per SM.
+  cudaError_t e = launch(ta, tb, g, epi, n_gemm + n_comm, stream);
+  return e == cudaSuccess ? 0 : static_cast<int>(e) + 1000;
+}
+
+}  // extern "C"

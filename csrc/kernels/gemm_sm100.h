@@ -22,7 +22,10 @@ constexpr int kStageBytes = kTileABytes + kTileBBytes;
 constexpr int kTmemCols = 512;    // two fp32 accumulators of 256 columns
 constexpr int kEpilogueWarps = 4;
 constexpr int kThreads = 32 * (2 + kEpilogueWarps);
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kCtlBytes = 256;            // barriers and control words
+constexpr int kEpiRowBytes = 128 + 16;    // 64 bf16 of one row + padding against bank conflicts
+constexpr int kEpiWarpBytes = 32 * kEpiRowBytes;  // per epilogue warp: 32 rows x 64 columns, for transposed stores
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + kCtlBytes + kEpilogueWarps * kEpiWarpBytes;
 
 struct GemmArgs {
   int M, N, K;
@@ -31,11 +34,20 @@ struct GemmArgs {
   int group_m;             // tile rasterisation: group of m-tiles that share B tiles in L2
   uint32_t* err;           // device error word (first failed wait)
   uint64_t wait_budget_ns;
-  // all-gather -> GEMM: chunk c of A's rows is valid once a_ready[c] >= a_epoch
+  // all-gather -> GEMM: chunk c of A's rows is valid once a_ready[c] >= epoch * a_ready_mult;
+  // chunks [a_local_first, a_local_first + a_local_count) are local and need no wait.
   const uint32_t* a_ready;
-  uint32_t a_epoch;
+  uint32_t a_ready_mult;
   int rows_per_chunk;
+  int a_local_first, a_local_count;
   int m_tile_rotate;       // first m-tile to compute (so that local rows go first)
+  // fused kernels: CTAs [0, n_gemm_ctas) compute tiles, the rest run the epilogue's
+  // comm_cta(); 0 means every CTA computes.
+  int n_gemm_ctas;
+  // Device-resident call counter of the fused op: the kernel works with epoch = *epoch_ptr + 1
+  // and its last CTA (ticket) stores it back, so a captured launch replays correctly.
+  uint32_t* epoch_ptr;
+  uint32_t* ticket_ptr;
 };
 
 // Tile index -> (tm, tn).  m-tiles are visited in groups of `group_m` so that a
@@ -59,7 +71,9 @@ __device__ __forceinline__ void tile_coords(const GemmArgs& g, int t, int tiles_
 template <bool OUT_F32>
 struct StoreEpilogue {
   // Thread holds row `row`, columns [col, col+32) as fp32 bit patterns.
-  __device__ __forceinline__ void store(const GemmArgs& g, int row, int col, const uint32_t (&r)[32], int, int) const {
+  // `chunk` counts the 32-column pieces of the tile; `warp_smem` is kEpiWarpBytes of scratch.
+  __device__ __forceinline__ void store(const GemmArgs& g, uint32_t /*epoch*/, int row, int col, const uint32_t (&r)[32],
+                                        int /*chunk*/, uint8_t* /*warp_smem*/, int /*lane*/) const {
     if (row >= g.M || col >= g.N) return;
     if constexpr (OUT_F32) {
       float* dst = static_cast<float*>(g.c) + static_cast<size_t>(row) * g.ldc + col;
@@ -89,17 +103,15 @@ struct StoreEpilogue {
       }
     }
   }
-  __device__ __forceinline__ void tile_done(const GemmArgs&, int, int, int, int) const {}
+  __device__ __forceinline__ void tile_done(const GemmArgs&, uint32_t, int, int, int, int) const {}
+  __device__ __forceinline__ void after_tiles(const GemmArgs&, uint32_t, int, int, int, int, volatile uint32_t*) const {}
+  __device__ __forceinline__ void comm_cta(const GemmArgs&, uint32_t, int, int, volatile uint32_t*) const {}
 };
 
 bool make_tensor_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_elems,
                           uint32_t box_rows, uint32_t box_cols, std::string* why);
 uint32_t* error_word();
 int sm_count();
-
-template <typename Epilogue>
-cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const Epilogue& epi, int grid,
-                   cudaStream_t stream);
 
 }  // namespace gemm
 }  // namespace mnccl

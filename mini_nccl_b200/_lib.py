@@ -88,6 +88,13 @@ def lib() -> C.CDLL:
     if hasattr(L, "mncclGemmBf16"):
         sig("mncclGemmBf16", i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp)
         sig("mncclGemmStatus", i32, P(u32))
+    if hasattr(L, "mncclGemmReduceScatterBf16"):
+        sig("mncclGemmRsStageBytes", sz, i32, i32, i32)
+        sig("mncclGemmRsFlagWords", sz, i32, i32, i32)
+        sig("mncclAgGemmReadyWords", sz, i32)
+        sig("mncclAgGemmBarWords", sz, i32, i32)
+        sig("mncclGemmReduceScatterBf16", i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, P(vp), P(vp), vp, vp)
+        sig("mncclAllGatherGemmBf16", i32, P(vp), vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, P(vp), P(vp), vp, i32, vp)
     # emulation + probes
     sig("mncclEmuCreate", i32, i32, sz, P(vp))
     sig("mncclEmuDestroy", i32, vp)

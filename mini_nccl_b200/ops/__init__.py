@@ -1,3 +1,4 @@
 """Hand-written sm_100a compute kernels: the tcgen05 / TMEM / TMA bf16 GEMM and its fusions
 with the collectives (GEMM -> reduce-scatter, all-gather -> GEMM)."""
 from .gemm import gemm_bf16, gemm_status  # noqa: F401
+from .fused import AllGatherGemm, GemmReduceScatter  # noqa: F401,E402

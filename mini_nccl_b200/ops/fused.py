@@ -1,0 +1,124 @@
+"""The two tensor-parallel fusions as Python objects that own their workspaces.
+
+``GemmReduceScatter``: ``out[M/R, N] = reduce_scatter(A_r[M, K_r] @ B_r[N, K_r].T)`` -- one kernel;
+tiles are pushed to their owner over NVLink while the remaining tiles are computed.
+``AllGatherGemm``: ``C[M, N_r] = all_gather(X_r)[M, K] @ B_r[N_r, K].T`` -- one kernel; a few CTAs push
+the local shard to the peers while the others already compute on the local rows.
+
+Workspaces come from ``Communicator.empty`` (symmetric memory), so creating these objects is
+collective: every rank, same order, same shapes.  With one rank they run the same kernels locally.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+from .._lib import lib
+
+BM = 128
+
+
+def _native():
+    L = lib()
+    if not hasattr(L, "mncclGemmReduceScatterBf16"):
+        raise RuntimeError("libmini_nccl.so was built without the fused GEMM kernels (csrc/kernels/gemm_fused.cu)")
+    return L
+
+
+def _sym(comm, numel, dtype):
+    import torch
+
+    if comm.size > 1:
+        t = comm.empty(numel, dtype)
+    else:
+        t = torch.empty(numel, dtype=dtype, device="cuda")
+    t.zero_()
+    return t
+
+
+def _peers(comm, tensor):
+    if comm.size == 1:
+        return (C.c_void_p * 1)(tensor.data_ptr())
+    ptrs, _ = comm.peer_pointers(tensor)
+    return (C.c_void_p * comm.size)(*ptrs)
+
+
+class GemmReduceScatter:
+    def __init__(self, comm, M: int, N: int):
+        import torch
+
+        L = _native()
+        R = comm.size
+        if M % R or (M // R) % BM or N % 8:
+            raise ValueError("M / ranks must be a multiple of 128 and N a multiple of 8")
+        self.comm, self.M, self.N = comm, M, N
+        self.stage = _sym(comm, L.mncclGemmRsStageBytes(M, N, R), torch.uint8)
+        self.flags = _sym(comm, max(4, L.mncclGemmRsFlagWords(M, N, R)), torch.int32)
+        self.state = torch.zeros(4, dtype=torch.int32, device="cuda")
+        torch.cuda.synchronize()
+        if R > 1:
+            comm.barrier()
+        self._stage_peers = _peers(comm, self.stage)
+        self._flag_peers = _peers(comm, self.flags)
+
+    def __call__(self, a, b, out=None, stream=None):
+        """``a [M, K_r]``, ``b [N, K_r]`` bf16 -> ``out [M / ranks, N]`` bf16 (this rank's rows of the sum)."""
+        import torch
+
+        M, N = self.M, self.N
+        if tuple(a.shape)[0] != M or tuple(b.shape)[0] != N or a.shape[1] != b.shape[1]:
+            raise ValueError("shape mismatch")
+        if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or a.stride(1) != 1 or b.stride(1) != 1:
+            raise TypeError("bf16 operands with a unit inner stride")
+        if out is None:
+            out = torch.empty((M // self.comm.size, N), dtype=torch.bfloat16, device=a.device)
+        s = stream.cuda_stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        rc = _native().mncclGemmReduceScatterBf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, a.shape[1], a.stride(0),
+                                                  b.stride(0), out.stride(0), self.comm.rank, self.comm.size,
+                                                  self._stage_peers, self._flag_peers, self.state.data_ptr(), s)
+        if rc != 0:
+            raise RuntimeError(f"mncclGemmReduceScatterBf16 failed with code {rc}")
+        return out
+
+
+class AllGatherGemm:
+    def __init__(self, comm, M: int, K: int, n_comm_ctas: int = 16):
+        import torch
+
+        L = _native()
+        R = comm.size
+        if M % R or (M // R) % BM or K % 8:
+            raise ValueError("M / ranks must be a multiple of 128 and K a multiple of 8")
+        self.comm, self.M, self.K, self.n_comm = comm, M, K, n_comm_ctas
+        self.gather = _sym(comm, M * K, torch.bfloat16).view(M, K)   # X of every rank lands here
+        self.ready = _sym(comm, max(4, L.mncclAgGemmReadyWords(M)), torch.int32)
+        self.bar = _sym(comm, max(4, L.mncclAgGemmBarWords(R, max(n_comm_ctas, 1))), torch.int32)
+        self.state = torch.zeros(4, dtype=torch.int32, device="cuda")
+        torch.cuda.synchronize()
+        if R > 1:
+            comm.barrier()
+        self._xg = _peers(comm, self.gather)
+        self._ready = _peers(comm, self.ready)
+        self._bar = _peers(comm, self.bar)
+
+    @property
+    def local_shard(self):
+        """The rows of the gather buffer this rank fills before calling (write the input here)."""
+        r, per = self.comm.rank, self.M // self.comm.size
+        return self.gather[r * per:(r + 1) * per]
+
+    def __call__(self, b, out=None, stream=None):
+        """``b [N_r, K]`` bf16 -> ``out [M, N_r]`` bf16 = (all ranks' shards stacked) @ b.T."""
+        import torch
+
+        if b.dtype != torch.bfloat16 or b.shape[1] != self.K or b.stride(1) != 1:
+            raise TypeError("b must be bf16 [N, K] with a unit inner stride")
+        N = b.shape[0]
+        if out is None:
+            out = torch.empty((self.M, N), dtype=torch.bfloat16, device=b.device)
+        s = stream.cuda_stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        rc = _native().mncclAllGatherGemmBf16(self._xg, b.data_ptr(), out.data_ptr(), self.M, N, self.K, self.K, b.stride(0),
+                                              out.stride(0), self.comm.rank, self.comm.size, self._ready, self._bar,
+                                              self.state.data_ptr(), self.n_comm, s)
+        if rc != 0:
+            raise RuntimeError(f"mncclAllGatherGemmBf16 failed with code {rc}")
+        return out

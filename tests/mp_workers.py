@@ -334,7 +334,57 @@ def gpu_stall(rank, n, kw):
     return {"rank": rank, "async": err, "rc_after": rc, "it_fail": it_fail, "sync_seconds": t_sync - t0, "stats": stats}
 
 
-FUNCS = {f.__name__: f for f in (cpu_ring, cpu_ring_fault, gpu_battery, gpu_stall)}
+def gpu_tp(rank, n, kw):
+    """Fused tensor-parallel kernels across real GPUs against a PyTorch fp32 reference."""
+    import torch
+
+    import mini_nccl_b200 as mn
+    from mini_nccl_b200.ops import AllGatherGemm, GemmReduceScatter, gemm_status
+
+    torch.cuda.set_device(rank % torch.cuda.device_count())
+    comm = mn.Communicator(n, rank, "127.0.0.1")
+    M, N, K = kw.get("M", 1024), kw.get("N", 1024), kw.get("K", 512)
+    per = M // n
+    rs = GemmReduceScatter(comm, M, N)
+    ag = AllGatherGemm(comm, M, K, n_comm_ctas=kw.get("n_comm", 16))
+    worst = 0.0
+    for it in range(kw.get("iters", 4)):
+        # every rank can rebuild every rank's operands from the seeds
+        def operands(r):
+            g = torch.Generator(device="cuda").manual_seed(1000 * it + r)
+            a = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+            b = torch.randn(N, K, generator=g, device="cuda").to(torch.bfloat16)
+            x = torch.randn(per, K, generator=g, device="cuda").to(torch.bfloat16)
+            return a, b, x
+        mine = operands(rank)
+        # GEMM -> reduce-scatter: rows of this rank of sum_r A_r B_r^T
+        ref = torch.zeros(per, N, device="cuda")
+        for r in range(n):
+            a, b, _ = operands(r)
+            ref += a[rank * per:(rank + 1) * per].float() @ b.float().t()
+        out = rs(mine[0], mine[1])
+        torch.cuda.synchronize()
+        assert gemm_status() == 0, "a bounded wait ran out in GEMM->reduce-scatter"
+        err = (out.float() - ref).abs().max().item() / ref.abs().max().item()
+        assert err < 3e-2, f"gemm_rs it {it}: rel err {err}"
+        worst = max(worst, err)
+        # all-gather -> GEMM: stack of every rank's x times my b
+        xs = torch.cat([operands(r)[2] for r in range(n)])
+        ref2 = xs.float() @ mine[1].float().t()
+        ag.local_shard.copy_(mine[2])
+        c = ag(mine[1])
+        torch.cuda.synchronize()
+        assert gemm_status() == 0, "a bounded wait ran out in all-gather->GEMM"
+        assert torch.equal(ag.gather, xs), f"ag_gemm it {it}: gathered rows differ"
+        err2 = (c.float() - ref2).abs().max().item() / ref2.abs().max().item()
+        assert err2 < 2e-2, f"ag_gemm it {it}: rel err {err2}"
+        worst = max(worst, err2)
+    comm.barrier()
+    comm.destroy()
+    return {"rank": rank, "worst": worst}
+
+
+FUNCS = {f.__name__: f for f in (cpu_ring, cpu_ring_fault, gpu_battery, gpu_stall, gpu_tp)}
 
 if __name__ == "__main__":
     fn, rank, n, kw = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), json.loads(sys.argv[4])

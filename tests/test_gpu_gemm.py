@@ -44,3 +44,31 @@ def test_gemm_ragged_edges_and_strides():
 
 def test_gemm_many_more_tiles_than_sms():
     _check(8192, 4096, 512)
+
+
+def test_fused_kernels_single_rank():
+    # One rank: the same kernels run locally (push to the own staging slot, reduce one slot; no
+    # communication CTAs).  Checks the epilogue hooks, the epochs over repeated calls and the
+    # staging halves.
+    import mini_nccl_b200 as mn
+    from mini_nccl_b200.ops import AllGatherGemm, GemmReduceScatter, gemm_status
+
+    comm = mn.Communicator(1, 0)
+    try:
+        M, N, K = 512, 1024, 384
+        rs = GemmReduceScatter(comm, M, N)
+        ag = AllGatherGemm(comm, M, K)
+        for it in range(3):
+            g = torch.Generator(device="cuda").manual_seed(it)
+            a = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+            b = torch.randn(N, K, generator=g, device="cuda").to(torch.bfloat16)
+            ref = a.float() @ b.float().t()
+            out = rs(a, b)
+            assert gemm_status() == 0
+            assert (out.float() - ref).abs().max().item() / ref.abs().max().item() < 2e-2
+            ag.local_shard.copy_(a)
+            c = ag(b)
+            assert gemm_status() == 0
+            assert (c.float() - ref).abs().max().item() / ref.abs().max().item() < 2e-2
+    finally:
+        comm.destroy()

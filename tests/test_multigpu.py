@@ -69,3 +69,17 @@ def test_hera_bootstrap_and_stall_bounded_failure(free_port, lib):
     tripped = sum(r["stats"]["watchdog"]["trips"] + r["stats"]["watchdog"]["device_failures"] for r in res)
     assert tripped >= 1, "at least one watchdog saw the hang"
     assert any("TIMEOUT DETECTED" in r["_stderr"] or "reported status" in r["_stderr"] for r in res)
+
+
+@pytest.mark.multigpu(2)
+def test_fused_tensor_parallel_kernels(free_port):
+    n = 2
+    res = run_ranks("gpu_tp", n, {"M": 1024, "N": 1024, "K": 512}, {"MINI_NCCL_BOOTSTRAP_PORT": free_port}, timeout=300)
+    assert len(res) == n and all(r["worst"] < 3e-2 for r in res)
+
+
+@pytest.mark.multigpu(8)
+def test_fused_tensor_parallel_kernels_llama_shape(free_port):
+    # Llama-3-8B block at TP=8: 4096 tokens, hidden 4096, FFN 14336 / 8 = 1792 per rank
+    res = run_ranks("gpu_tp", 8, {"M": 4096, "N": 4096, "K": 1792, "iters": 2}, {"MINI_NCCL_BOOTSTRAP_PORT": free_port}, timeout=600)
+    assert len(res) == 8
