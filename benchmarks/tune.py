@@ -45,7 +45,7 @@ def main():
     ap.add_argument("--out", default="")
     ap.add_argument("--sizes", default="8192,65536,262144,1048576,4194304,16777216,67108864,268435456,1073741824")
     ap.add_argument("--dtype", default="fp32")
-    ap.add_argument("--blocks", default="32,64,96,148")
+    ap.add_argument("--blocks", default="16,24,32,64,96")
     ap.add_argument("--plain", action="store_true", help="also time ordinary (staged) buffers")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

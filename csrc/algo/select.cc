@@ -33,7 +33,7 @@ Algo parse_algo(const std::string& s) {
   return Algo::Auto;
 }
 
-Thresholds thresholds_for(int nranks, const Config& cfg) {
+Thresholds thresholds_for(int nranks, const Config& cfg, bool symmetric) {
   Thresholds t;
   // Crossovers from the device-timed sweep on 8xB200 (benchmarks/tune.py, fp32
   // sum, symmetric buffers).  N=2: one-shot moves no more bytes than two-shot
@@ -49,6 +49,10 @@ Thresholds thresholds_for(int nranks, const Config& cfg) {
     t.ll_max = 64u << 10;
     t.oneshot_max = 192u << 10;
   }
+  // Ordinary (not symmetric) buffers have to be staged by the two-phase kernels, which costs
+  // two extra passes over the data; one-shot reads the user buffer directly, so it stays ahead
+  // up to 2 MB.
+  if (!symmetric && nranks > 2) t.oneshot_max = 2u << 20;
   t.nvls_min = t.oneshot_max + 1;
   if (cfg.ll_max_bytes) t.ll_max = cfg.ll_max_bytes;
   if (cfg.oneshot_max_bytes) t.oneshot_max = cfg.oneshot_max_bytes;
@@ -57,13 +61,13 @@ Thresholds thresholds_for(int nranks, const Config& cfg) {
 }
 
 size_t default_ll_slot_bytes(int nranks, const Config& cfg) {
-  size_t payload = std::max<size_t>(thresholds_for(nranks, cfg).ll_max, 64u << 10);
+  size_t payload = std::max<size_t>(thresholds_for(nranks, cfg, true).ll_max, 64u << 10);
   return 2 * payload;
 }
 
 size_t default_inbox_slot_bytes(int nranks, const Config& cfg) {
-  size_t cap = nranks <= 2 ? (4u << 20) : nranks <= 4 ? (2u << 20) : (1u << 20);
-  return std::max<size_t>(cap, thresholds_for(nranks, cfg).oneshot_max);
+  size_t cap = nranks <= 2 ? (4u << 20) : (2u << 20);
+  return std::max<size_t>(cap, thresholds_for(nranks, cfg, false).oneshot_max);
 }
 
 Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
@@ -94,7 +98,7 @@ Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
 
   const uint64_t total_elems = in.mode == Mode::AllReduce ? in.count : in.count * uint64_t(N);
   const uint64_t wire_bytes = total_elems * wsz;
-  const Thresholds th = thresholds_for(N, cfg);
+  const Thresholds th = thresholds_for(N, cfg, in.in_symmetric && in.out_symmetric);
   Algo algo = in.forced;
   const bool nvls_types = nvls_type_ok(in.in, in.wire, in.out, in.op);
   // NVLS needs multicast views of whatever it touches: staging always has one
@@ -159,7 +163,7 @@ Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
   const uint64_t tiles = ceil_div(std::min(sv, shard_vecs), 512 * uint64_t(p.spec.unroll));
   // Measured: the switch path peaks with ~32 CTAs (more only add contention),
   // the P2P path wants ~96.
-  int cap = max_blocks ? max_blocks : (algo == Algo::Nvls ? 32 : 96);
+  int cap = max_blocks ? max_blocks : ((algo == Algo::Nvls && !p.copy_in && !p.copy_out) ? 32 : 96);
   p.spec.nblocks = static_cast<int>(std::clamp<uint64_t>(tiles, 1, cap));
   p.valid = true;
   return p;

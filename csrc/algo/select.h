@@ -32,7 +32,7 @@ struct Thresholds {
 
 // Built-in crossovers for a rank count (measured on 8xB200 NVSwitch; see the
 // benchmark sweep), adjusted by the config overrides.
-Thresholds thresholds_for(int nranks, const Config& cfg);
+Thresholds thresholds_for(int nranks, const Config& cfg, bool symmetric = true);
 // Default capacities of the inbox slots for a rank count.
 size_t default_ll_slot_bytes(int nranks, const Config& cfg);
 size_t default_inbox_slot_bytes(int nranks, const Config& cfg);

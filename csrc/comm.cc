@@ -5,6 +5,7 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <chrono>
 #include <cstring>
 #include <functional>
@@ -365,6 +366,17 @@ Comm::~Comm() {
   if (store_ && !aborted_.load()) {
     try { store_->barrier(); } catch (...) {}
   }
+  if (pipe_) {
+    cudaStreamDestroy(pipe_->s_in);
+    cudaStreamDestroy(pipe_->s_out);
+    cudaEventDestroy(pipe_->ev_start);
+    for (int h = 0; h < 2; ++h) {
+      cudaEventDestroy(pipe_->ev_in[h]);
+      cudaEventDestroy(pipe_->ev_comm[h]);
+      cudaEventDestroy(pipe_->ev_out[h]);
+    }
+    pipe_.reset();
+  }
   ring_.reset();
   transport_.reset();
   {
@@ -443,6 +455,15 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
   Plan plan = make_plan(pi, caps_, cfg_);
   if (!plan.valid) fail(Result::InvalidArgument, std::string("no kernel for this request: ") + plan.reason);
   if (!kernel_exists(plan.spec)) fail(Result::InvalidArgument, "no kernel for this type / operator combination");
+  if (mode == Mode::AllReduce && size_ > 1 && (plan.copy_in || plan.copy_out) &&
+      (plan.spec.algo == Algo::TwoShot || plan.spec.algo == Algo::Nvls) && cfg_.pipeline_min_bytes != 0 &&
+      count * dtype_size(wire_t) >= cfg_.pipeline_min_bytes) {
+    launch_pipelined(send, send_t, recv, recv_t, wire_t, count, op, scale, forced, stream);
+    stats_.calls++;
+    stats_.bytes += in_bytes;
+    stats_.pipelined++;
+    return;
+  }
 
   KParams kp;
   memset(&kp, 0, sizeof(kp));
@@ -482,6 +503,132 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
   stats_.calls++;
   stats_.bytes += in_bytes;
   stats_.by_algo[static_cast<int>(plan.spec.algo)]++;
+}
+
+// Large AllReduce on ordinary buffers.  The two-phase kernels need their operands in symmetric
+// memory; instead of staging inside one kernel (copy, barrier, reduce, barrier, copy: the
+// link idles during the copies) the message is cut into chunks that flow through two halves of
+// the staging areas: a copy-in kernel on one side stream, the zero-copy collective on the
+// caller's stream, a copy-out kernel on another side stream, tied together with events.  The
+// collective of chunk i overlaps the copy-in of chunk i+1 and the copy-out of chunk i-1.
+// Slot reuse is safe across ranks because every collective kernel starts and ends with a
+// cross-rank barrier: a peer touches this rank's half only between those two barriers, and this
+// rank enters the barrier of chunk i+2 only after its own copy-out of chunk i.
+void Comm::launch_pipelined(const void* send, DType send_t, void* recv, DType recv_t, DType wire_t, size_t count,
+                            RedOp op, double scale, Algo forced, cudaStream_t stream) {
+  if (!pipe_) {
+    pipe_.reset(new Pipeline());
+    RT_CHECK(cudaStreamCreateWithFlags(&pipe_->s_in, cudaStreamNonBlocking), "cudaStreamCreate");
+    RT_CHECK(cudaStreamCreateWithFlags(&pipe_->s_out, cudaStreamNonBlocking), "cudaStreamCreate");
+    RT_CHECK(cudaEventCreateWithFlags(&pipe_->ev_start, cudaEventDisableTiming), "cudaEventCreate");
+    for (int h = 0; h < 2; ++h) {
+      RT_CHECK(cudaEventCreateWithFlags(&pipe_->ev_in[h], cudaEventDisableTiming), "cudaEventCreate");
+      RT_CHECK(cudaEventCreateWithFlags(&pipe_->ev_comm[h], cudaEventDisableTiming), "cudaEventCreate");
+      RT_CHECK(cudaEventCreateWithFlags(&pipe_->ev_out[h], cudaEventDisableTiming), "cudaEventCreate");
+    }
+  }
+  const size_t wsz = dtype_size(wire_t), osz = dtype_size(recv_t), isz = dtype_size(send_t);
+  const size_t half = (caps_.stage_bytes / 2) & ~size_t(4095);
+  // Chunks: a quarter of the message, at least 32 MB (the collective kernel needs size to be
+  // efficient: measured 620 GB/s bus bandwidth at 32 MB, 770 at 128 MB on 8 GPUs), at most what
+  // one half of the staging holds.
+  size_t chunk_bytes = std::max<size_t>(count * wsz / 4, size_t(32) << 20);
+  size_t chunk = chunk_bytes / wsz;
+  chunk = std::min(chunk, half / std::max(wsz, osz));
+  chunk &= ~size_t(4095);
+  if (chunk == 0) fail(Result::InternalError, "staging too small for the chunk pipeline");
+  const bool is_float = send_t != DType::Int8 && send_t != DType::Uint8 && send_t != DType::Int32 &&
+                        send_t != DType::Uint32 && send_t != DType::Int64 && send_t != DType::Uint64;
+  const double factor = scale * (op == RedOp::Avg ? 1.0 / static_cast<double>(size_) : 1.0);
+
+  auto local_copy = [&](const void* src, DType st, void* dst, DType dt, size_t n, cudaStream_t s) {
+    LaunchSpec ls;
+    ls.algo = Algo::Local;
+    ls.in = st;
+    ls.wire = (st == dt) ? st : DType::Bfloat16;  // the mixed triples all travel as bf16
+    ls.out = dt;
+    ls.op = RedOp::Sum;
+    ls.nthreads = 512;
+    const size_t vecs = (n * std::max(dtype_size(st), dtype_size(dt)) + 15) / 16;
+    ls.nblocks = static_cast<int>(std::min<size_t>(std::max<size_t>(vecs / 2048, 1), 48));
+    KParams kp;
+    memset(&kp, 0, sizeof(kp));
+    kp.comm = dev_;
+    kp.args.send = src;
+    kp.args.recv = dst;
+    kp.args.count = n;
+    kp.args.scale_f = 1.0f;
+    kp.args.scale_d = 1.0;
+    if (!kernel_exists(ls)) fail(Result::InvalidArgument, "no copy kernel for this type combination");
+    RT_CHECK(launch_collective(ls, kp, s), "copy kernel launch");
+  };
+
+  RT_CHECK(cudaEventRecord(pipe_->ev_start, stream), "cudaEventRecord");
+  RT_CHECK(cudaStreamWaitEvent(pipe_->s_in, pipe_->ev_start, 0), "cudaStreamWaitEvent");
+  RT_CHECK(cudaStreamWaitEvent(pipe_->s_out, pipe_->ev_start, 0), "cudaStreamWaitEvent");
+  size_t i = 0;
+  for (size_t off = 0; off < count; off += chunk, ++i) {
+    const int h = static_cast<int>(i & 1);
+    const size_t n = std::min(chunk, count - off);
+    char* a_h = dev_.ctrl[rank_] + dev_.off_stage_a + h * half;
+    char* b_h = dev_.ctrl[rank_] + dev_.off_stage_b + h * half;
+    // copy-in (after the collective that last read this half)
+    if (i >= 2) RT_CHECK(cudaStreamWaitEvent(pipe_->s_in, pipe_->ev_comm[h], 0), "cudaStreamWaitEvent");
+    local_copy(static_cast<const char*>(send) + off * isz, send_t, a_h, wire_t, n, pipe_->s_in);
+    RT_CHECK(cudaEventRecord(pipe_->ev_in[h], pipe_->s_in), "cudaEventRecord");
+    // collective on the staging halves, zero-copy (after the copy-out that last read B_h)
+    RT_CHECK(cudaStreamWaitEvent(stream, pipe_->ev_in[h], 0), "cudaStreamWaitEvent");
+    if (i >= 2) RT_CHECK(cudaStreamWaitEvent(stream, pipe_->ev_out[h], 0), "cudaStreamWaitEvent");
+    PlanInput pi;
+    pi.mode = Mode::AllReduce;
+    pi.count = n;
+    pi.in = wire_t;
+    pi.wire = wire_t;
+    pi.out = recv_t;
+    pi.op = op;
+    pi.forced = forced;
+    pi.in_symmetric = pi.out_symmetric = true;
+    pi.in_has_mc = pi.out_has_mc = caps_.nvls;
+    Plan plan = make_plan(pi, caps_, cfg_);
+    if (!plan.valid || plan.copy_in || plan.copy_out || !kernel_exists(plan.spec))
+      fail(Result::InternalError, "chunk pipeline: no zero-copy plan for a chunk");
+    if (plan.spec.algo != Algo::TwoShot && plan.spec.algo != Algo::Nvls) {
+      plan.spec.algo = Algo::TwoShot;  // small tail chunk: stay on a kernel that uses the staging views
+      if (!kernel_exists(plan.spec)) fail(Result::InternalError, "chunk pipeline: no kernel");
+      const uint64_t VW = 16 / wsz;
+      plan.shard_elems = ((n + VW - 1) / VW + size_ - 1) / size_ * VW;
+      plan.chunk_shard_vecs = (plan.shard_elems + VW - 1) / VW;
+      plan.spec.nthreads = 512;
+      plan.spec.nblocks = static_cast<int>(std::min<uint64_t>(std::max<uint64_t>(plan.chunk_shard_vecs / 2048, 1), 96));
+    }
+    KParams kp;
+    memset(&kp, 0, sizeof(kp));
+    kp.comm = dev_;
+    CollArgs& a = kp.args;
+    a.send = a_h;
+    a.recv = b_h;
+    a.count = n;
+    a.shard_elems = plan.shard_elems;
+    a.chunk_shard_vecs = plan.chunk_shard_vecs;
+    a.scale_f = static_cast<float>(factor);
+    a.scale_d = factor;
+    a.int_div = (op == RedOp::Avg && !is_float) ? size_ : 0;
+    for (int r = 0; r < size_; ++r) {
+      a.in_peer[r] = dev_.ctrl[r] + dev_.off_stage_a + h * half;
+      a.out_peer[r] = dev_.ctrl[r] + dev_.off_stage_b + h * half;
+    }
+    a.in_mc = dev_.ctrl_mc ? dev_.ctrl_mc + dev_.off_stage_a + h * half : nullptr;
+    a.out_mc = dev_.ctrl_mc ? dev_.ctrl_mc + dev_.off_stage_b + h * half : nullptr;
+    RT_CHECK(launch_collective(plan.spec, kp, stream), "kernel launch");
+    RT_CHECK(cudaEventRecord(pipe_->ev_comm[h], stream), "cudaEventRecord");
+    stats_.by_algo[static_cast<int>(plan.spec.algo)]++;
+    // copy-out
+    RT_CHECK(cudaStreamWaitEvent(pipe_->s_out, pipe_->ev_comm[h], 0), "cudaStreamWaitEvent");
+    local_copy(b_h, recv_t, static_cast<char*>(recv) + off * osz, recv_t, n, pipe_->s_out);
+    RT_CHECK(cudaEventRecord(pipe_->ev_out[h], pipe_->s_out), "cudaEventRecord");
+  }
+  RT_CHECK(cudaStreamWaitEvent(stream, pipe_->ev_out[0], 0), "cudaStreamWaitEvent");
+  if (i >= 2) RT_CHECK(cudaStreamWaitEvent(stream, pipe_->ev_out[1], 0), "cudaStreamWaitEvent");
 }
 
 void Comm::wait_blocking(cudaStream_t stream) {
@@ -666,7 +813,7 @@ std::string Comm::stats_json() {
     o << "\"" << algo_name(a) << "\":" << stats_.by_algo[static_cast<int>(a)];
   }
   o << "},\"zero_copy_in\":" << stats_.zero_copy_in << ",\"zero_copy_out\":" << stats_.zero_copy_out
-    << ",\"staged_calls\":" << stats_.staged_passes << ",\"graph_captures_seen\":" << stats_.graph_captures_seen;
+    << ",\"staged_calls\":" << stats_.staged_passes << ",\"pipelined_calls\":" << stats_.pipelined << ",\"graph_captures_seen\":" << stats_.graph_captures_seen;
   if (watchdog_) {
     o << ",\"watchdog\":{\"polls\":" << watchdog_->stats().polls.load() << ",\"trips\":" << watchdog_->stats().trips.load()
       << ",\"device_failures\":" << watchdog_->stats().device_failures.load() << ",\"remote_aborts\":"

@@ -34,7 +34,7 @@ namespace hera { class Worker; }
 struct CommStats {
   uint64_t calls = 0, bytes = 0;
   uint64_t by_algo[8] = {0};
-  uint64_t zero_copy_in = 0, zero_copy_out = 0, staged_passes = 0;
+  uint64_t zero_copy_in = 0, zero_copy_out = 0, staged_passes = 0, pipelined = 0;
   uint64_t graph_captures_seen = 0, errors = 0;
 };
 
@@ -77,6 +77,8 @@ class Comm {
   void check_usable();
   void launch(Mode mode, const void* send, DType send_t, void* recv, DType recv_t, DType wire_t, size_t count,
               RedOp op, double scale, Algo forced, cudaStream_t stream);
+  void launch_pipelined(const void* send, DType send_t, void* recv, DType recv_t, DType wire_t, size_t count, RedOp op,
+                        double scale, Algo forced, cudaStream_t stream);
   void ring_all_reduce(const void* send, void* recv, size_t count, DType t, RedOp op, cudaStream_t stream);
   // Segment containing [ptr, ptr+bytes) on this rank; offset returned.
   std::shared_ptr<Segment> find_segment(const void* ptr, size_t bytes, size_t* offset);
@@ -107,6 +109,13 @@ class Comm {
   volatile uint32_t* abort_host_ = nullptr;
   volatile uint32_t* progress_host_ = nullptr;
   std::unique_ptr<Watchdog> watchdog_;
+
+  // chunk pipeline for large AllReduces on ordinary buffers
+  struct Pipeline {
+    cudaStream_t s_in = nullptr, s_out = nullptr;
+    cudaEvent_t ev_start = nullptr, ev_in[2] = {nullptr, nullptr}, ev_comm[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
+  };
+  std::unique_ptr<Pipeline> pipe_;
 
   // network plane
   std::unique_ptr<OneSidedTransport> transport_;

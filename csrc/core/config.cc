@@ -92,6 +92,7 @@ Config Config::from_getter(Getter get, void* ctx) {
   r.num("MINI_NCCL_ONESHOT_MAX_BYTES", c.oneshot_max_bytes);
   r.num("MINI_NCCL_NVLS_MIN_BYTES", c.nvls_min_bytes);
   r.num("MINI_NCCL_STAGING_BYTES", c.staging_bytes);
+  r.num("MINI_NCCL_PIPELINE_MIN_BYTES", c.pipeline_min_bytes);
   r.num("MINI_NCCL_MAX_BLOCKS", c.max_blocks);
   r.num("MINI_NCCL_UNROLL", c.unroll);
   r.boolean("MINI_NCCL_NUMA_BIND", c.numa_bind);

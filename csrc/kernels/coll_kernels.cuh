@@ -43,13 +43,25 @@ __device__ __forceinline__ void local_body(const KParams& P, int blk, int nblk) 
                          : 16 / sizeof(typename Elem<OutT>::Raw);
   const bool in_al = vec_aligned<InT, VW>(a.send), out_al = vec_aligned<OutT, VW>(a.recv);
   const uint64_t nvec = (a.count + VW - 1) / VW;
-  for (uint64_t v = uint64_t(blk) * blockDim.x + threadIdx.x; v < nvec; v += uint64_t(nblk) * blockDim.x) {
-    typename Elem<InT>::Acc x[VW];
-    load_vec<InT, VW>(a.send, v * VW, a.count, in_al, x);
-    typename Elem<OutT>::Acc y[VW];
+  // Four vectors in flight per thread: a copy is bound by how many loads are outstanding.
+  constexpr int U = 4;
+  const uint64_t stride = uint64_t(nblk) * blockDim.x;
+  for (uint64_t v0 = uint64_t(blk) * blockDim.x + threadIdx.x; v0 < nvec; v0 += U * stride) {
+    typename Elem<InT>::Acc x[U][VW];
 #pragma unroll
-    for (int k = 0; k < VW; ++k) y[k] = finalize<OutT>(static_cast<typename Elem<OutT>::Acc>(x[k]), a);
-    store_vec<OutT, VW>(a.recv, v * VW, a.count, out_al, y);
+    for (int u = 0; u < U; ++u) {
+      const uint64_t v = v0 + u * stride;
+      if (v < nvec) load_vec<InT, VW>(a.send, v * VW, a.count, in_al, x[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint64_t v = v0 + u * stride;
+      if (v >= nvec) continue;
+      typename Elem<OutT>::Acc y[VW];
+#pragma unroll
+      for (int k = 0; k < VW; ++k) y[k] = finalize<OutT>(static_cast<typename Elem<OutT>::Acc>(x[u][k]), a);
+      store_vec<OutT, VW>(a.recv, v * VW, a.count, out_al, y);
+    }
   }
 }
 

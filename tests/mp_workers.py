@@ -195,6 +195,31 @@ def gpu_battery(rank, n, kw):
                     assert _bits_equal(got, want), f"{algo} {O.DTYPE_NAMES[dtype]} {O.OP_NAMES[op]} {count} {where}: mismatch"
                 res["cases"] += 1
                 comm.barrier()
+    # large message on ordinary buffers: the chunk pipeline (copy-in / collective / copy-out overlapped)
+    count = (16 << 20) + 12345
+    ins = _np_inputs(_lib.FLOAT32, count, n, _lib.SUM)
+    want = O.oracle_allreduce(ins, _lib.FLOAT32, _lib.AVG)
+    big = torch.from_numpy(ins[rank]).cuda()
+    big_out = torch.zeros_like(big)
+    comm.all_reduce(big, "avg", out=big_out)
+    torch.cuda.synchronize()
+    err = float(np.abs(big_out.cpu().numpy() - want).max())
+    assert err <= (1e-5 * n if res["nvls"] else 0.0), f"pipelined AllReduce: err {err}"
+    assert comm.stats()["pipelined_calls"] >= 1
+    gp = torch.cuda.CUDAGraph()
+    sp = torch.cuda.Stream()
+    sp.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(sp):
+        with torch.cuda.graph(gp, stream=sp):
+            comm.all_reduce(big, "avg", out=big_out)
+    torch.cuda.current_stream().wait_stream(sp)
+    big_out.zero_()
+    gp.replay()
+    gp.replay()
+    torch.cuda.synchronize()
+    err = float(np.abs(big_out.cpu().numpy() - want).max())
+    assert err <= (1e-5 * n if res["nvls"] else 0.0), f"pipelined AllReduce in a graph: err {err}"
+    del gp, big, big_out
     # NVLS on exactly representable data is bit-exact whatever the order
     if res["nvls"]:
         count = 1 << 18

@@ -125,6 +125,8 @@ def test_planner_picks_by_size(lib):
     assert plan(lib, 8, 16384)["algo"] == "ll"                     # 64 KB
     assert plan(lib, 8, 40000)["algo"] == "oneshot"                # 160 KB
     assert plan(lib, 8, 1 << 20)["algo"] == "twoshot"              # 4 MB, no multicast
+    assert plan(lib, 8, 1 << 18)["algo"] == "oneshot"              # 1 MB on ordinary buffers: no staging copies
+    assert plan(lib, 8, 1 << 18, in_sym=1, out_sym=1)["algo"] == "twoshot"
     assert plan(lib, 8, 1 << 20, nvls=1)["algo"] == "nvls"
     assert plan(lib, 8, 1 << 20, nvls=1, op=_lib.MAX)["algo"] == "twoshot"      # the switch only adds
     assert plan(lib, 8, 1 << 20, nvls=1, dtype=_lib.INT32)["algo"] == "twoshot"
