@@ -43,7 +43,7 @@ def main():
     except Exception:
         pass
     res = {"world": world, "tokens": tokens, "hidden": hidden, "ffn": ffn}
-    for n_comm in (8, 16, 24):
+    for n_comm in (0, 16, 36):
         mlp = TensorParallelMLP(comm, tokens, hidden, ffn, n_comm_ctas=n_comm)
         x = (torch.randn(tokens // world, hidden, device="cuda") * 0.5).to(torch.bfloat16)
         mlp.input_shard.copy_(x)
@@ -57,7 +57,7 @@ def main():
         res[f"ncomm{n_comm}"] = {"ag_gemm_us": round(ms_ag * 1e3, 1), "gemm_rs_us": round(ms_rs * 1e3, 1),
                                  "mlp_fused_us": round(ms_fused * 1e3, 1), "rel_err_vs_unfused": round(err, 5),
                                  "status": gemm_status()}
-        if n_comm == 16:
+        if n_comm == 0:
             ms_unf = _time_loop(lambda: mlp.forward_unfused(x), 30, 5, world)
             res["mlp_cublas_nccl_us"] = round(ms_unf * 1e3, 1)
             fl = world and 2.0 * tokens * hidden * (ffn // world)

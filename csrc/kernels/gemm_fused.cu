@@ -336,8 +336,22 @@ MNCCL_EXPORT int mncclAllGatherGemmBf16(void* const* xg_peers, const void* B, vo
     return -3;
   }
   const int sms = sm_count();
-  int n_comm = nranks > 1 ? (n_comm_ctas > 0 ? n_comm_ctas : 16) : 0;
-  if (n_comm > sms / 2) n_comm = sms / 2;
+  const int all_tiles = (M / kBM) * ((N + kBN - 1) / kBN);
+  int n_comm = 0;
+  if (nranks > 1) {
+    if (n_comm_ctas > 0) {
+      n_comm = n_comm_ctas;
+    } else {
+      // The tiles need ceil(tiles / CTAs) waves anyway: give the GEMM just enough CTAs for that
+      // number of waves and let the rest move data (at least 16, at most 48).
+      const int waves = (all_tiles + (sms - 16) - 1) / (sms - 16);
+      const int need = (all_tiles + waves - 1) / waves;
+      n_comm = sms - need;
+      if (n_comm < 16) n_comm = 16;
+      if (n_comm > 48) n_comm = 48;
+    }
+    if (n_comm > sms / 2) n_comm = sms / 2;
+  }
   AgEpilogue epi{};
   epi.rank = rank;
   epi.nranks = nranks;

@@ -34,7 +34,10 @@ class MiniNcclError(RuntimeError):
 
 
 def lib_file() -> Path:
-    return _HERE / "lib" / "libmini_nccl.so"
+    """The shared object to load; MINI_NCCL_LIB overrides the in-tree default (used by the tests
+    to load the variant built against the stand-in verbs implementation)."""
+    override = os.environ.get("MINI_NCCL_LIB")
+    return Path(override) if override else _HERE / "lib" / "libmini_nccl.so"
 
 
 def lib() -> C.CDLL:

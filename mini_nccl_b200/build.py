@@ -163,6 +163,38 @@ def build(verbose: bool = False, programs: bool = True, jobs: int | None = None)
     return lib
 
 
+def build_fake_verbs_variant(verbose: bool = False) -> Path:
+    """Test-only variant of the library with the verbs provider compiled against the stand-in
+    header and implementation under tests/fake_verbs (no libibverbs needed).  Reuses the objects
+    of the normal build; only the transport factory and the provider are compiled again."""
+    lib = build(verbose=verbose, programs=False)
+    fake = ROOT / "tests" / "fake_verbs"
+    out = LIBDIR / "libmini_nccl_fakeverbs.so"
+    extra = ["-DMNCCL_HAVE_VERBS=1", "-I", str(fake)]
+    special = {CSRC / "net/factory.cc", CSRC / "net/verbs_transport.cc", fake / "fake_verbs.cc"}
+    objs = []
+    hdr = _newest_header_mtime()
+    for s in special:
+        o = BUILD / f"fakeverbs-{s.stem}.o"
+        if not o.exists() or o.stat().st_mtime < max(s.stat().st_mtime, hdr):
+            cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wextra", "-pthread",
+                   *_common_includes(), *extra, "-c", str(s), "-o", str(o)]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError(f"compile failed: {s}\n{r.stderr}")
+        objs.append(o)
+    host = [s for s in HOST_SOURCES if s != "net/factory.cc"]
+    cuda = list(CUDA_SOURCES) + [o for o in OPTIONAL_CUDA if (CSRC / o).exists()]
+    objs += [_obj_path(CSRC / s) for s in host + cuda]
+    if not out.exists() or out.stat().st_mtime < max(o.stat().st_mtime for o in objs):
+        cmd = [NVCC, "-shared", *ARCH, "-cudart", "static", "-Xlinker", "-Bsymbolic-functions", "-o", str(out),
+               *map(str, objs), "-lpthread", "-lrt", "-ldl"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed\n{r.stdout}\n{r.stderr}")
+    return out
+
+
 def clean() -> None:
     shutil.rmtree(BUILD, ignore_errors=True)
     for p in (lib_path(),):

@@ -81,7 +81,7 @@ class GemmReduceScatter:
 
 
 class AllGatherGemm:
-    def __init__(self, comm, M: int, K: int, n_comm_ctas: int = 16):
+    def __init__(self, comm, M: int, K: int, n_comm_ctas: int = 0):
         import torch
 
         L = _native()
@@ -91,7 +91,7 @@ class AllGatherGemm:
         self.comm, self.M, self.K, self.n_comm = comm, M, K, n_comm_ctas
         self.gather = _sym(comm, M * K, torch.bfloat16).view(M, K)   # X of every rank lands here
         self.ready = _sym(comm, max(4, L.mncclAgGemmReadyWords(M)), torch.int32)
-        self.bar = _sym(comm, max(4, L.mncclAgGemmBarWords(R, max(n_comm_ctas, 1))), torch.int32)
+        self.bar = _sym(comm, max(4, L.mncclAgGemmBarWords(R, max(n_comm_ctas, 74))), torch.int32)
         self.state = torch.zeros(4, dtype=torch.int32, device="cuda")
         torch.cuda.synchronize()
         if R > 1:

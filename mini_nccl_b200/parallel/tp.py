@@ -17,7 +17,7 @@ from ..ops.fused import AllGatherGemm, GemmReduceScatter
 
 
 class TensorParallelMLP:
-    def __init__(self, comm, tokens: int, hidden: int, ffn: int, seed: int = 0, n_comm_ctas: int = 16):
+    def __init__(self, comm, tokens: int, hidden: int, ffn: int, seed: int = 0, n_comm_ctas: int = 0):
         R = comm.size
         if ffn % R:
             raise ValueError("ffn must divide by the number of ranks")
