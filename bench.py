@@ -102,10 +102,17 @@ def main():
         comm.all_reduce(buf, "sum", out=out, scale=1.0 / world if world > 1 else 1.0)
 
     # ---- headline: device-timed, K steps, max over ranks
+    # Untimed pre-warm for ~0.3 s: clocks and NVLink links leave their idle power states (a cold
+    # start measured 15 % below the steady state), then the W warm-up steps proper.
+    t_pre = time.perf_counter()
+    while time.perf_counter() - t_pre < 0.3:
+        for _ in range(10):
+            step()
+        torch.cuda.synchronize()
     for _ in range(max(args.warmup, 3)):
         step()
     sync_all()
-    sampler = ClockSampler(torch.cuda.current_device()).start()
+    sampler = ClockSampler(torch.cuda.current_device(), period_s=0.004).start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(args.steps):

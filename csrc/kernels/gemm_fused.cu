@@ -151,16 +151,25 @@ struct RsEpilogue {
         const int rr = row0 + v / vec_per_row;
         const int cc = col0 + (v % vec_per_row) * 8;
         if (rr >= rows_per_rank) continue;
-        float acc[8];
-        for (int src = 0; src < nranks; ++src) {
-          const uint4 x = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(src) * slot_elems(g) +
-                                                          static_cast<size_t>(rr) * g.N + cc);
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+        // issue every slot's load before the first add: the pass is bound by load latency
+        uint4 x[kMaxTpRanks];
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const float2 f = __bfloat1622float2(h[k]);
-            acc[2 * k] = src == 0 ? f.x : acc[2 * k] + f.x;
-            acc[2 * k + 1] = src == 0 ? f.y : acc[2 * k + 1] + f.y;
+        for (int src = 0; src < kMaxTpRanks; ++src) {
+          if (src < nranks)
+            x[src] = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(src) * slot_elems(g) +
+                                                     static_cast<size_t>(rr) * g.N + cc);
+        }
+        float acc[8];
+#pragma unroll
+        for (int src = 0; src < kMaxTpRanks; ++src) {
+          if (src < nranks) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x[src]);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float2 f = __bfloat1622float2(h[k]);
+              acc[2 * k] = src == 0 ? f.x : acc[2 * k] + f.x;
+              acc[2 * k + 1] = src == 0 ? f.y : acc[2 * k + 1] + f.y;
+            }
           }
         }
         uint4 y;
@@ -213,17 +222,18 @@ struct AgEpilogue {
       const int peer = (rank - s + nranks) % nranks;       // the peer that wants this shard soonest first
       for (int c = 0; c < chunks; ++c) {
         const int row0 = rank * rows_per_rank + c * kBM;
-        for (int v0 = cta * static_cast<int>(blockDim.x) + t; v0 < vecs; v0 += 4 * stride) {
-          uint4 x[4];
-          size_t off[4];
+        constexpr int U = 8;  // 128 bytes in flight per thread: the push is bound by the latency of the local loads
+        for (int v0 = cta * static_cast<int>(blockDim.x) + t; v0 < vecs; v0 += U * stride) {
+          uint4 x[U];
+          size_t off[U];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int u = 0; u < U; ++u) {
             const int v = v0 + u * stride;
             off[u] = (static_cast<size_t>(row0 + v / vec_per_row) * lda + static_cast<size_t>(v % vec_per_row) * 8) * 2;
             if (v < vecs) x[u] = *reinterpret_cast<const uint4*>(xg[rank] + off[u]);
           }
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int u = 0; u < U; ++u) {
             const int v = v0 + u * stride;
             if (v < vecs) *reinterpret_cast<uint4*>(xg[peer] + off[u]) = x[u];
           }

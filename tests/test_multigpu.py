@@ -83,3 +83,33 @@ def test_fused_tensor_parallel_kernels_llama_shape(free_port):
     # Llama-3-8B block at TP=8: 4096 tokens, hidden 4096, FFN 14336 / 8 = 1792 per rank
     res = run_ranks("gpu_tp", 8, {"M": 4096, "N": 4096, "K": 1792, "iters": 2}, {"MINI_NCCL_BOOTSTRAP_PORT": free_port}, timeout=600)
     assert len(res) == 8
+
+
+@pytest.mark.multigpu(2)
+def test_reference_shaped_programs_on_gpus(free_port):
+    # `app` and `perf_test` through the C ABI, one process per GPU; pinned host buffers as in the
+    # reference's programs, then device buffers.
+    import os
+    import subprocess
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    bindir = root / "mini_nccl_b200" / "bin"
+    if not (bindir / "app").exists():
+        from mini_nccl_b200 import build
+
+        build.build()
+    env = dict(os.environ, MINI_NCCL_BOOTSTRAP_PORT=str(free_port))
+    ps = [subprocess.Popen([str(bindir / "app"), str(r), "127.0.0.1", "2"], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+          for r in range(2)]
+    outs = [p.communicate(timeout=180) for p in ps]
+    assert all(p.returncode == 0 for p in ps), outs
+    assert all("[PASS]" in o[0] and "= 3.0" in o[0] for o in outs)
+    for k, dev in enumerate(("0", "1")):
+        env2 = dict(env, MINI_NCCL_BOOTSTRAP_PORT=str(free_port + 1 + k), PERF_TEST_MAX_MIB="64", PERF_TEST_DEVICE_BUFFERS=dev)
+        ps = [subprocess.Popen([str(bindir / "perf_test"), str(r), "2", "127.0.0.1"], env=env2, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+              for r in range(2)]
+        outs = [p.communicate(timeout=300) for p in ps]
+        assert all(p.returncode == 0 for p in ps), outs
+        assert "BusBW(GB/s)" in outs[0][0] and "67108864" in outs[0][0] and "(FAIL)" not in outs[0][0]
+        print(outs[0][0])
