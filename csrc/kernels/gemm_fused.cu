@@ -31,6 +31,8 @@ namespace mnccl {
 namespace gemm {
 
 constexpr int kMaxTpRanks = 8;
+constexpr int kAgSlots = 16;          // rows in flight per communication CTA (ring in shared memory)
+constexpr int kAgPartsPerChunk = 4;   // a 128-row chunk is pushed as four independent quarters
 
 __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -182,7 +184,7 @@ struct RsEpilogue {
     }
   }
 
-  __device__ __forceinline__ void comm_cta(const GemmArgs&, uint32_t, int, int, volatile uint32_t*) const {}
+  __device__ __forceinline__ void comm_cta(const GemmArgs&, uint32_t, int, int, volatile uint32_t*, uint8_t*, uint32_t) const {}
 };
 
 // ------------------------------------------------------------------ all-gather -> GEMM
@@ -203,44 +205,70 @@ struct AgEpilogue {
   __device__ __forceinline__ void tile_done(const GemmArgs&, uint32_t, int, int, int, int) const {}
   __device__ __forceinline__ void after_tiles(const GemmArgs&, uint32_t, int, int, int, int, volatile uint32_t*) const {}
 
-  // A communication CTA: barrier with the same CTA of every peer (everyone has left
-  // the previous use of the gather buffers), then push the local shard to every peer.
+  // A communication CTA: barrier with the same CTA of every peer (everyone has left the previous
+  // use of the gather buffers), then push the local shard to every peer with the TMA engine:
+  // bulk copies local memory -> shared memory -> peer memory, a ring of row-sized slots, driven by
+  // one thread.  Work items are (peer, chunk of 128 rows, quarter of the chunk), dealt round-robin
+  // to the communication CTAs in the order the peers will need them; each finished quarter adds
+  // one to the peer's counter for that chunk (kAgPartsPerChunk per chunk and call).
   __device__ __forceinline__ void comm_cta(const GemmArgs& g, uint32_t epoch, int cta, int n_comm,
-                                           volatile uint32_t* abort_flag) const {
+                                           volatile uint32_t* abort_flag, uint8_t* smem, uint32_t smem_base) const {
+    __shared__ uint64_t s_full[kAgSlots];
     const int t = threadIdx.x;
     if (t < nranks && t != rank) {
       st_release_sys_u32(bar[t] + cta * nranks + rank, epoch);
       wait_flag_sys(bar[rank] + cta * nranks + t, epoch, abort_flag, g.wait_budget_ns);
     }
+    if (t == 0) {
+      for (int i = 0; i < kAgSlots; ++i) mbar_init(smem_u32(&s_full[i]), 1);
+      fence_barrier_init();
+      fence_proxy_async();
+    }
     __syncthreads();
-    if (*abort_flag != 0u) return;
+    if (*abort_flag != 0u || t != 0) return;
+    (void)smem;
+    const uint32_t row_bytes = static_cast<uint32_t>(g.K) * 2u;
+    int slots = static_cast<int>((kStages * kStageBytes) / row_bytes);
+    if (slots > kAgSlots) slots = kAgSlots;
+    const int depth = slots / 2;                       // loads run this many rows ahead of the stores
     const int chunks = rows_per_rank / kBM;
-    const int vec_per_row = g.K / 8;                       // 16-byte vectors in a row
-    const int vecs = kBM * vec_per_row;                    // per chunk
-    const int stride = n_comm * static_cast<int>(blockDim.x);
-    for (int s = 1; s < nranks; ++s) {
-      const int peer = (rank - s + nranks) % nranks;       // the peer that wants this shard soonest first
-      for (int c = 0; c < chunks; ++c) {
-        const int row0 = rank * rows_per_rank + c * kBM;
-        constexpr int U = 8;  // 128 bytes in flight per thread: the push is bound by the latency of the local loads
-        for (int v0 = cta * static_cast<int>(blockDim.x) + t; v0 < vecs; v0 += U * stride) {
-          uint4 x[U];
-          size_t off[U];
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const int v = v0 + u * stride;
-            off[u] = (static_cast<size_t>(row0 + v / vec_per_row) * lda + static_cast<size_t>(v % vec_per_row) * 8) * 2;
-            if (v < vecs) x[u] = *reinterpret_cast<const uint4*>(xg[rank] + off[u]);
+    const int rows_per_part = kBM / kAgPartsPerChunk;
+    const int items = (nranks - 1) * chunks * kAgPartsPerChunk;
+    uint32_t n_loaded = 0;                             // rows whose load has been issued, over all items
+    for (int item = cta; item < items; item += n_comm) {
+      const int s = item / (chunks * kAgPartsPerChunk) + 1;
+      const int c = (item / kAgPartsPerChunk) % chunks;
+      const int part = item % kAgPartsPerChunk;
+      const int peer = (rank - s + nranks) % nranks;   // the peer that wants this shard soonest first
+      const int row0 = rank * rows_per_rank + c * kBM + part * rows_per_part;
+      const uint32_t first = n_loaded;
+      bool ok = true;
+      for (int i = 0; i < rows_per_part + depth && ok; ++i) {
+        if (i < rows_per_part) {
+          const uint32_t n = first + i, slot = n % slots;
+          // the store that last used this slot must have finished reading it
+          if (n >= static_cast<uint32_t>(slots)) {
+            // with the full ring (16 slots, stores 8 rows behind) that store is the 8th most recent group
+            if (slots == kAgSlots) bulk_wait_read<kAgSlots / 2 - 1>();
+            else bulk_wait_read<0>();
           }
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const int v = v0 + u * stride;
-            if (v < vecs) *reinterpret_cast<uint4*>(xg[peer] + off[u]) = x[u];
-          }
+          const uint32_t full = smem_u32(&s_full[slot]);
+          mbar_arrive_expect_tx(full, row_bytes);
+          bulk_load(smem_base + slot * row_bytes, xg[rank] + static_cast<size_t>(row0 + i) * lda * 2, row_bytes, full);
+          ++n_loaded;
         }
-        __syncthreads();  // every store of this CTA's part of the chunk precedes the count
-        if (t == 0) red_release_sys_add(ready[peer] + (row0 / kBM), 1u);
+        const int k = i - depth;
+        if (k >= 0) {
+          const uint32_t n = first + k, slot = n % slots;
+          if (!mbar_wait(smem_u32(&s_full[slot]), (n / slots) & 1u, abort_flag, g.wait_budget_ns)) { ok = false; break; }
+          bulk_store(xg[peer] + static_cast<size_t>(row0 + k) * lda * 2, smem_base + slot * row_bytes, row_bytes);
+          bulk_commit();
+        }
       }
+      bulk_wait_all();            // the rows of this quarter are written
+      if (!ok) return;
+      fence_proxy_async_all();    // writes of the async proxy before the release below
+      red_release_sys_add(ready[peer] + (row0 / kBM), 1u);
     }
   }
 };
@@ -334,6 +362,10 @@ MNCCL_EXPORT int mncclAllGatherGemmBf16(void* const* xg_peers, const void* B, vo
   if (!xg_peers || !B || !C || !state) return -1;
   if (!check_common(M, N, K, rank, nranks, "all-gather->GEMM")) return -2;
   if (nranks > 1 && (!ready_peers || !bar_peers)) return -1;
+  if (K * 2 > kStages * kStageBytes / 4) {
+    fprintf(stderr, "[Mini-NCCL] all-gather->GEMM: K too large for the row ring (max %d)\n", kStages * kStageBytes / 8);
+    return -2;
+  }
   if (lda == 0) lda = K;
   if (ldb == 0) ldb = K;
   if (ldc == 0) ldc = N;
@@ -387,7 +419,7 @@ MNCCL_EXPORT int mncclAllGatherGemmBf16(void* const* xg_peers, const void* B, vo
   g.ticket_ptr = state + 1;
   if (nranks > 1) {
     g.a_ready = epi.ready[rank];
-    g.a_ready_mult = static_cast<uint32_t>(n_comm);
+    g.a_ready_mult = static_cast<uint32_t>(kAgPartsPerChunk);
     g.rows_per_chunk = kBM;
     g.a_local_first = rank * tiles_m_local;
     g.a_local_count = tiles_m_local;

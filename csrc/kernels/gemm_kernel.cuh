@@ -68,7 +68,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       s_abort = 0;
     }
     __syncthreads();
-    epi.comm_cta(g, s_epoch, static_cast<int>(blockIdx.x) - n_gemm, static_cast<int>(gridDim.x) - n_gemm, &s_abort);
+    epi.comm_cta(g, s_epoch, static_cast<int>(blockIdx.x) - n_gemm, static_cast<int>(gridDim.x) - n_gemm, &s_abort, smem, base);
     __syncthreads();
     if (threadIdx.x == 0) {
       if (s_abort != 0u && g.err != nullptr) atomicCAS(g.err, 0u, s_abort);
