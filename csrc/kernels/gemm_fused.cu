@@ -132,55 +132,69 @@ struct RsEpilogue {
                                               volatile uint32_t* abort_flag) const {
     const int tiles_n = (g.N + kBN - 1) / kBN;
     const int tiles_m_local = rows_per_rank / kBM;
-    const int items = tiles_m_local * tiles_n * 4;  // a tile quarter: 32 rows x 256 columns
-    const int tid = ((q + 2) & 3) * 32 + lane;      // 0..127 over warps 2,3,4,5 in launch order
+    constexpr int kParts = 8, kRows = kBM / kParts;   // an item: 16 rows x 256 columns of one tile
+    const int items = tiles_m_local * tiles_n * kParts;
+    const int tid = ((q + 2) & 3) * 32 + lane;        // 0..127 over warps 2,3,4,5 in launch order
     const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(stage[rank]) +
                                 static_cast<size_t>(epoch & 1u) * nranks * slot_elems(g);
+    int last_tile = -1;
     for (int item = cta; item < items; item += n_cta) {
-      const int tile = item >> 2, quarter = item & 3;
+      const int tile = item / kParts, part = item % kParts;
       const int ltm = tile / tiles_n, tn = tile - ltm * tiles_n;
-      if (tid < nranks) {
-        wait_flag_sys(flags[rank] + (static_cast<size_t>(tid) * tiles_m_local + ltm) * tiles_n + tn, epoch, abort_flag,
-                      g.wait_budget_ns);
+      if (tile != last_tile) {
+        if (tid < nranks) {
+          wait_flag_sys(flags[rank] + (static_cast<size_t>(tid) * tiles_m_local + ltm) * tiles_n + tn, epoch, abort_flag,
+                        g.wait_budget_ns);
+        }
+        epilogue_warps_sync();
+        if (*abort_flag != 0u) return;
+        last_tile = tile;
       }
-      epilogue_warps_sync();
-      if (*abort_flag != 0u) return;
-      const int row0 = ltm * kBM + quarter * 32;
+      const int row0 = ltm * kBM + part * kRows;
       const int col0 = tn * kBN;
       const int ncols = min(kBN, g.N - col0);
       const int vec_per_row = ncols / 8;  // 8 bf16 = 16 bytes (N is a multiple of 8)
-      for (int v = tid; v < 32 * vec_per_row; v += 128) {
-        const int rr = row0 + v / vec_per_row;
-        const int cc = col0 + (v % vec_per_row) * 8;
-        if (rr >= rows_per_rank) continue;
-        // issue every slot's load before the first add: the pass is bound by load latency
-        uint4 x[kMaxTpRanks];
+      const int nvec = kRows * vec_per_row;
+      constexpr int U = 2;  // vectors per thread per pass: U * nranks loads in flight (the pass is latency-bound)
+      for (int v0 = tid; v0 < nvec; v0 += 128 * U) {
+        uint4 x[U][kMaxTpRanks];
+        size_t off[U];
 #pragma unroll
-        for (int src = 0; src < kMaxTpRanks; ++src) {
-          if (src < nranks)
-            x[src] = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(src) * slot_elems(g) +
-                                                     static_cast<size_t>(rr) * g.N + cc);
+        for (int u = 0; u < U; ++u) {
+          const int v = v0 + u * 128;
+          const int rr = row0 + v / vec_per_row;
+          const int cc = col0 + (v % vec_per_row) * 8;
+          off[u] = static_cast<size_t>(rr) * g.N + cc;
+#pragma unroll
+          for (int src = 0; src < kMaxTpRanks; ++src)
+            if (src < nranks && v < nvec) x[u][src] = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(src) * slot_elems(g) + off[u]);
         }
-        float acc[8];
 #pragma unroll
-        for (int src = 0; src < kMaxTpRanks; ++src) {
-          if (src < nranks) {
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x[src]);
+        for (int u = 0; u < U; ++u) {
+          const int v = v0 + u * 128;
+          if (v >= nvec) continue;
+          float acc[8];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const float2 f = __bfloat1622float2(h[k]);
-              acc[2 * k] = src == 0 ? f.x : acc[2 * k] + f.x;
-              acc[2 * k + 1] = src == 0 ? f.y : acc[2 * k + 1] + f.y;
+          for (int src = 0; src < kMaxTpRanks; ++src) {
+            if (src < nranks) {
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x[u][src]);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const float2 f = __bfloat1622float2(h[k]);
+                acc[2 * k] = src == 0 ? f.x : acc[2 * k] + f.x;
+                acc[2 * k + 1] = src == 0 ? f.y : acc[2 * k + 1] + f.y;
+              }
             }
           }
-        }
-        uint4 y;
-        __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&y);
+          uint4 y;
+          __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&y);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
-        *reinterpret_cast<uint4*>(out + static_cast<size_t>(rr) * ldo + cc) = y;
+          for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+          const int rr = row0 + v / vec_per_row;
+          const int cc = col0 + (v % vec_per_row) * 8;
+          *reinterpret_cast<uint4*>(out + static_cast<size_t>(rr) * ldo + cc) = y;
+        }
       }
-      epilogue_warps_sync();
     }
   }
 

@@ -56,6 +56,8 @@ PROGRAMS = {
     # reference's header-only control plane.
     "hera_master": (["apps/hera_master.cpp", *_HERA_SRCS], False),
     "hera_test": (["apps/hera_test.cpp", *_HERA_SRCS], False),
+    "demo_dual_process": (["apps/demo_dual_process.cpp", "csrc/bootstrap/socket.cc", "csrc/bootstrap/store.cc",
+                           "csrc/core/log.cc", "csrc/core/config.cc", "csrc/net/soft_transport.cc", "csrc/net/factory.cc"], False),
     "app": (["apps/app.cpp"], True),
     "perf_test": (["apps/perf_test.cpp"], True),
 }
@@ -192,6 +194,29 @@ def build_fake_verbs_variant(verbose: bool = False) -> Path:
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed\n{r.stdout}\n{r.stderr}")
+    return out
+
+
+SELFTEST_SOURCES = ["core/log.cc", "core/config.cc", "bootstrap/socket.cc", "bootstrap/store.cc", "bootstrap/fdpass.cc",
+                    "bootstrap/hera.cc", "net/soft_transport.cc", "net/nic_select.cc", "net/ring.cc", "net/factory.cc",
+                    "algo/select.cc", "watchdog/watchdog.cc", "ref/oracle.cc", "testing/hooks.cc", "testing/selftest_main.cc"]
+
+
+def build_sanitized_selftest(kind: str = "address") -> Path:
+    """Host self-test (csrc/testing/selftest_main.cc) compiled with -fsanitize=address,undefined
+    (kind="address") or -fsanitize=thread (kind="thread").  No CUDA code is involved."""
+    flags = {"address": ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"], "thread": ["-fsanitize=thread"]}[kind]
+    BUILD.mkdir(exist_ok=True)
+    out = BUILD / f"host_selftest_{kind}"
+    srcs = [CSRC / s for s in SELFTEST_SOURCES]
+    newest = max([s.stat().st_mtime for s in srcs] + [_newest_header_mtime()])
+    if out.exists() and out.stat().st_mtime >= newest:
+        return out
+    cmd = ["g++", "-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", "-ffp-contract=off", "-pthread", *flags,
+           *_common_includes(), *map(str, srcs), "-o", str(out), "-lrt", "-ldl"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"sanitized build failed\n{r.stderr[-4000:]}")
     return out
 
 

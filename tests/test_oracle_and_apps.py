@@ -99,3 +99,13 @@ def test_app_and_perf_test_programs(free_port):
     assert "Size(B)" in table and "AlgBW(GB/s)" in table and "BusBW(GB/s)" in table
     assert "1048576" in table and "16777216" in table and "(FAIL)" not in table
     assert subprocess.run([_bin("perf_test")], capture_output=True).returncode == 1  # usage
+
+
+def test_dual_process_demo(free_port):
+    env = dict(os.environ)
+    ps = [subprocess.Popen([_bin("demo_dual_process"), role, "127.0.0.1", str(free_port)], env=env, stdout=subprocess.PIPE,
+                           stderr=subprocess.PIPE, text=True) for role in ("server", "client")]
+    outs = [p.communicate(timeout=60) for p in ps]
+    assert all(p.returncode == 0 for p in ps), outs
+    assert 'received: "Hello from the client' in outs[0][0] and 'received: "Hello from the server' in outs[1][0]
+    assert subprocess.run([_bin("demo_dual_process")], capture_output=True).returncode == 1
