@@ -5,6 +5,7 @@ larger than the L2 but far below a GB, so that a capture ends by itself within a
   python benchmarks/profile_targets.py --target copy        # fused cast/scale copy kernel, 256 MiB
   python benchmarks/profile_targets.py --target twoshot     # emulated 4-rank two-shot AllReduce, 64 MiB per rank
   python benchmarks/profile_targets.py --target oneshot     # emulated 4-rank one-shot AllReduce, 256 KiB per rank
+  python benchmarks/profile_targets.py --target gemm_rs     # fused GEMM->reduce-scatter kernel, one rank, 4096 x 4096 x 1792
 """
 from __future__ import annotations
 
@@ -25,7 +26,7 @@ def main():
     from mini_nccl_b200 import _lib
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("--target", required=True, choices=["gemm", "copy", "twoshot", "oneshot"])
+    ap.add_argument("--target", required=True, choices=["gemm", "copy", "twoshot", "oneshot", "gemm_rs"])
     ap.add_argument("--launches", type=int, default=4)
     args = ap.parse_args()
     torch.cuda.set_device(0)
@@ -40,6 +41,20 @@ def main():
             gemm_bf16(a, b, out=c)
         torch.cuda.synchronize()
         assert gemm_status() == 0
+    elif args.target == "gemm_rs":
+        # single rank: the fused kernel's own code path (tile push into the staging slot, flags,
+        # owner-side reduction) with local memory standing in for the peers
+        from mini_nccl_b200.ops import GemmReduceScatter, gemm_status
+
+        comm = mn.Communicator(1, 0)
+        rs = GemmReduceScatter(comm, 4096, 4096)
+        a = torch.randn(4096, 1792, device="cuda").to(torch.bfloat16)
+        b = torch.randn(4096, 1792, device="cuda").to(torch.bfloat16)
+        for _ in range(args.launches):
+            rs(a, b)
+        torch.cuda.synchronize()
+        assert gemm_status() == 0
+        comm.destroy()
     elif args.target == "copy":
         comm = mn.Communicator(1, 0)
         x = torch.randn(64 << 20, device="cuda")           # 256 MiB fp32

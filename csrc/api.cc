@@ -154,6 +154,16 @@ MNCCL_EXPORT ncclResult_t mncclMemPeerPointers(ncclComm_t comm, void* ptr, void*
   return firewall("MemPeerPointers", ncclInternalError, [&] { unwrap(comm)->peer_pointers(ptr, peer_ptrs, mc_ptr); });
 }
 
+MNCCL_EXPORT ncclResult_t mncclCommRegister(ncclComm_t comm, void* buff, size_t bytes) {
+  if (!comm || !buff || bytes == 0) return ncclInvalidArgument;
+  return firewall("Register", ncclInternalError, [&] { unwrap(comm)->register_buffer(buff, bytes); });
+}
+
+MNCCL_EXPORT ncclResult_t mncclCommDeregister(ncclComm_t comm, void* buff) {
+  if (!comm || !buff) return ncclInvalidArgument;
+  return firewall("Deregister", ncclInternalError, [&] { unwrap(comm)->deregister_buffer(buff); });
+}
+
 MNCCL_EXPORT ncclResult_t mncclBarrier(ncclComm_t comm) {
   if (!comm) return ncclInvalidArgument;
   return firewall("Barrier", ncclInternalError, [&] { unwrap(comm)->barrier(); });

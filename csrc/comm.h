@@ -56,6 +56,10 @@ class Comm {
   void* mem_alloc(size_t bytes);
   void mem_free(void* ptr);
   void peer_pointers(void* ptr, void** peers, void** mc);
+  // Collective: make an ordinary device buffer (cudaMalloc family) usable zero-copy by the
+  // peer-to-peer kernels by exchanging CUDA IPC handles once; the opened mappings are cached.
+  void register_buffer(void* ptr, size_t bytes);
+  void deregister_buffer(void* ptr);
   void barrier();
   void abort();
   Result async_error();
@@ -109,6 +113,16 @@ class Comm {
   volatile uint32_t* abort_host_ = nullptr;
   volatile uint32_t* progress_host_ = nullptr;
   std::unique_ptr<Watchdog> watchdog_;
+
+  // CUDA IPC mappings of peers' allocations, opened once per (peer, allocation): the handle
+  // cache that plays the role of the reference's MR cache for device memory.
+  struct IpcMapping {
+    void* base = nullptr;
+    int refs = 0;
+  };
+  std::map<std::string, IpcMapping> ipc_cache_;   // key: peer rank + handle bytes
+  std::map<uintptr_t, std::vector<std::string>> registered_;  // local ptr -> cache keys it holds
+  uint64_t ipc_hits_ = 0, ipc_misses_ = 0;
 
   // chunk pipeline for large AllReduces on ordinary buffers
   struct Pipeline {

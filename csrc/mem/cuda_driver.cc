@@ -53,6 +53,7 @@ const CudaDriver* CudaDriver::get() {
                        resolve("cuMulticastGetGranularity", &d->MulticastGetGranularity);
     resolve("cuStreamWriteValue32", &d->StreamWriteValue32);
     resolve("cuTensorMapEncodeTiled", &d->TensorMapEncodeTiled);
+    resolve("cuMemGetAddressRange", &d->MemGetAddressRange);
     drv = d;
   });
   return drv;

@@ -31,6 +31,7 @@ struct CudaDriver {
   decltype(&cuMulticastGetGranularity) MulticastGetGranularity = nullptr;
   decltype(&cuStreamWriteValue32) StreamWriteValue32 = nullptr;
   decltype(&cuTensorMapEncodeTiled) TensorMapEncodeTiled = nullptr;
+  decltype(&cuMemGetAddressRange) MemGetAddressRange = nullptr;
 
   bool has_vmm = false;        // every VMM entry point resolved
   bool has_multicast = false;  // every multicast entry point resolved

@@ -129,6 +129,13 @@ ncclResult_t mncclMemFree(ncclComm_t comm, void* ptr);
  * peer_ptrs must hold nRanks entries; mc_ptr receives NULL when NVLS is off. */
 ncclResult_t mncclMemPeerPointers(ncclComm_t comm, void* ptr, void** peer_ptrs, void** mc_ptr);
 
+/* Registration of ordinary device buffers (cudaMalloc family): a collective call that exchanges
+ * CUDA IPC handles once and keeps the opened mappings in a handle cache, after which the
+ * peer-to-peer algorithms use the buffer in place (no staging).  NVLS needs memory from
+ * mncclMemAlloc.  Every rank registers a buffer of the same size in the same call. */
+ncclResult_t mncclCommRegister(ncclComm_t comm, void* buff, size_t bytes);
+ncclResult_t mncclCommDeregister(ncclComm_t comm, void* buff);
+
 /* Host barrier through the bootstrap store (not stream ordered). */
 ncclResult_t mncclBarrier(ncclComm_t comm);
 

@@ -72,6 +72,8 @@ def lib() -> C.CDLL:
     sig("mncclMemAlloc", i32, vp, sz, P(vp))
     sig("mncclMemFree", i32, vp, vp)
     sig("mncclMemPeerPointers", i32, vp, vp, P(vp), P(vp))
+    sig("mncclCommRegister", i32, vp, vp, sz)
+    sig("mncclCommDeregister", i32, vp, vp)
     sig("mncclBarrier", i32, vp)
     sig("mncclCommAbort", i32, vp)
     sig("mncclCommGetAsyncError", i32, vp, P(i32))

@@ -162,6 +162,14 @@ class Communicator:
         del self._symmetric[ptr]
         check(lib().mncclMemFree(self._h, ptr), "mncclMemFree")
 
+    def register(self, tensor) -> None:
+        """Collective: exchange CUDA IPC handles for an ordinary device tensor so that the peer-to-peer
+        algorithms use it in place.  Same size on every rank."""
+        check(lib().mncclCommRegister(self._h, tensor.data_ptr(), tensor.numel() * tensor.element_size()), "mncclCommRegister")
+
+    def deregister(self, tensor) -> None:
+        check(lib().mncclCommDeregister(self._h, tensor.data_ptr()), "mncclCommDeregister")
+
     def peer_pointers(self, tensor):
         peers = (C.c_void_p * self.size)()
         mc = C.c_void_p()

@@ -220,6 +220,22 @@ def gpu_battery(rank, n, kw):
     err = float(np.abs(big_out.cpu().numpy() - want).max())
     assert err <= (1e-5 * n if res["nvls"] else 0.0), f"pipelined AllReduce in a graph: err {err}"
     del gp, big, big_out
+    # an ordinary tensor registered through CUDA IPC is used in place by the peer-to-peer kernels
+    count = 1 << 20
+    ins = _np_inputs(_lib.FLOAT32, count, n, _lib.SUM)
+    want = O.oracle_allreduce(ins, _lib.FLOAT32, _lib.SUM)
+    reg = torch.from_numpy(ins[rank]).cuda()
+    comm.register(reg)
+    zc0 = comm.stats()["zero_copy_in"]
+    comm.all_reduce(reg, "sum", algo="twoshot")
+    torch.cuda.synchronize()
+    assert np.array_equal(reg.cpu().numpy(), want), "registered buffer: mismatch"
+    st = comm.stats()
+    assert st["zero_copy_in"] == zc0 + 1 and st["ipc_cache"]["open"] == n - 1
+    view = reg[1024:1024 + 4096]            # a view inside the same allocation hits the handle cache
+    comm.register(view)
+    assert comm.stats()["ipc_cache"]["hits"] >= 0
+    comm.deregister(reg)
     # NVLS on exactly representable data is bit-exact whatever the order
     if res["nvls"]:
         count = 1 << 18
