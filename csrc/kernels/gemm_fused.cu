@@ -71,6 +71,7 @@ struct RsEpilogue {
   uint32_t* flags[kMaxTpRanks];      // every rank's flags:   [nranks][tiles_m_local * tiles_n]
   __nv_bfloat16* out;                // [rows_per_rank, N] on this rank
   int ldo;
+  int bn;                            // tile width of this launch (256 or 192)
 
   __device__ __forceinline__ size_t slot_elems(const GemmArgs& g) const {
     return static_cast<size_t>(rows_per_rank) * g.N;
@@ -119,7 +120,7 @@ struct RsEpilogue {
   __device__ __forceinline__ void tile_done(const GemmArgs& g, uint32_t epoch, int tm, int tn, int q, int lane) const {
     epilogue_warps_sync();  // every store of the tile precedes the flag
     if (q == 0 && lane == 0) {
-      const int tiles_n = (g.N + kBN - 1) / kBN;
+      const int tiles_n = (g.N + bn - 1) / bn;
       const int tiles_m_local = rows_per_rank / kBM;
       const int owner = (tm * kBM) / rows_per_rank;
       const int ltm = tm - owner * tiles_m_local;
@@ -130,7 +131,7 @@ struct RsEpilogue {
   // Reduction of the rows this rank owns, by the epilogue warps of every CTA.
   __device__ __forceinline__ void after_tiles(const GemmArgs& g, uint32_t epoch, int cta, int n_cta, int q, int lane,
                                               volatile uint32_t* abort_flag) const {
-    const int tiles_n = (g.N + kBN - 1) / kBN;
+    const int tiles_n = (g.N + bn - 1) / bn;
     const int tiles_m_local = rows_per_rank / kBM;
     constexpr int kParts = 8, kRows = kBM / kParts;   // an item: 16 rows x 256 columns of one tile
     const int items = tiles_m_local * tiles_n * kParts;
@@ -151,8 +152,8 @@ struct RsEpilogue {
         last_tile = tile;
       }
       const int row0 = ltm * kBM + part * kRows;
-      const int col0 = tn * kBN;
-      const int ncols = min(kBN, g.N - col0);
+      const int col0 = tn * bn;
+      const int ncols = min(bn, g.N - col0);
       const int vec_per_row = ncols / 8;  // 8 bf16 = 16 bytes (N is a multiple of 8)
       const int nvec = kRows * vec_per_row;
       constexpr int U = 2;  // vectors per thread per pass: U * nranks loads in flight (the pass is latency-bound)
@@ -316,7 +317,7 @@ MNCCL_EXPORT size_t mncclGemmRsStageBytes(int M, int N, int /*nranks*/) {
   return size_t(2) * M * N * 2;  // two halves x nranks slots x (M / nranks) rows x N bf16
 }
 MNCCL_EXPORT size_t mncclGemmRsFlagWords(int M, int N, int nranks) {
-  return size_t(nranks) * (M / nranks / kBM) * ((N + kBN - 1) / kBN);
+  return size_t(nranks) * (M / nranks / kBM) * ((N + 191) / 192);  // sized for the narrowest tile
 }
 MNCCL_EXPORT size_t mncclAgGemmReadyWords(int M) { return size_t(M) / kBM; }
 MNCCL_EXPORT size_t mncclAgGemmBarWords(int nranks, int n_comm) { return size_t(nranks) * n_comm; }
@@ -334,7 +335,8 @@ MNCCL_EXPORT int mncclGemmReduceScatterBf16(const void* A, const void* B, void* 
   if (ldo == 0) ldo = N;
   CUtensorMap ta, tb;
   std::string why;
-  if (!make_tensor_map_bf16(&ta, A, M, K, lda, kBM, kBK, &why) || !make_tensor_map_bf16(&tb, B, N, K, ldb, kBN, kBK, &why)) {
+  const int bn = pick_tile_n(M, N, sm_count(), false);
+  if (!make_tensor_map_bf16(&ta, A, M, K, lda, kBM, kBK, &why) || !make_tensor_map_bf16(&tb, B, N, K, ldb, bn, kBK, &why)) {
     fprintf(stderr, "[Mini-NCCL] GEMM->reduce-scatter: %s\n", why.c_str());
     return -3;
   }
@@ -344,6 +346,7 @@ MNCCL_EXPORT int mncclGemmReduceScatterBf16(const void* A, const void* B, void* 
   epi.rows_per_rank = M / nranks;
   epi.out = static_cast<__nv_bfloat16*>(out);
   epi.ldo = ldo;
+  epi.bn = bn;
   for (int r = 0; r < nranks; ++r) {
     epi.stage[r] = static_cast<char*>(stage_peers[r]);
     epi.flags[r] = static_cast<uint32_t*>(flag_peers[r]);
@@ -359,9 +362,9 @@ MNCCL_EXPORT int mncclGemmReduceScatterBf16(const void* A, const void* B, void* 
   g.m_tile_rotate = ((rank + 1) % nranks) * tiles_m_local;  // next rank's rows first, own rows last
   g.epoch_ptr = state;
   g.ticket_ptr = state + 1;
-  const int tiles = (M / kBM) * ((N + kBN - 1) / kBN);
+  const int tiles = (M / kBM) * ((N + bn - 1) / bn);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  cudaError_t e = launch(ta, tb, g, epi, grid, stream);
+  cudaError_t e = launch(ta, tb, g, epi, grid, stream, bn);
   return e == cudaSuccess ? 0 : static_cast<int>(e) + 1000;
 }
 
@@ -386,13 +389,14 @@ MNCCL_EXPORT int mncclAllGatherGemmBf16(void* const* xg_peers, const void* B, vo
   CUtensorMap ta, tb;
   std::string why;
   // The A operand is this rank's own gather buffer: TMA only ever reads local memory.
+  const int bn = pick_tile_n(M, N, sm_count() - (nranks > 1 ? 16 : 0), true);
   if (!make_tensor_map_bf16(&ta, xg_peers[rank], M, K, lda, kBM, kBK, &why) ||
-      !make_tensor_map_bf16(&tb, B, N, K, ldb, kBN, kBK, &why)) {
+      !make_tensor_map_bf16(&tb, B, N, K, ldb, bn, kBK, &why)) {
     fprintf(stderr, "[Mini-NCCL] all-gather->GEMM: %s\n", why.c_str());
     return -3;
   }
   const int sms = sm_count();
-  const int all_tiles = (M / kBM) * ((N + kBN - 1) / kBN);
+  const int all_tiles = (M / kBM) * ((N + bn - 1) / bn);
   int n_comm = 0;
   if (nranks > 1) {
     if (n_comm_ctas > 0) {
@@ -438,13 +442,13 @@ MNCCL_EXPORT int mncclAllGatherGemmBf16(void* const* xg_peers, const void* B, vo
     g.a_local_first = rank * tiles_m_local;
     g.a_local_count = tiles_m_local;
   }
-  const int tiles = (M / kBM) * ((N + kBN - 1) / kBN);
+  const int tiles = all_tiles;
   int n_gemm = sms - n_comm;
   if (tiles < n_gemm) n_gemm = tiles;
   g.n_gemm_ctas = n_gemm;
   // Every CTA must be resident at once (communication CTAs wait for peers while GEMM CTAs
   // wait for data): the grid never exceeds one CTA per SM.
-  cudaError_t e = launch(ta, tb, g, epi, n_gemm + n_comm, stream);
+  cudaError_t e = launch(ta, tb, g, epi, n_gemm + n_comm, stream, bn);
   return e == cudaSuccess ? 0 : static_cast<int>(e) + 1000;
 }
 

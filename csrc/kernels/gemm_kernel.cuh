@@ -43,7 +43,7 @@ struct __align__(8) SharedCtl {
   volatile uint32_t abort;
 };
 
-template <typename Epilogue>
+template <typename Epilogue, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const __grid_constant__ GemmArgs g, const __grid_constant__ Epilogue epi) {
@@ -77,7 +77,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     return;
   }
   const int tiles_m = (g.M + kBM - 1) / kBM;
-  const int tiles_n = (g.N + kBN - 1) / kBN;
+  static_assert(BN % 32 == 0 && BN >= 64 && BN <= kBN, "tile width: a multiple of 32 up to 256");
+  const int tiles_n = (g.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (g.K + kBK - 1) / kBK;
 
@@ -146,10 +147,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           const uint32_t ph = (it / kStages) & 1u;
           if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1u, &ctl->abort, budget)) { ok = false; break; }
           const uint32_t full = smem_u32(&ctl->full[s]);
-          mbar_arrive_expect_tx(full, kStageBytes);
+          mbar_arrive_expect_tx(full, kTileABytes + BN * kBK * 2);
           const uint32_t sa = base + s * kStageBytes;
           tma_load_2d(sa, &tma_a, full, kb * kBK, tm * kBM);
-          tma_load_2d(sa + kTileABytes, &tma_b, full, kb * kBK, tn * kBN);
+          tma_load_2d(sa + kTileABytes, &tma_b, full, kb * kBK, tn * BN);
         }
       }
       // Wind-down after a failed wait: let copies that are still in flight land
@@ -165,7 +166,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(kBM, kBN);
+      constexpr uint32_t idesc = make_idesc_bf16(kBM, BN);
       uint32_t it = 0;
       uint32_t local = 0;
       bool ok = true;
@@ -209,11 +210,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const int row = tm * kBM + q * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kBN;
 #pragma unroll 1
-      for (int c = 0; c < kBN / 32; ++c) {
+      for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
-        epi.store(g, epoch, row, tn * kBN + c * 32, r, c, epi_smem + (warp - 2) * kEpiWarpBytes, lane);
+        epi.store(g, epoch, row, tn * BN + c * 32, r, c, epi_smem + (warp - 2) * kEpiWarpBytes, lane);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -235,10 +236,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   }
 }
 
-template <typename Epilogue>
-inline cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const Epilogue& epi, int grid,
-                   cudaStream_t stream) {
-  auto kernel = gemm_bf16_kernel<Epilogue>;
+template <typename Epilogue, int BN>
+inline cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const Epilogue& epi, int grid,
+                             cudaStream_t stream) {
+  auto kernel = gemm_bf16_kernel<Epilogue, BN>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
@@ -249,6 +250,17 @@ inline cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const Ge
   return cudaGetLastError();
 }
 
+// `bn` is the tile width the B tensor map was built for: 256, 224 or 192.
+template <typename Epilogue>
+inline cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const Epilogue& epi, int grid,
+                          cudaStream_t stream, int bn = kBN) {
+  switch (bn) {
+    case 256: return launch_bn<Epilogue, 256>(ta, tb, g, epi, grid, stream);
+    case 224: return launch_bn<Epilogue, 224>(ta, tb, g, epi, grid, stream);
+    case 192: return launch_bn<Epilogue, 192>(ta, tb, g, epi, grid, stream);
+  }
+  return cudaErrorInvalidValue;
+}
 
 }  // namespace gemm
 }  // namespace mnccl

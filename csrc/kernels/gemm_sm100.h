@@ -12,7 +12,8 @@ namespace mnccl {
 namespace gemm {
 
 constexpr int kBM = 128;          // tile rows  (UMMA M; TMEM lanes)
-constexpr int kBN = 256;          // tile cols  (UMMA N; TMEM columns per accumulator)
+constexpr int kBN = 256;          // widest tile (UMMA N; TMEM columns per accumulator); 224 and 192 are used
+                                 // when they cut the number of waves (shared memory is laid out for 256)
 constexpr int kBK = 64;           // k-block: 64 bf16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;        // K of one tcgen05.mma for 16-bit types
 constexpr int kStages = 4;
@@ -112,6 +113,10 @@ bool make_tensor_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uin
                           uint32_t box_rows, uint32_t box_cols, std::string* why);
 uint32_t* error_word();
 int sm_count();
+
+// Tile width (256, 224 or 192; `allow_224` false for epilogues that work on pairs of 32-column
+// pieces) that minimises waves x per-tile cost for an M x N problem on `ctas` CTAs.
+int pick_tile_n(int M, int N, int ctas, bool allow_224);
 
 }  // namespace gemm
 }  // namespace mnccl
