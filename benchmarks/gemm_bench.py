@@ -35,6 +35,7 @@ def main():
     import torch
 
     from mini_nccl_b200.ops import gemm_bf16, gemm_status
+    from mini_nccl_b200.ops.gemm import set_pair_mode
 
     peak = 1590.0
     try:
@@ -42,16 +43,27 @@ def main():
     except Exception:
         pass
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    shapes = [(4096, 3584, 4096), (4096, 4096, 1792), (4096, 4096, 512), (8192, 8192, 8192), (1024, 1024, 1024)]
+    shapes = [(4096, 3584, 4096), (4096, 4096, 1792), (4096, 4096, 512), (8192, 8192, 8192), (1024, 1024, 1024),
+              (8192, 4096, 4096), (16384, 8192, 4096), (2048, 2048, 8192), (4096, 14336, 4096)]
+    import ctypes
+    import mini_nccl_b200 as mn
+    L = mn.lib()
+    L.mncclGemmMaxPairs.restype = ctypes.c_int
+    print(json.dumps({"max_resident_cta_pairs": L.mncclGemmMaxPairs()}), flush=True)
     rows = []
     for M, N, K in shapes:
         a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
         b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
         c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        set_pair_mode(0)
+        ms_single = time_op(lambda: gemm_bf16(a, b, out=c), flush=flush)
+        set_pair_mode(1)
+        ms_pair = time_op(lambda: gemm_bf16(a, b, out=c), flush=flush)
+        set_pair_mode(-1)
         ms_ours = time_op(lambda: gemm_bf16(a, b, out=c), flush=flush)
         ms_lib = time_op(lambda: torch.matmul(a, b.t(), out=c), flush=flush)
         fl = 2.0 * M * N * K
-        row = {"M": M, "N": N, "K": K, "ours_us": round(ms_ours * 1e3, 1), "cublas_us": round(ms_lib * 1e3, 1),
+        row = {"M": M, "N": N, "K": K, "ours_us": round(ms_ours * 1e3, 1), "single_cta_us": round(ms_single * 1e3, 1), "cta_pair_us": round(ms_pair * 1e3, 1), "cublas_us": round(ms_lib * 1e3, 1),
                "ours_tflops": round(fl / ms_ours / 1e9, 1), "cublas_tflops": round(fl / ms_lib / 1e9, 1),
                "ours_frac_of_measured_peak": round(fl / ms_ours / 1e9 / peak, 3), "status": gemm_status()}
         rows.append(row)

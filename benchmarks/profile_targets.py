@@ -1,7 +1,8 @@
 """Small single-GPU workloads for `ncu`: one kernel family per target, a few launches, inputs
 larger than the L2 but far below a GB, so that a capture ends by itself within a minute or two.
 
-  python benchmarks/profile_targets.py --target gemm        # tcgen05 GEMM, 4096 x 3584 x 4096
+  python benchmarks/profile_targets.py --target gemm        # tcgen05 GEMM, 4096 x 3584 x 4096, single-CTA tiles
+  python benchmarks/profile_targets.py --target gemm_pair   # the same product on CTA pairs (cta_group::2)
   python benchmarks/profile_targets.py --target copy        # fused cast/scale copy kernel, 256 MiB
   python benchmarks/profile_targets.py --target twoshot     # emulated 4-rank two-shot AllReduce, 64 MiB per rank
   python benchmarks/profile_targets.py --target oneshot     # emulated 4-rank one-shot AllReduce, 256 KiB per rank
@@ -26,13 +27,16 @@ def main():
     from mini_nccl_b200 import _lib
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("--target", required=True, choices=["gemm", "copy", "twoshot", "oneshot", "gemm_rs"])
+    ap.add_argument("--target", required=True, choices=["gemm", "gemm_pair", "copy", "twoshot", "oneshot", "gemm_rs"])
     ap.add_argument("--launches", type=int, default=4)
     args = ap.parse_args()
     torch.cuda.set_device(0)
     lib = mn.lib()
-    if args.target == "gemm":
+    if args.target in ("gemm", "gemm_pair"):
         from mini_nccl_b200.ops import gemm_bf16, gemm_status
+        from mini_nccl_b200.ops.gemm import set_pair_mode
+
+        set_pair_mode(1 if args.target == "gemm_pair" else 0)
 
         a = torch.randn(4096, 4096, device="cuda").to(torch.bfloat16)
         b = torch.randn(3584, 4096, device="cuda").to(torch.bfloat16)

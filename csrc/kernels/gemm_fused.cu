@@ -25,6 +25,7 @@
 // are what "AllReduce fused with the adjacent compute" means for this library.
 #include <cstdio>
 
+#include "kernels/gemm2_kernel.cuh"
 #include "kernels/gemm_kernel.cuh"
 
 namespace mnccl {
@@ -335,8 +336,12 @@ MNCCL_EXPORT int mncclGemmReduceScatterBf16(const void* A, const void* B, void* 
   if (ldo == 0) ldo = N;
   CUtensorMap ta, tb;
   std::string why;
-  const int bn = pick_tile_n(M, N, sm_count(), false);
-  if (!make_tensor_map_bf16(&ta, A, M, K, lda, kBM, kBK, &why) || !make_tensor_map_bf16(&tb, B, N, K, ldb, bn, kBK, &why)) {
+  // CTA pairs need every rank's rows to be whole 256-row tiles (the rasterisation works on pairs of m-tiles)
+  const bool pair = ((M / nranks) % (2 * kBM)) == 0 && want_pair(M, N, sm_count()) &&
+                    2 * max_pairs<RsEpilogue>() >= (sm_count() & ~1);
+  const int bn = pair ? kBN : pick_tile_n(M, N, sm_count(), false);
+  if (!make_tensor_map_bf16(&ta, A, M, K, lda, kBM, kBK, &why) ||
+      !make_tensor_map_bf16(&tb, B, N, K, ldb, pair ? kBN / 2 : bn, kBK, &why)) {
     fprintf(stderr, "[Mini-NCCL] GEMM->reduce-scatter: %s\n", why.c_str());
     return -3;
   }
@@ -363,8 +368,14 @@ MNCCL_EXPORT int mncclGemmReduceScatterBf16(const void* A, const void* B, void* 
   g.epoch_ptr = state;
   g.ticket_ptr = state + 1;
   const int tiles = (M / kBM) * ((N + bn - 1) / bn);
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  cudaError_t e = launch(ta, tb, g, epi, grid, stream, bn);
+  cudaError_t e;
+  if (pair) {
+    const int grid = tiles < (sm_count() & ~1) ? tiles : (sm_count() & ~1);  // tiles is even: M / kBM is
+    e = launch_pair(ta, tb, g, epi, grid, stream);
+  } else {
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    e = launch(ta, tb, g, epi, grid, stream, bn);
+  }
   return e == cudaSuccess ? 0 : static_cast<int>(e) + 1000;
 }
 
@@ -389,13 +400,15 @@ MNCCL_EXPORT int mncclAllGatherGemmBf16(void* const* xg_peers, const void* B, vo
   CUtensorMap ta, tb;
   std::string why;
   // The A operand is this rank's own gather buffer: TMA only ever reads local memory.
-  const int bn = pick_tile_n(M, N, sm_count() - (nranks > 1 ? 16 : 0), true);
+  const bool pair = ((M / nranks) % (2 * kBM)) == 0 && want_pair(M, N, sm_count() - (nranks > 1 ? 16 : 0)) &&
+                    2 * max_pairs<AgEpilogue>() >= (sm_count() & ~1);
+  const int bn = pair ? kBN : pick_tile_n(M, N, sm_count() - (nranks > 1 ? 16 : 0), true);
   if (!make_tensor_map_bf16(&ta, xg_peers[rank], M, K, lda, kBM, kBK, &why) ||
-      !make_tensor_map_bf16(&tb, B, N, K, ldb, bn, kBK, &why)) {
+      !make_tensor_map_bf16(&tb, B, N, K, ldb, pair ? kBN / 2 : bn, kBK, &why)) {
     fprintf(stderr, "[Mini-NCCL] all-gather->GEMM: %s\n", why.c_str());
     return -3;
   }
-  const int sms = sm_count();
+  const int sms = pair ? (sm_count() & ~1) : sm_count();
   const int all_tiles = (M / kBM) * ((N + bn - 1) / bn);
   int n_comm = 0;
   if (nranks > 1) {
@@ -411,6 +424,7 @@ MNCCL_EXPORT int mncclAllGatherGemmBf16(void* const* xg_peers, const void* B, vo
       if (n_comm > 48) n_comm = 48;
     }
     if (n_comm > sms / 2) n_comm = sms / 2;
+    if (pair) n_comm = (n_comm + 1) & ~1;  // communication CTAs come as whole clusters too
   }
   AgEpilogue epi{};
   epi.rank = rank;
@@ -448,7 +462,8 @@ MNCCL_EXPORT int mncclAllGatherGemmBf16(void* const* xg_peers, const void* B, vo
   g.n_gemm_ctas = n_gemm;
   // Every CTA must be resident at once (communication CTAs wait for peers while GEMM CTAs
   // wait for data): the grid never exceeds one CTA per SM.
-  cudaError_t e = launch(ta, tb, g, epi, n_gemm + n_comm, stream, bn);
+  cudaError_t e = pair ? launch_pair(ta, tb, g, epi, n_gemm + n_comm, stream)
+                       : launch(ta, tb, g, epi, n_gemm + n_comm, stream, bn);
   return e == cudaSuccess ? 0 : static_cast<int>(e) + 1000;
 }
 

@@ -19,9 +19,10 @@
 // The reference has no GEMM and no tensor-core code; this exists because the
 // tensor-parallel workload fuses it with the collectives of this library.
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
-#include "kernels/gemm_kernel.cuh"
+#include "kernels/gemm2_kernel.cuh"
 #include "mem/cuda_driver.h"
 
 namespace mnccl {
@@ -32,6 +33,14 @@ namespace gemm {
 namespace {
 
 std::mutex g_mu;
+// -1: automatic, 0: single-CTA kernel, 1: CTA-pair kernel; MINI_NCCL_GEMM_PAIR sets the initial value
+int pair_mode_from_env() {
+  const char* e = getenv("MINI_NCCL_GEMM_PAIR");
+  if (e == nullptr || *e == 0) return -1;
+  const int v = atoi(e);
+  return v < 0 ? -1 : (v > 0 ? 1 : 0);
+}
+int g_use_pair = pair_mode_from_env();
 uint32_t* g_err_dev = nullptr;  // one error word per process and device (device 0..15)
 int g_err_device = -1;
 
@@ -98,6 +107,23 @@ int pick_tile_n(int M, int N, int ctas, bool allow_224) {
   return best;
 }
 
+bool want_pair(int M, int N, int ctas) {
+  if (g_use_pair == 0 || M < 2 * kBM || N < kBN || ctas < 2) return false;
+  if (g_use_pair == 1) return true;
+  // Measured on B200: pairs win by 5-15 % (a third less operand traffic from L2 per FLOP) once
+  // they have enough tiles; with fewer tiles than pairs, or a worse last wave, single tiles win.
+  const long pairs = ctas / 2;
+  const long t2 = static_cast<long>((M + 2 * kBM - 1) / (2 * kBM)) * ((N + kBN - 1) / kBN);
+  const long t1 = static_cast<long>((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
+  if (t2 < pairs) return false;
+  const double fill2 = static_cast<double>(t2) / static_cast<double>(((t2 + pairs - 1) / pairs) * pairs);
+  const double fill1 = static_cast<double>(t1) / static_cast<double>(((t1 + ctas - 1) / ctas) * ctas);
+  return fill2 >= fill1 - 0.04;
+}
+
+int pair_mode() { return g_use_pair; }
+void set_pair_mode(int m) { g_use_pair = m; }
+
 int sm_count() {
   static int sms = 0;
   if (sms == 0) {
@@ -132,11 +158,6 @@ MNCCL_EXPORT int mncclGemmBf16(const void* A, const void* B, void* C, int M, int
   if (lda < K || ldb < K || ldc < N) return -2;
   CUtensorMap ta, tb;
   std::string why;
-  const int bn = pick_tile_n(M, N, sm_count(), true);
-  if (!make_tensor_map_bf16(&ta, A, M, K, lda, kBM, kBK, &why) || !make_tensor_map_bf16(&tb, B, N, K, ldb, bn, kBK, &why)) {
-    fprintf(stderr, "[Mini-NCCL] GEMM: %s\n", why.c_str());
-    return -3;
-  }
   GemmArgs g{};
   g.M = M;
   g.N = N;
@@ -146,12 +167,36 @@ MNCCL_EXPORT int mncclGemmBf16(const void* A, const void* B, void* C, int M, int
   g.err = error_word();
   g.wait_budget_ns = 2000000000ull;
   g.group_m = 8;
-  const int tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  cudaError_t e = out_f32 ? launch(ta, tb, g, StoreEpilogue<true>{}, grid, stream, bn)
-                          : launch(ta, tb, g, StoreEpilogue<false>{}, grid, stream, bn);
+  cudaError_t e;
+  const bool pair = want_pair(M, N, sm_count());
+  if (pair) {
+    // CTA pairs: 256 x 256 tiles, each CTA loads 128 rows of A and 128 rows (half of N) of B
+    if (!make_tensor_map_bf16(&ta, A, M, K, lda, kBM, kBK, &why) || !make_tensor_map_bf16(&tb, B, N, K, ldb, kBN / 2, kBK, &why)) {
+      fprintf(stderr, "[Mini-NCCL] GEMM: %s\n", why.c_str());
+      return -3;
+    }
+    const int tiles2 = ((M + 2 * kBM - 1) / (2 * kBM)) * ((N + kBN - 1) / kBN);
+    int grid = 2 * tiles2;
+    if (grid > (sm_count() & ~1)) grid = sm_count() & ~1;
+    e = out_f32 ? launch_pair(ta, tb, g, StoreEpilogue<true>{}, grid, stream) : launch_pair(ta, tb, g, StoreEpilogue<false>{}, grid, stream);
+  } else {
+    const int bn = pick_tile_n(M, N, sm_count(), true);
+    if (!make_tensor_map_bf16(&ta, A, M, K, lda, kBM, kBK, &why) || !make_tensor_map_bf16(&tb, B, N, K, ldb, bn, kBK, &why)) {
+      fprintf(stderr, "[Mini-NCCL] GEMM: %s\n", why.c_str());
+      return -3;
+    }
+    const int tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    e = out_f32 ? launch(ta, tb, g, StoreEpilogue<true>{}, grid, stream, bn) : launch(ta, tb, g, StoreEpilogue<false>{}, grid, stream, bn);
+  }
   return e == cudaSuccess ? 0 : static_cast<int>(e) + 1000;
 }
+
+// Pairs of CTAs (clusters of 2) of the GEMM kernel that fit the current device at once.
+MNCCL_EXPORT int mncclGemmMaxPairs(void) { return max_pairs<StoreEpilogue<false>>(); }
+
+// Kernel choice for the calls that follow: -1 automatic, 0 single-CTA tiles, 1 CTA pairs (cta_group::2).
+MNCCL_EXPORT void mncclGemmSetPairMode(int mode) { set_pair_mode(mode); }
 
 // Reads and clears the GEMM error word of the current device (0 = no bounded
 // wait ever ran out).  Synchronises the device.

@@ -113,10 +113,16 @@ bool make_tensor_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uin
                           uint32_t box_rows, uint32_t box_cols, std::string* why);
 uint32_t* error_word();
 int sm_count();
+int pair_mode();
+void set_pair_mode(int mode);
 
 // Tile width (256, 224 or 192; `allow_224` false for epilogues that work on pairs of 32-column
 // pieces) that minimises waves x per-tile cost for an M x N problem on `ctas` CTAs.
 int pick_tile_n(int M, int N, int ctas, bool allow_224);
+// Whether the CTA-pair kernel (256 x 256 tiles on two SMs) should compute an M x N product on
+// `ctas` CTAs: never when switched off or when the shape does not divide into pair tiles; in
+// automatic mode when the pair tiles fill the SM pairs about as well as single tiles fill the SMs.
+bool want_pair(int M, int N, int ctas);
 
 }  // namespace gemm
 }  // namespace mnccl

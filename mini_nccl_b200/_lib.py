@@ -93,6 +93,8 @@ def lib() -> C.CDLL:
     if hasattr(L, "mncclGemmBf16"):
         sig("mncclGemmBf16", i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp)
         sig("mncclGemmStatus", i32, P(u32))
+        if hasattr(L, "mncclGemmSetPairMode"):
+            sig("mncclGemmSetPairMode", None, i32)
     if hasattr(L, "mncclGemmReduceScatterBf16"):
         sig("mncclGemmRsStageBytes", sz, i32, i32, i32)
         sig("mncclGemmRsFlagWords", sz, i32, i32, i32)

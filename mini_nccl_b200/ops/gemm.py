@@ -47,3 +47,8 @@ def gemm_status() -> int:
     if rc != 0:
         raise RuntimeError(f"mncclGemmStatus failed with code {rc}")
     return st.value
+
+
+def set_pair_mode(mode: int) -> None:
+    """-1: automatic; 0: single-CTA 128 x 256 tiles; 1: CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles)."""
+    _native().mncclGemmSetPairMode(int(mode))

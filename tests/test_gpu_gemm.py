@@ -21,6 +21,16 @@ def _check(M, N, K, out_dtype=torch.bfloat16, lda_pad=0):
     assert err / scale < tol, f"M={M} N={N} K={K}: max err {err} (scale {scale})"
 
 
+@pytest.fixture(params=[0, 1], ids=["single_cta", "cta_pair"], autouse=True)
+def kernel_choice(request):
+    """Every GEMM test runs on the single-CTA kernel and on the CTA-pair (cta_group::2) kernel."""
+    from mini_nccl_b200.ops.gemm import set_pair_mode
+
+    set_pair_mode(request.param)
+    yield request.param
+    set_pair_mode(-1)
+
+
 def test_gemm_single_tile():
     _check(128, 256, 64)
     _check(128, 256, 256)
