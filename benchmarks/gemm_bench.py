@@ -1,6 +1,6 @@
 """bf16 GEMM throughput: the hand-written tcgen05 kernel against cuBLAS (torch.matmul) on the
 shapes of the tensor-parallel block.  CUDA events, warm-up, L2 flushed between timed calls by
-writing a 256 MB buffer; fractions are of the measured cuBLAS peak in MEASURED_PEAKS.json."""
+writing a 256 MB buffer; the kernels take turns inside each iteration and medians are reported; fractions are of the measured cuBLAS peak in MEASURED_PEAKS.json."""
 from __future__ import annotations
 
 import json
@@ -12,23 +12,27 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 
-def time_op(fn, iters=20, flush=None):
+def time_ops(fns, iters=20, flush=None):
+    """Median device time (ms) of each callable; the callables take turns inside every iteration, so
+    that clock and temperature drift hits all of them alike."""
     import torch
 
-    for _ in range(3):
-        fn()
+    for fn in fns:
+        for _ in range(3):
+            fn()
     torch.cuda.synchronize()
-    total = 0.0
+    samples = [[] for _ in fns]
     for _ in range(iters):
-        if flush is not None:
-            flush.zero_()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        fn()
-        e1.record()
-        torch.cuda.synchronize()
-        total += e0.elapsed_time(e1)
-    return total / iters
+        for i, fn in enumerate(fns):
+            if flush is not None:
+                flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            samples[i].append(e0.elapsed_time(e1))
+    return [sorted(x)[len(x) // 2] for x in samples]
 
 
 def main():
@@ -55,13 +59,13 @@ def main():
         a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
         b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
         c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-        set_pair_mode(0)
-        ms_single = time_op(lambda: gemm_bf16(a, b, out=c), flush=flush)
-        set_pair_mode(1)
-        ms_pair = time_op(lambda: gemm_bf16(a, b, out=c), flush=flush)
+        def run(mode):
+            set_pair_mode(mode)
+            gemm_bf16(a, b, out=c)
+
+        ms_single, ms_pair, ms_ours, ms_lib = time_ops(
+            [lambda: run(0), lambda: run(1), lambda: run(-1), lambda: torch.matmul(a, b.t(), out=c)], flush=flush)
         set_pair_mode(-1)
-        ms_ours = time_op(lambda: gemm_bf16(a, b, out=c), flush=flush)
-        ms_lib = time_op(lambda: torch.matmul(a, b.t(), out=c), flush=flush)
         fl = 2.0 * M * N * K
         row = {"M": M, "N": N, "K": K, "ours_us": round(ms_ours * 1e3, 1), "single_cta_us": round(ms_single * 1e3, 1), "cta_pair_us": round(ms_pair * 1e3, 1), "cublas_us": round(ms_lib * 1e3, 1),
                "ours_tflops": round(fl / ms_ours / 1e9, 1), "cublas_tflops": round(fl / ms_lib / 1e9, 1),

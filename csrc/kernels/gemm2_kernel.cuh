@@ -265,9 +265,11 @@ inline cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, con
   return cudaLaunchKernelEx(&cfg, kernel, ta, tb, g, epi);
 }
 
-// Number of CTA pairs of this kernel the device can hold at once.
+// Number of CTA pairs of this kernel the device can hold at once (asked once per kernel).
 template <typename Epilogue>
 inline int max_pairs() {
+  static int cached = 0;
+  if (cached > 0) return cached;
   auto kernel = gemm2_bf16_kernel<Epilogue>;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * 74);
@@ -286,6 +288,7 @@ inline int max_pairs() {
     (void)cudaGetLastError();
     n = 64;
   }
+  cached = n;
   return n;
 }
 

@@ -250,7 +250,7 @@ inline cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const
   return cudaGetLastError();
 }
 
-// `bn` is the tile width the B tensor map was built for: 256, 224 or 192.
+// `bn` is the tile width the B tensor map was built for: 256, 224, 192 or 128.
 template <typename Epilogue>
 inline cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const Epilogue& epi, int grid,
                           cudaStream_t stream, int bn = kBN) {
@@ -258,6 +258,7 @@ inline cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const Ge
     case 256: return launch_bn<Epilogue, 256>(ta, tb, g, epi, grid, stream);
     case 224: return launch_bn<Epilogue, 224>(ta, tb, g, epi, grid, stream);
     case 192: return launch_bn<Epilogue, 192>(ta, tb, g, epi, grid, stream);
+    case 128: return launch_bn<Epilogue, 128>(ta, tb, g, epi, grid, stream);
   }
   return cudaErrorInvalidValue;
 }

@@ -86,13 +86,13 @@ uint32_t* error_word() {
 }
 
 int pick_tile_n(int M, int N, int ctas, bool allow_224) {
-  const int cand[3] = {256, 224, 192};
+  const int cand[4] = {256, 224, 192, 128};  // 128: small products that leave most SMs without a tile
   int best = 256;
   long best_cost = -1;
   const int tiles_m = (M + kBM - 1) / kBM;
-  for (int i = 0; i < 3; ++i) {
+  for (int i = 0; i < 4; ++i) {
     const int bn = cand[i];
-    if (bn == 224 && !allow_224) continue;
+    if ((bn == 224 || bn == 128) && !allow_224) continue;
     const long tiles = static_cast<long>(tiles_m) * ((N + bn - 1) / bn);
     const long waves = (tiles + ctas - 1) / ctas;
     // Measured on B200 (4096 x 4096 x 1792): a wave of 256-wide tiles takes 13.9 us, of 192-wide
