@@ -24,6 +24,7 @@
 // be replayed.  The reference has neither tensor parallelism nor a GEMM; these kernels
 // are what "AllReduce fused with the adjacent compute" means for this library.
 #include <cstdio>
+#include <cstdlib>
 
 #include "kernels/gemm2_kernel.cuh"
 #include "kernels/gemm_kernel.cuh"
@@ -129,12 +130,23 @@ struct RsEpilogue {
     }
   }
 
-  // Reduction of the rows this rank owns, by the epilogue warps of every CTA.
+  // Reduction of the rows this rank owns, by the epilogue warps of every CTA.  The pass is bound by
+  // load latency, so every thread keeps 32 independent 16-byte loads in flight whatever the number
+  // of ranks: NR sources x U vectors.
   __device__ __forceinline__ void after_tiles(const GemmArgs& g, uint32_t epoch, int cta, int n_cta, int q, int lane,
                                               volatile uint32_t* abort_flag) const {
+    if (nranks <= 1) reduce_owned<1, 16>(g, epoch, cta, n_cta, q, lane, abort_flag);
+    else if (nranks <= 2) reduce_owned<2, 16>(g, epoch, cta, n_cta, q, lane, abort_flag);
+    else if (nranks <= 4) reduce_owned<4, 8>(g, epoch, cta, n_cta, q, lane, abort_flag);
+    else reduce_owned<kMaxTpRanks, 4>(g, epoch, cta, n_cta, q, lane, abort_flag);
+  }
+
+  template <int NR, int U>
+  __device__ __forceinline__ void reduce_owned(const GemmArgs& g, uint32_t epoch, int cta, int n_cta, int q, int lane,
+                                               volatile uint32_t* abort_flag) const {
     const int tiles_n = (g.N + bn - 1) / bn;
     const int tiles_m_local = rows_per_rank / kBM;
-    constexpr int kParts = 8, kRows = kBM / kParts;   // an item: 16 rows x 256 columns of one tile
+    constexpr int kParts = 32 / U, kRows = kBM / kParts;   // an item: 4 * U rows x 256 columns of one tile: one pass of the 128 threads
     const int items = tiles_m_local * tiles_n * kParts;
     const int tid = ((q + 2) & 3) * 32 + lane;        // 0..127 over warps 2,3,4,5 in launch order
     const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(stage[rank]) +
@@ -157,9 +169,8 @@ struct RsEpilogue {
       const int ncols = min(bn, g.N - col0);
       const int vec_per_row = ncols / 8;  // 8 bf16 = 16 bytes (N is a multiple of 8)
       const int nvec = kRows * vec_per_row;
-      constexpr int U = 2;  // vectors per thread per pass: U * nranks loads in flight (the pass is latency-bound)
       for (int v0 = tid; v0 < nvec; v0 += 128 * U) {
-        uint4 x[U][kMaxTpRanks];
+        uint4 x[U][NR];
         size_t off[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -168,7 +179,7 @@ struct RsEpilogue {
           const int cc = col0 + (v % vec_per_row) * 8;
           off[u] = static_cast<size_t>(rr) * g.N + cc;
 #pragma unroll
-          for (int src = 0; src < kMaxTpRanks; ++src)
+          for (int src = 0; src < NR; ++src)
             if (src < nranks && v < nvec) x[u][src] = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(src) * slot_elems(g) + off[u]);
         }
 #pragma unroll
@@ -177,7 +188,7 @@ struct RsEpilogue {
           if (v >= nvec) continue;
           float acc[8];
 #pragma unroll
-          for (int src = 0; src < kMaxTpRanks; ++src) {
+          for (int src = 0; src < NR; ++src) {
             if (src < nranks) {
               const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x[u][src]);
 #pragma unroll
