@@ -377,6 +377,10 @@ Comm::~Comm() {
     }
     pipe_.reset();
   }
+  if (solo_stage_) {
+    cudaFree(solo_stage_);
+    solo_stage_ = nullptr;
+  }
   ring_.reset();
   transport_.reset();
   {
@@ -467,10 +471,24 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
   Plan plan = make_plan(pi, caps_, cfg_);
   if (!plan.valid) fail(Result::InvalidArgument, std::string("no kernel for this request: ") + plan.reason);
   if (!kernel_exists(plan.spec)) fail(Result::InvalidArgument, "no kernel for this type / operator combination");
+  // Pinned host buffers: the copy engines move them (both directions at once over PCIe) in chunks
+  // that overlap the collective, instead of kernels reading and writing host memory word by word.
+  const bool host_in = !in_seg && classify(send, true) == MemKind::PinnedHost;
+  const bool host_out = !out_seg && classify(recv, true) == MemKind::PinnedHost;
+  const bool host_pipe = mode == Mode::AllReduce && (host_in || host_out) && cfg_.host_pipeline_min_bytes != 0 &&
+                         std::max(in_bytes, out_bytes) >= cfg_.host_pipeline_min_bytes;
+  if (host_pipe && size_ == 1) {
+    launch_solo_host(send, send_t, recv, recv_t, count, scale, stream, host_in, host_out);  // one rank: Avg == Sum
+    stats_.calls++;
+    stats_.bytes += in_bytes;
+    stats_.pipelined++;
+    return;
+  }
   if (mode == Mode::AllReduce && size_ > 1 && (plan.copy_in || plan.copy_out) &&
-      (plan.spec.algo == Algo::TwoShot || plan.spec.algo == Algo::Nvls) && cfg_.pipeline_min_bytes != 0 &&
-      count * dtype_size(wire_t) >= cfg_.pipeline_min_bytes) {
-    launch_pipelined(send, send_t, recv, recv_t, wire_t, count, op, scale, forced, stream);
+      (plan.spec.algo == Algo::TwoShot || plan.spec.algo == Algo::Nvls || host_pipe) &&
+      ((cfg_.pipeline_min_bytes != 0 && count * dtype_size(wire_t) >= cfg_.pipeline_min_bytes) || host_pipe)) {
+    launch_pipelined(send, send_t, recv, recv_t, wire_t, count, op, scale, forced, stream, host_pipe && host_in,
+                     host_pipe && host_out);
     stats_.calls++;
     stats_.bytes += in_bytes;
     stats_.pipelined++;
@@ -526,9 +544,9 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
 // Slot reuse is safe across ranks because every collective kernel starts and ends with a
 // cross-rank barrier: a peer touches this rank's half only between those two barriers, and this
 // rank enters the barrier of chunk i+2 only after its own copy-out of chunk i.
-void Comm::launch_pipelined(const void* send, DType send_t, void* recv, DType recv_t, DType wire_t, size_t count,
-                            RedOp op, double scale, Algo forced, cudaStream_t stream) {
-  if (!pipe_) {
+void Comm::ensure_pipeline() {
+  if (pipe_) return;
+  {
     pipe_.reset(new Pipeline());
     RT_CHECK(cudaStreamCreateWithFlags(&pipe_->s_in, cudaStreamNonBlocking), "cudaStreamCreate");
     RT_CHECK(cudaStreamCreateWithFlags(&pipe_->s_out, cudaStreamNonBlocking), "cudaStreamCreate");
@@ -539,12 +557,20 @@ void Comm::launch_pipelined(const void* send, DType send_t, void* recv, DType re
       RT_CHECK(cudaEventCreateWithFlags(&pipe_->ev_out[h], cudaEventDisableTiming), "cudaEventCreate");
     }
   }
+}
+
+void Comm::launch_pipelined(const void* send, DType send_t, void* recv, DType recv_t, DType wire_t, size_t count,
+                            RedOp op, double scale, Algo forced, cudaStream_t stream, bool host_in, bool host_out) {
+  ensure_pipeline();
   const size_t wsz = dtype_size(wire_t), osz = dtype_size(recv_t), isz = dtype_size(send_t);
   const size_t half = (caps_.stage_bytes / 2) & ~size_t(4095);
   // Chunks: a quarter of the message, at least 32 MB (the collective kernel needs size to be
   // efficient: measured 620 GB/s bus bandwidth at 32 MB, 770 at 128 MB on 8 GPUs), at most what
   // one half of the staging holds.
   size_t chunk_bytes = std::max<size_t>(count * wsz / 4, size_t(32) << 20);
+  // Host buffers: PCIe (not NVLink) sets the pace, so chunks are small: the exposed head (first
+  // copy-in) and tail (last collective and copy-out) shrink with them.
+  if (host_in || host_out) chunk_bytes = cfg_.host_chunk_bytes;
   size_t chunk = chunk_bytes / wsz;
   chunk = std::min(chunk, half / std::max(wsz, osz));
   chunk &= ~size_t(4095);
@@ -586,7 +612,10 @@ void Comm::launch_pipelined(const void* send, DType send_t, void* recv, DType re
     char* b_h = dev_.ctrl[rank_] + dev_.off_stage_b + h * half;
     // copy-in (after the collective that last read this half)
     if (i >= 2) RT_CHECK(cudaStreamWaitEvent(pipe_->s_in, pipe_->ev_comm[h], 0), "cudaStreamWaitEvent");
-    local_copy(static_cast<const char*>(send) + off * isz, send_t, a_h, wire_t, n, pipe_->s_in);
+    if (host_in && send_t == wire_t)
+      RT_CHECK(cudaMemcpyAsync(a_h, static_cast<const char*>(send) + off * isz, n * isz, cudaMemcpyHostToDevice, pipe_->s_in), "cudaMemcpyAsync");
+    else
+      local_copy(static_cast<const char*>(send) + off * isz, send_t, a_h, wire_t, n, pipe_->s_in);
     RT_CHECK(cudaEventRecord(pipe_->ev_in[h], pipe_->s_in), "cudaEventRecord");
     // collective on the staging halves, zero-copy (after the copy-out that last read B_h)
     RT_CHECK(cudaStreamWaitEvent(stream, pipe_->ev_in[h], 0), "cudaStreamWaitEvent");
@@ -636,11 +665,88 @@ void Comm::launch_pipelined(const void* send, DType send_t, void* recv, DType re
     stats_.by_algo[static_cast<int>(plan.spec.algo)]++;
     // copy-out
     RT_CHECK(cudaStreamWaitEvent(pipe_->s_out, pipe_->ev_comm[h], 0), "cudaStreamWaitEvent");
-    local_copy(b_h, recv_t, static_cast<char*>(recv) + off * osz, recv_t, n, pipe_->s_out);
+    if (host_out)
+      RT_CHECK(cudaMemcpyAsync(static_cast<char*>(recv) + off * osz, b_h, n * osz, cudaMemcpyDeviceToHost, pipe_->s_out), "cudaMemcpyAsync");
+    else
+      local_copy(b_h, recv_t, static_cast<char*>(recv) + off * osz, recv_t, n, pipe_->s_out);
     RT_CHECK(cudaEventRecord(pipe_->ev_out[h], pipe_->s_out), "cudaEventRecord");
   }
   RT_CHECK(cudaStreamWaitEvent(stream, pipe_->ev_out[0], 0), "cudaStreamWaitEvent");
   if (i >= 2) RT_CHECK(cudaStreamWaitEvent(stream, pipe_->ev_out[1], 0), "cudaStreamWaitEvent");
+}
+
+// One rank, pinned host buffers: out = factor * in with the types converted, as a three-stage
+// pipeline through private device staging: copy engine in, kernel, copy engine out.  Host -> device
+// and device -> host run at the same time (PCIe is full duplex).
+void Comm::launch_solo_host(const void* send, DType send_t, void* recv, DType recv_t, size_t count, double factor,
+                            cudaStream_t stream, bool host_in, bool host_out) {
+  ensure_pipeline();
+  const size_t isz = dtype_size(send_t), osz = dtype_size(recv_t);
+  size_t chunk = cfg_.host_chunk_bytes / std::max(isz, osz);
+  chunk &= ~size_t(4095);
+  if (chunk == 0) chunk = 4096;
+  const size_t half = chunk * std::max(isz, osz);
+  if (solo_stage_ == nullptr || solo_stage_half_ < half) {
+    if (solo_stage_) {
+      RT_CHECK(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+      cudaFree(solo_stage_);
+      solo_stage_ = nullptr;
+    }
+    RT_CHECK(cudaMalloc(reinterpret_cast<void**>(&solo_stage_), 4 * half), "cudaMalloc (host staging)");
+    solo_stage_half_ = half;
+  }
+  LaunchSpec ls;
+  ls.algo = Algo::Local;
+  ls.in = send_t;
+  ls.wire = (send_t == recv_t) ? send_t : DType::Bfloat16;
+  ls.out = recv_t;
+  ls.op = RedOp::Sum;
+  ls.nthreads = 512;
+  if (!kernel_exists(ls)) fail(Result::InvalidArgument, "no kernel for this type combination");
+  // only the side streams that get work are forked (a forked stream must be joined under capture)
+  RT_CHECK(cudaEventRecord(pipe_->ev_start, stream), "cudaEventRecord");
+  if (host_in) RT_CHECK(cudaStreamWaitEvent(pipe_->s_in, pipe_->ev_start, 0), "cudaStreamWaitEvent");
+  if (host_out) RT_CHECK(cudaStreamWaitEvent(pipe_->s_out, pipe_->ev_start, 0), "cudaStreamWaitEvent");
+  size_t i = 0;
+  for (size_t off = 0; off < count; off += chunk, ++i) {
+    const int h = static_cast<int>(i & 1);
+    const size_t n = std::min(chunk, count - off);
+    char* a_h = solo_stage_ + h * half;
+    char* b_h = solo_stage_ + (2 + h) * half;
+    const char* src = static_cast<const char*>(send) + off * isz;
+    char* dst = static_cast<char*>(recv) + off * osz;
+    const void* k_in = src;
+    if (host_in) {
+      if (i >= 2) RT_CHECK(cudaStreamWaitEvent(pipe_->s_in, pipe_->ev_comm[h], 0), "cudaStreamWaitEvent");
+      RT_CHECK(cudaMemcpyAsync(a_h, src, n * isz, cudaMemcpyHostToDevice, pipe_->s_in), "cudaMemcpyAsync");
+      RT_CHECK(cudaEventRecord(pipe_->ev_in[h], pipe_->s_in), "cudaEventRecord");
+      RT_CHECK(cudaStreamWaitEvent(stream, pipe_->ev_in[h], 0), "cudaStreamWaitEvent");
+      k_in = a_h;
+    }
+    if (host_out && i >= 2) RT_CHECK(cudaStreamWaitEvent(stream, pipe_->ev_out[h], 0), "cudaStreamWaitEvent");
+    KParams kp;
+    memset(&kp, 0, sizeof(kp));
+    kp.comm = dev_;
+    kp.args.send = k_in;
+    kp.args.recv = host_out ? static_cast<void*>(b_h) : static_cast<void*>(dst);
+    kp.args.count = n;
+    kp.args.scale_f = static_cast<float>(factor);
+    kp.args.scale_d = factor;
+    const size_t vecs = (n * std::max(isz, osz) + 15) / 16;
+    ls.nblocks = static_cast<int>(std::min<size_t>(std::max<size_t>(vecs / 2048, 1), 96));
+    RT_CHECK(launch_collective(ls, kp, stream), "kernel launch");
+    RT_CHECK(cudaEventRecord(pipe_->ev_comm[h], stream), "cudaEventRecord");
+    if (host_out) {
+      RT_CHECK(cudaStreamWaitEvent(pipe_->s_out, pipe_->ev_comm[h], 0), "cudaStreamWaitEvent");
+      RT_CHECK(cudaMemcpyAsync(dst, b_h, n * osz, cudaMemcpyDeviceToHost, pipe_->s_out), "cudaMemcpyAsync");
+      RT_CHECK(cudaEventRecord(pipe_->ev_out[h], pipe_->s_out), "cudaEventRecord");
+    }
+  }
+  stats_.by_algo[static_cast<int>(Algo::Local)]++;
+  if (host_out) {
+    RT_CHECK(cudaStreamWaitEvent(stream, pipe_->ev_out[0], 0), "cudaStreamWaitEvent");
+    if (i >= 2) RT_CHECK(cudaStreamWaitEvent(stream, pipe_->ev_out[1], 0), "cudaStreamWaitEvent");
+  }
 }
 
 void Comm::wait_blocking(cudaStream_t stream) {

@@ -82,7 +82,10 @@ class Comm {
   void launch(Mode mode, const void* send, DType send_t, void* recv, DType recv_t, DType wire_t, size_t count,
               RedOp op, double scale, Algo forced, cudaStream_t stream);
   void launch_pipelined(const void* send, DType send_t, void* recv, DType recv_t, DType wire_t, size_t count, RedOp op,
-                        double scale, Algo forced, cudaStream_t stream);
+                        double scale, Algo forced, cudaStream_t stream, bool host_in = false, bool host_out = false);
+  void launch_solo_host(const void* send, DType send_t, void* recv, DType recv_t, size_t count, double factor,
+                        cudaStream_t stream, bool host_in, bool host_out);
+  void ensure_pipeline();
   void ring_all_reduce(const void* send, void* recv, size_t count, DType t, RedOp op, cudaStream_t stream);
   // Segment containing [ptr, ptr+bytes) on this rank; offset returned.
   std::shared_ptr<Segment> find_segment(const void* ptr, size_t bytes, size_t* offset);
@@ -130,6 +133,9 @@ class Comm {
     cudaEvent_t ev_start = nullptr, ev_in[2] = {nullptr, nullptr}, ev_comm[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
   };
   std::unique_ptr<Pipeline> pipe_;
+  // single rank with pinned-host buffers: private device staging (two halves per direction)
+  char* solo_stage_ = nullptr;
+  size_t solo_stage_half_ = 0;
 
   // network plane
   std::unique_ptr<OneSidedTransport> transport_;

@@ -93,6 +93,8 @@ Config Config::from_getter(Getter get, void* ctx) {
   r.num("MINI_NCCL_NVLS_MIN_BYTES", c.nvls_min_bytes);
   r.num("MINI_NCCL_STAGING_BYTES", c.staging_bytes);
   r.num("MINI_NCCL_PIPELINE_MIN_BYTES", c.pipeline_min_bytes);
+  r.num("MINI_NCCL_HOST_PIPELINE_MIN_BYTES", c.host_pipeline_min_bytes);
+  r.num("MINI_NCCL_HOST_CHUNK_BYTES", c.host_chunk_bytes);
   r.num("MINI_NCCL_MAX_BLOCKS", c.max_blocks);
   r.num("MINI_NCCL_UNROLL", c.unroll);
   r.boolean("MINI_NCCL_NUMA_BIND", c.numa_bind);
@@ -107,6 +109,7 @@ Config Config::from_getter(Getter get, void* ctx) {
   if (c.watchdog_timeout_ms <= 0) c.watchdog_timeout_ms = 1;
   if (c.socket_timeout_ms <= 0) c.socket_timeout_ms = 1;
   if (c.connect_retries <= 0) c.connect_retries = 1;
+  if (c.host_chunk_bytes < (64u << 10)) c.host_chunk_bytes = 64u << 10;
   if (c.staging_bytes < (1u << 20)) c.staging_bytes = 1u << 20;
   c.staging_bytes = (c.staging_bytes + 4095) & ~size_t(4095);
   return c;

@@ -289,6 +289,26 @@ def gpu_battery(rank, n, kw):
         assert float(np.abs(hy.numpy() - want).max()) <= 1e-5 * n
     else:
         assert np.array_equal(hy.numpy(), want), "pinned host buffers mismatch"
+    # larger pinned buffers are moved by the copy engines in chunks that overlap the collective:
+    # several chunks, a count that is no multiple of anything, in place
+    cnt = (6 << 20) + 1000
+    big = _np_inputs(_lib.FLOAT32, cnt, n, _lib.SUM)
+    hb = torch.from_numpy(big[rank].copy()).pin_memory()
+    before = comm.stats()["pipelined_calls"]
+    comm.all_reduce(hb, "sum")
+    torch.cuda.synchronize()
+    want = O.oracle_allreduce(big, _lib.FLOAT32, _lib.SUM)
+    if res["nvls"]:
+        assert float(np.abs(hb.numpy() - want).max()) <= 1e-5 * n, "pinned host pipeline mismatch"
+    else:
+        assert np.array_equal(hb.numpy(), want), "pinned host pipeline mismatch"
+    assert comm.stats()["pipelined_calls"] == before + 1, "large pinned buffers must take the copy-engine pipeline"
+    # device in, pinned host out, fused average
+    dv = torch.from_numpy(big[rank].copy()).cuda()
+    ho = torch.zeros(cnt).pin_memory()
+    comm.all_reduce(dv, "avg", out=ho)
+    torch.cuda.synchronize()
+    assert float(np.abs(ho.numpy() - want / n).max()) <= 2e-6 * n, "device -> pinned host average mismatch"
     # CUDA graph: capture 50 AllReduces of 64 KB bf16, replay 20 times
     g_in = comm.empty(32768, torch.bfloat16)
     ones = torch.ones(32768, dtype=torch.bfloat16, device="cuda")
