@@ -54,4 +54,30 @@ def run() -> None:
                 assert np.array_equal(b.cpu().numpy(), want), f"algorithm {algo} mismatch"
     finally:
         lib.mncclEmuDestroy(world)
-    print(f"smoke ok: loss={loss.item():.4f} buckets={len(ddp.buckets)} kernels=local,ll,oneshot,twoshot")
+    # tcgen05 GEMM on single-CTA tiles and on CTA pairs, and the two fused tensor-parallel kernels
+    # with one rank, against an fp32 matmul.
+    from mini_nccl_b200.ops import gemm_bf16, gemm_status
+    from mini_nccl_b200.ops.fused import AllGatherGemm, GemmReduceScatter
+    from mini_nccl_b200.ops.gemm import set_pair_mode
+
+    a = (torch.randn(512, 256, device="cuda") * 0.5).to(torch.bfloat16)
+    b = (torch.randn(512, 256, device="cuda") * 0.5).to(torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    for mode in (0, 1):
+        set_pair_mode(mode)
+        c = gemm_bf16(a, b)
+        torch.cuda.synchronize()
+        assert (c.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item(), f"GEMM (pair mode {mode}) mismatch"
+    set_pair_mode(-1)
+    solo = mn.Communicator(1, 0)
+    rs = GemmReduceScatter(solo, 512, 512)
+    out = rs(a, b)
+    ag = AllGatherGemm(solo, 512, 256)
+    ag.local_shard.copy_(a)
+    c2 = ag(b)
+    torch.cuda.synchronize()
+    for got, name in ((out, "GEMM->reduce-scatter"), (c2, "all-gather->GEMM")):
+        assert (got.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item(), name + " mismatch"
+    assert gemm_status() == 0
+    solo.destroy()
+    print(f"smoke ok: loss={loss.item():.4f} buckets={len(ddp.buckets)} kernels=local,ll,oneshot,twoshot,gemm,gemm_pair,gemm_rs,ag_gemm")
