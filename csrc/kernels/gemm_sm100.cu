@@ -111,11 +111,11 @@ bool want_pair(int M, int N, int ctas) {
   if (g_use_pair == 0 || M < 2 * kBM || N < kBN || ctas < 2) return false;
   if (g_use_pair == 1) return true;
   // Measured on B200: pairs win by 5-15 % (a third less operand traffic from L2 per FLOP) once
-  // they have enough tiles; with fewer tiles than pairs, or a worse last wave, single tiles win.
+  // they have enough tiles; with far fewer tiles than pairs, or a worse last wave, single tiles win.
   const long pairs = ctas / 2;
   const long t2 = static_cast<long>((M + 2 * kBM - 1) / (2 * kBM)) * ((N + kBN - 1) / kBN);
   const long t1 = static_cast<long>((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
-  if (t2 < pairs) return false;
+  if (2 * t2 < pairs) return false;  // small products: narrower single-CTA tiles reach more SMs
   const double fill2 = static_cast<double>(t2) / static_cast<double>(((t2 + pairs - 1) / pairs) * pairs);
   const double fill1 = static_cast<double>(t1) / static_cast<double>(((t1 + ctas - 1) / ctas) * ctas);
   return fill2 >= fill1 - 0.04;

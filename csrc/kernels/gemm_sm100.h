@@ -73,21 +73,42 @@ template <bool OUT_F32>
 struct StoreEpilogue {
   // Thread holds row `row`, columns [col, col+32) as fp32 bit patterns.
   // `chunk` counts the 32-column pieces of the tile; `warp_smem` is kEpiWarpBytes of scratch.
+  // A lane's own 32 columns are 64 (bf16) or 128 (fp32) bytes of ONE row, so storing straight from
+  // registers makes every instruction touch 32 different lines with 16 bytes each.  Where alignment
+  // allows (decided for the whole warp), the piece goes through shared memory instead and leaves as
+  // whole rows: 4 (bf16) or 8 (fp32) lanes per row, 16 bytes each.
   __device__ __forceinline__ void store(const GemmArgs& g, uint32_t /*epoch*/, int row, int col, const uint32_t (&r)[32],
-                                        int /*chunk*/, uint8_t* /*warp_smem*/, int /*lane*/) const {
-    if (row >= g.M || col >= g.N) return;
-    if constexpr (OUT_F32) {
-      float* dst = static_cast<float*>(g.c) + static_cast<size_t>(row) * g.ldc + col;
-      if (col + 32 <= g.N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                                        int /*chunk*/, uint8_t* warp_smem, int lane) const {
+    if (col >= g.N) return;  // the same for the whole warp
+    constexpr int kElem = OUT_F32 ? 4 : 2;
+    const bool whole_rows = col + 32 <= g.N && ((static_cast<size_t>(g.ldc) * kElem) & 15u) == 0 &&
+                            (reinterpret_cast<uintptr_t>(g.c) & 15u) == 0;
+    if (whole_rows) {
+      const int row_base = row - lane;
+      if constexpr (OUT_F32) {
+        // 128 bytes per row; two passes of 16 rows through the 32 x 144-byte scratch
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          reinterpret_cast<uint4*>(dst)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        for (int half = 0; half < 2; ++half) {
+          if ((lane >> 4) == half) {
+            uint8_t* mine = warp_smem + (lane & 15) * kEpiRowBytes;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<uint4*>(mine + j * 16) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+          }
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int rr = it * 4 + (lane >> 3), seg = lane & 7;
+            const int grow = row_base + half * 16 + rr;
+            if (grow < g.M) {
+              const uint4 v = *reinterpret_cast<const uint4*>(warp_smem + rr * kEpiRowBytes + seg * 16);
+              *reinterpret_cast<uint4*>(static_cast<float*>(g.c) + static_cast<size_t>(grow) * g.ldc + col + seg * 4) = v;
+            }
+          }
+          __syncwarp();
+        }
       } else {
-        for (int j = 0; j < 32 && col + j < g.N; ++j) dst[j] = __uint_as_float(r[j]);
-      }
-    } else {
-      __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.c) + static_cast<size_t>(row) * g.ldc + col;
-      if (col + 32 <= g.N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+        uint8_t* mine = warp_smem + lane * kEpiRowBytes;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           uint4 v;
@@ -97,11 +118,29 @@ struct StoreEpilogue {
             __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * k]), __uint_as_float(r[8 * j + 2 * k + 1]));
             w[k] = *reinterpret_cast<uint32_t*>(&p);
           }
-          reinterpret_cast<uint4*>(dst)[j] = v;
+          *reinterpret_cast<uint4*>(mine + j * 16) = v;
         }
-      } else {
-        for (int j = 0; j < 32 && col + j < g.N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+        __syncwarp();
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int rr = it * 8 + (lane >> 2), seg = lane & 3;
+          const int grow = row_base + rr;
+          if (grow < g.M) {
+            const uint4 v = *reinterpret_cast<const uint4*>(warp_smem + rr * kEpiRowBytes + seg * 16);
+            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(g.c) + static_cast<size_t>(grow) * g.ldc + col + seg * 8) = v;
+          }
+        }
+        __syncwarp();
       }
+      return;
+    }
+    if (row >= g.M) return;
+    if constexpr (OUT_F32) {
+      float* dst = static_cast<float*>(g.c) + static_cast<size_t>(row) * g.ldc + col;
+      for (int j = 0; j < 32 && col + j < g.N; ++j) dst[j] = __uint_as_float(r[j]);
+    } else {
+      __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.c) + static_cast<size_t>(row) * g.ldc + col;
+      for (int j = 0; j < 32 && col + j < g.N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
     }
   }
   __device__ __forceinline__ void tile_done(const GemmArgs&, uint32_t, int, int, int, int) const {}
