@@ -22,9 +22,12 @@
 namespace mnccl {
 namespace gemm {
 
-constexpr int k2Stages = 6;
+constexpr int k2Stages = 6;  // deepest ring; an epilogue may ask for fewer (Epilogue::kPairStages)
 constexpr int k2StageBytes = kTileABytes + kBM * kBK * 2;  // A 128 x 64 + this CTA's half of B 128 x 64: 32 KB
-constexpr int k2SmemBytes = k2Stages * k2StageBytes + 1024 + kCtlBytes + kEpilogueWarps * kEpiWarpBytes;
+template <typename Epilogue>
+constexpr int pair_smem_bytes() {
+  return Epilogue::kPairStages * k2StageBytes + 1024 + kCtlBytes + kEpilogueWarps * Epilogue::kWarpSmemBytes;
+}
 
 struct __align__(8) SharedCtl2 {
   uint64_t full[k2Stages];    // used in the leader: 2 arrivals (one per producer) + 64 KB of bytes
@@ -44,9 +47,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw);
-  SharedCtl2* ctl = reinterpret_cast<SharedCtl2*>(smem + k2Stages * k2StageBytes);
+  constexpr int NS = Epilogue::kPairStages;
+  constexpr int kWarpSmem = Epilogue::kWarpSmemBytes;
+  static_assert(NS >= 2 && NS <= k2Stages, "ring depth");
+  SharedCtl2* ctl = reinterpret_cast<SharedCtl2*>(smem + NS * k2StageBytes);
   static_assert(sizeof(SharedCtl2) <= kCtlBytes, "control block outgrew its slot");
-  uint8_t* epi_smem = smem + k2Stages * k2StageBytes + kCtlBytes;
+  uint8_t* epi_smem = smem + NS * k2StageBytes + kCtlBytes;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -77,7 +83,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   const int num_kb = (g.K + kBK - 1) / kBK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < k2Stages; ++s) {
+    for (int s = 0; s < NS; ++s) {
       mbar_init(smem_u32(&ctl->full[s]), 2);
       mbar_init(smem_u32(&ctl->empty[s]), 1);
     }
@@ -143,8 +149,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           if (waited) asm volatile("fence.proxy.async.global;" ::: "memory");
         }
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const uint32_t s = it % k2Stages;
-          const uint32_t ph = (it / k2Stages) & 1u;
+          const uint32_t s = it % NS;
+          const uint32_t ph = (it / NS) & 1u;
           if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1u, &ctl->abort, budget)) { ok = false; break; }
           const uint32_t leader_full = map_to_cta(smem_u32(&ctl->full[s]), 0);
           mbar_arrive_expect_tx_cluster(leader_full, k2StageBytes);
@@ -167,8 +173,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         tc_fence_after_sync();
         const uint32_t d = tmem_base + buf * kBN;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const uint32_t s = it % k2Stages;
-          const uint32_t ph = (it / k2Stages) & 1u;
+          const uint32_t s = it % NS;
+          const uint32_t ph = (it / NS) & 1u;
           if (!mbar_wait(smem_u32(&ctl->full[s]), ph, &ctl->abort, budget)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = base + s * k2StageBytes;
@@ -186,6 +192,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   } else {
     // ------------------------------------------------------------ epilogue (both CTAs, own rows)
     const int q = warp & 3;
+    uint8_t* warp_smem = epi_smem + (warp - 2) * kWarpSmem;
+    epi.warp_begin(warp_smem, lane);
     uint32_t local = 0;
     bool ok = true;
     for (int t = pair; t < num_tiles && ok; t += n_pairs, ++local) {
@@ -203,15 +211,15 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
-        epi.store(g, epoch, row, tn * kBN + c * 32, r, c, epi_smem + (warp - 2) * kEpiWarpBytes, lane);
+        epi.store(g, epoch, row, tn * kBN + c * 32, r, c, warp_smem, lane);
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->tmem_empty[buf]), 0));
-      if (tm * kBM < g.M) epi.tile_done(g, epoch, tm, tn, q, lane);
+      if (tm * kBM < g.M) epi.tile_done(g, epoch, tm, tn, q, lane, warp_smem);
     }
     // the single-CTA numbering of CTAs for the epilogues' follow-up pass
-    epi.after_tiles(g, epoch, static_cast<int>(blockIdx.x), n_gemm, q, lane, &ctl->abort);
+    epi.after_tiles(g, epoch, static_cast<int>(blockIdx.x), n_gemm, q, lane, &ctl->abort, warp_smem);
   }
 
   tc_fence_before_sync();
@@ -239,7 +247,7 @@ inline cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, con
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = k2SmemBytes;
+  cfg.dynamicSmemBytes = pair_smem_bytes<Epilogue>();
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -249,7 +257,7 @@ inline cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, con
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, k2SmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes<Epilogue>());
     if (e != cudaSuccess) return e;
     cfg.gridDim = dim3(2 * 74);
     e = cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg);
@@ -274,7 +282,7 @@ inline int max_pairs() {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * 74);
   cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = k2SmemBytes;
+  cfg.dynamicSmemBytes = pair_smem_bytes<Epilogue>();
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
@@ -283,7 +291,7 @@ inline int max_pairs() {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, k2SmemBytes) != cudaSuccess ||
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes<Epilogue>()) != cudaSuccess ||
       cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
     (void)cudaGetLastError();
     n = 64;

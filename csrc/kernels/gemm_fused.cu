@@ -67,6 +67,9 @@ __device__ __forceinline__ bool wait_flag_sys(const uint32_t* p, uint32_t target
 // ------------------------------------------------------------------ GEMM -> reduce-scatter
 
 struct RsEpilogue {
+  static constexpr int kWarpSmemBytes = kEpiWarpBytes;
+  static constexpr int kSingleStages = kStages;
+  static constexpr int kPairStages = 6;
   int rank, nranks;
   int rows_per_rank;                 // M / nranks, a multiple of 128
   char* stage[kMaxTpRanks];          // every rank's staging: [2][nranks][rows_per_rank][N] bf16
@@ -119,7 +122,10 @@ struct RsEpilogue {
   }
 
   // All four epilogue warps call this after the last store of a tile.
-  __device__ __forceinline__ void tile_done(const GemmArgs& g, uint32_t epoch, int tm, int tn, int q, int lane) const {
+  __device__ __forceinline__ void warp_begin(uint8_t*, int) const {}
+
+  __device__ __forceinline__ void tile_done(const GemmArgs& g, uint32_t epoch, int tm, int tn, int q, int lane,
+                                            uint8_t* /*warp_smem*/) const {
     epilogue_warps_sync();  // every store of the tile precedes the flag
     if (q == 0 && lane == 0) {
       const int tiles_n = (g.N + bn - 1) / bn;
@@ -134,7 +140,7 @@ struct RsEpilogue {
   // load latency, so every thread keeps 32 independent 16-byte loads in flight whatever the number
   // of ranks: NR sources x U vectors.
   __device__ __forceinline__ void after_tiles(const GemmArgs& g, uint32_t epoch, int cta, int n_cta, int q, int lane,
-                                              volatile uint32_t* abort_flag) const {
+                                              volatile uint32_t* abort_flag, uint8_t* /*warp_smem*/) const {
     if (nranks <= 1) reduce_owned<1, 16>(g, epoch, cta, n_cta, q, lane, abort_flag);
     else if (nranks <= 2) reduce_owned<2, 16>(g, epoch, cta, n_cta, q, lane, abort_flag);
     else if (nranks <= 4) reduce_owned<4, 8>(g, epoch, cta, n_cta, q, lane, abort_flag);
@@ -229,8 +235,12 @@ struct AgEpilogue {
                                         int chunk, uint8_t* warp_smem, int lane) const {
     plain.store(g, epoch, row, col, r, chunk, warp_smem, lane);
   }
-  __device__ __forceinline__ void tile_done(const GemmArgs&, uint32_t, int, int, int, int) const {}
-  __device__ __forceinline__ void after_tiles(const GemmArgs&, uint32_t, int, int, int, int, volatile uint32_t*) const {}
+  static constexpr int kWarpSmemBytes = kEpiWarpBytes;
+  static constexpr int kSingleStages = kStages;
+  static constexpr int kPairStages = 6;
+  __device__ __forceinline__ void warp_begin(uint8_t*, int) const {}
+  __device__ __forceinline__ void tile_done(const GemmArgs&, uint32_t, int, int, int, int, uint8_t*) const {}
+  __device__ __forceinline__ void after_tiles(const GemmArgs&, uint32_t, int, int, int, int, volatile uint32_t*, uint8_t*) const {}
 
   // A communication CTA: barrier with the same CTA of every peer (everyone has left the previous
   // use of the gather buffers), then push the local shard to every peer with the TMA engine:
@@ -329,7 +339,7 @@ MNCCL_EXPORT size_t mncclGemmRsStageBytes(int M, int N, int /*nranks*/) {
   return size_t(2) * M * N * 2;  // two halves x nranks slots x (M / nranks) rows x N bf16
 }
 MNCCL_EXPORT size_t mncclGemmRsFlagWords(int M, int N, int nranks) {
-  return size_t(nranks) * (M / nranks / kBM) * ((N + 191) / 192);  // sized for the narrowest tile
+  return size_t(nranks) * (M / nranks / kBM) * ((N + 127) / 128);  // sized for the narrowest tile
 }
 MNCCL_EXPORT size_t mncclAgGemmReadyWords(int M) { return size_t(M) / kBM; }
 MNCCL_EXPORT size_t mncclAgGemmBarWords(int nranks, int n_comm) { return size_t(nranks) * n_comm; }

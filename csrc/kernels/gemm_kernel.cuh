@@ -52,9 +52,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw);
-  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(smem + kStages * kStageBytes);
+  constexpr int NS = Epilogue::kSingleStages;  // ring depth: an epilogue with a large scratch takes a stage
+  constexpr int kWarpSmem = Epilogue::kWarpSmemBytes;
+  static_assert(NS >= 2 && NS <= kStages, "ring depth");
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(smem + NS * kStageBytes);
   static_assert(sizeof(SharedCtl) <= kCtlBytes, "control block outgrew its slot");
-  uint8_t* epi_smem = smem + kStages * kStageBytes + kCtlBytes;
+  uint8_t* epi_smem = smem + NS * kStageBytes + kCtlBytes;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -83,7 +86,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int num_kb = (g.K + kBK - 1) / kBK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < NS; ++s) {
       mbar_init(smem_u32(&ctl->full[s]), 1);
       mbar_init(smem_u32(&ctl->empty[s]), 1);
     }
@@ -143,8 +146,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           if (waited) asm volatile("fence.proxy.async.global;" ::: "memory");
         }
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const uint32_t s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1u;
+          const uint32_t s = it % NS;
+          const uint32_t ph = (it / NS) & 1u;
           if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1u, &ctl->abort, budget)) { ok = false; break; }
           const uint32_t full = smem_u32(&ctl->full[s]);
           mbar_arrive_expect_tx(full, kTileABytes + BN * kBK * 2);
@@ -156,9 +159,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       // Wind-down after a failed wait: let copies that are still in flight land
       // before the CTA (and its shared memory) goes away.
       if (!ok) {
-        for (uint32_t back = 0; back < kStages && back < it; ++back) {
+        for (uint32_t back = 0; back < NS && back < it; ++back) {
           const uint32_t j = it - 1 - back;
-          mbar_wait(smem_u32(&ctl->full[j % kStages]), (j / kStages) & 1u, &ctl->abort /*already set*/, 0);
+          mbar_wait(smem_u32(&ctl->full[j % NS]), (j / NS) & 1u, &ctl->abort /*already set*/, 0);
           // (budget 0: one more try each; the data either landed or the MMA side consumed it)
         }
       }
@@ -177,8 +180,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tc_fence_after_sync();
         const uint32_t d = tmem_base + buf * kBN;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const uint32_t s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1u;
+          const uint32_t s = it % NS;
+          const uint32_t ph = (it / NS) & 1u;
           if (!mbar_wait(smem_u32(&ctl->full[s]), ph, &ctl->abort, budget)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = base + s * kStageBytes;
@@ -198,6 +201,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
+    uint8_t* warp_smem = epi_smem + (warp - 2) * kWarpSmem;
+    epi.warp_begin(warp_smem, lane);
     uint32_t local = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += n_gemm, ++local) {
@@ -214,14 +219,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
-        epi.store(g, epoch, row, tn * BN + c * 32, r, c, epi_smem + (warp - 2) * kEpiWarpBytes, lane);
+        epi.store(g, epoch, row, tn * BN + c * 32, r, c, warp_smem, lane);
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[buf]));
-      epi.tile_done(g, epoch, tm, tn, q, lane);
+      epi.tile_done(g, epoch, tm, tn, q, lane, warp_smem);
     }
-    epi.after_tiles(g, epoch, static_cast<int>(blockIdx.x), n_gemm, q, lane, &ctl->abort);
+    epi.after_tiles(g, epoch, static_cast<int>(blockIdx.x), n_gemm, q, lane, &ctl->abort, warp_smem);
   }
 
   tc_fence_before_sync();
@@ -240,13 +245,16 @@ template <typename Epilogue, int BN>
 inline cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const Epilogue& epi, int grid,
                              cudaStream_t stream) {
   auto kernel = gemm_bf16_kernel<Epilogue, BN>;
+  constexpr int smem_bytes = Epilogue::kSingleStages * kStageBytes + 1024 /*alignment slack*/ + kCtlBytes +
+                             kEpilogueWarps * Epilogue::kWarpSmemBytes;
+  static_assert(smem_bytes <= 227 * 1024, "shared memory of the single-CTA kernel");
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  kernel<<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, g, epi);
+  kernel<<<grid, kThreads, smem_bytes, stream>>>(ta, tb, g, epi);
   return cudaGetLastError();
 }
 

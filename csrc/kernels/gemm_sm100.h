@@ -26,7 +26,6 @@ constexpr int kThreads = 32 * (2 + kEpilogueWarps);
 constexpr int kCtlBytes = 256;            // barriers and control words
 constexpr int kEpiRowBytes = 128 + 16;    // 64 bf16 of one row + padding against bank conflicts
 constexpr int kEpiWarpBytes = 32 * kEpiRowBytes;  // per epilogue warp: 32 rows x 64 columns, for transposed stores
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + kCtlBytes + kEpilogueWarps * kEpiWarpBytes;
 
 struct GemmArgs {
   int M, N, K;
@@ -71,6 +70,11 @@ __device__ __forceinline__ void tile_coords(const GemmArgs& g, int t, int tiles_
 // Plain epilogue: convert and store the accumulator tile to C.
 template <bool OUT_F32>
 struct StoreEpilogue {
+  // what the kernels size their shared memory by: scratch per epilogue warp, TMA ring depth of the
+  // single-CTA and of the CTA-pair kernel
+  static constexpr int kWarpSmemBytes = kEpiWarpBytes;
+  static constexpr int kSingleStages = kStages;
+  static constexpr int kPairStages = 6;
   // Thread holds row `row`, columns [col, col+32) as fp32 bit patterns.
   // `chunk` counts the 32-column pieces of the tile; `warp_smem` is kEpiWarpBytes of scratch.
   // A lane's own 32 columns are 64 (bf16) or 128 (fp32) bytes of ONE row, so storing straight from
@@ -143,8 +147,9 @@ struct StoreEpilogue {
       for (int j = 0; j < 32 && col + j < g.N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
     }
   }
-  __device__ __forceinline__ void tile_done(const GemmArgs&, uint32_t, int, int, int, int) const {}
-  __device__ __forceinline__ void after_tiles(const GemmArgs&, uint32_t, int, int, int, int, volatile uint32_t*) const {}
+  __device__ __forceinline__ void warp_begin(uint8_t*, int) const {}
+  __device__ __forceinline__ void tile_done(const GemmArgs&, uint32_t, int, int, int, int, uint8_t*) const {}
+  __device__ __forceinline__ void after_tiles(const GemmArgs&, uint32_t, int, int, int, int, volatile uint32_t*, uint8_t*) const {}
   __device__ __forceinline__ void comm_cta(const GemmArgs&, uint32_t, int, int, volatile uint32_t*, uint8_t*, uint32_t) const {}
 };
 
