@@ -198,6 +198,14 @@ MNCCL_EXPORT int mncclGemmMaxPairs(void) { return max_pairs<StoreEpilogue<false>
 // Kernel choice for the calls that follow: -1 automatic, 0 single-CTA tiles, 1 CTA pairs (cta_group::2).
 MNCCL_EXPORT void mncclGemmSetPairMode(int mode) { set_pair_mode(mode); }
 
+// The host-side choice for an M x N product on `ctas` CTAs, without launching anything (needs no
+// GPU): *tile_n = tile width of the single-CTA kernel (`narrow` = 1 admits 224 and 128), *pair = 1
+// when the CTA-pair kernel would be taken instead.
+MNCCL_EXPORT void mncclGemmPlan(int M, int N, int ctas, int narrow, int* tile_n, int* pair) {
+  if (tile_n) *tile_n = pick_tile_n(M, N, ctas, narrow != 0);
+  if (pair) *pair = want_pair(M, N, ctas) ? 1 : 0;
+}
+
 // Reads and clears the GEMM error word of the current device (0 = no bounded
 // wait ever ran out).  Synchronises the device.
 MNCCL_EXPORT int mncclGemmStatus(uint32_t* status) {

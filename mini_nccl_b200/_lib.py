@@ -95,6 +95,8 @@ def lib() -> C.CDLL:
         sig("mncclGemmStatus", i32, P(u32))
         if hasattr(L, "mncclGemmSetPairMode"):
             sig("mncclGemmSetPairMode", None, i32)
+        if hasattr(L, "mncclGemmPlan"):
+            sig("mncclGemmPlan", None, i32, i32, i32, i32, C.POINTER(C.c_int), C.POINTER(C.c_int))
     if hasattr(L, "mncclGemmReduceScatterBf16"):
         sig("mncclGemmRsStageBytes", sz, i32, i32, i32)
         sig("mncclGemmRsFlagWords", sz, i32, i32, i32)

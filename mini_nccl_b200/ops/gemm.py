@@ -52,3 +52,13 @@ def gemm_status() -> int:
 def set_pair_mode(mode: int) -> None:
     """-1: automatic; 0: single-CTA 128 x 256 tiles; 1: CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles)."""
     _native().mncclGemmSetPairMode(int(mode))
+
+
+def gemm_plan(M: int, N: int, ctas: int = 148, narrow: bool = True):
+    """``(tile_n, pair)``: the tile width the single-CTA kernel would use for an ``M x N`` product on
+    ``ctas`` CTAs and whether the CTA-pair kernel would be taken instead.  Host logic only; needs no GPU."""
+    import ctypes as C
+
+    tile_n, pair = C.c_int(0), C.c_int(0)
+    _native().mncclGemmPlan(int(M), int(N), int(ctas), 1 if narrow else 0, C.byref(tile_n), C.byref(pair))
+    return tile_n.value, bool(pair.value)

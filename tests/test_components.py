@@ -148,3 +148,33 @@ def test_planner_geometry(lib):
     assert rs["algo"] == "twoshot" and rs["shard"] == 1001 and rs["copy_out"] == 0
     ag = plan(lib, 4, 1001, mode=2)
     assert ag["algo"] == "twoshot" and ag["copy_in"] == 0 and ag["copy_out"] == 1
+
+
+def test_gemm_host_plan_picks_tiles_and_cta_pairs():
+    """Host-side choice of the GEMM kernel (no GPU needed): CTA pairs for products whose 256 x 256
+    tiles fill the SM pairs, narrower single-CTA tiles for small products, and the pinned modes."""
+    import mini_nccl_b200 as mn
+    from mini_nccl_b200.ops.gemm import gemm_plan, set_pair_mode
+
+    if not hasattr(mn.lib(), "mncclGemmPlan"):
+        pytest.skip("library built without the GEMM translation unit")
+    try:
+        set_pair_mode(-1)
+        assert gemm_plan(8192, 8192)[1] is True
+        assert gemm_plan(4096, 3584)[1] is True          # 224 pair tiles on 74 pairs
+        assert gemm_plan(2048, 2048)[1] is True          # 64 pair tiles: most pairs busy
+        assert gemm_plan(1024, 1024) == (128, False)     # 16 pair tiles would leave 58 pairs idle
+        assert gemm_plan(128, 4096)[1] is False          # fewer than 256 rows: no pair tile
+        assert gemm_plan(4096, 128)[1] is False          # fewer than 256 columns
+        assert gemm_plan(4096, 4096, ctas=1)[1] is False
+        # the tile width is never one the epilogue cannot take
+        for m, n in ((4096, 3584), (512, 7168), (300, 1000)):
+            assert gemm_plan(m, n, narrow=False)[0] in (256, 192)
+            assert gemm_plan(m, n, narrow=True)[0] in (256, 224, 192, 128)
+        set_pair_mode(0)
+        assert gemm_plan(8192, 8192)[1] is False
+        set_pair_mode(1)
+        assert gemm_plan(1024, 1024)[1] is True
+        assert gemm_plan(128, 4096)[1] is False          # pinned on, but the shape has no pair tile
+    finally:
+        set_pair_mode(-1)
