@@ -104,10 +104,10 @@ def main():
         comm.all_reduce(buf, "sum", out=out, scale=1.0 / world if world > 1 else 1.0)
 
     # ---- headline: device-timed, K steps, max over ranks
-    # Untimed pre-warm for ~0.3 s: clocks and NVLink links leave their idle power states (a cold
-    # start measured 15 % below the steady state), then the W warm-up steps proper.
+    # Untimed pre-warm for ~1 s: clocks and NVLink links leave their idle power states (a cold
+    # start measured 15 to 25 % below the steady state), then the W warm-up steps proper.
     t_pre = time.perf_counter()
-    while time.perf_counter() - t_pre < 0.3:
+    while time.perf_counter() - t_pre < 1.0:
         for _ in range(10):
             step()
         torch.cuda.synchronize()

@@ -77,11 +77,12 @@ struct RsEpilogue {
   __nv_bfloat16* out;                // [rows_per_rank, N] on this rank
   int ldo;
   int bn;                            // tile width of this launch (256 or 192)
-  int tiled;                         // staging layout: 1 tile by tile (below), 0 row-major [rows_per_rank][N]
+  int tiled;                         // staging layout: 0 row-major [rows_per_rank][N] (default), 1 tile by tile (MINI_NCCL_RS_TILED=1)
 
-  // One source rank's partial sums of the rows one rank owns, TILE by tile: a 128 x bn tile is one
-  // contiguous block.  Stores that land 128 bytes here, 128 bytes a row (N * 2 bytes) further on
-  // reached half the NVLink rate of stores into a compact region (measured 340 against 665 GB/s).
+  // One source rank's partial sums of the rows one rank owns.  Row-major by default.  The tiled
+  // layout (a 128 x bn tile is one contiguous block) looked better in a two-GPU store test (compact
+  // destinations 665 GB/s, 512-byte runs 8 KB apart 340 GB/s) but measured WORSE on 8 GPUs
+  // (107 against 89 us on 4096 x 4096 x 1792), so it stays an option.
   __device__ __forceinline__ size_t tile_elems() const { return static_cast<size_t>(kBM) * bn; }
   __device__ __forceinline__ size_t slot_elems(const GemmArgs& g) const {
     return tiled ? static_cast<size_t>(rows_per_rank / kBM) * ((g.N + bn - 1) / bn) * tile_elems()
@@ -390,7 +391,7 @@ MNCCL_EXPORT int mncclGemmReduceScatterBf16(const void* A, const void* B, void* 
   {
     static const int tiled_env = [] {
       const char* e = getenv("MINI_NCCL_RS_TILED");
-      return (e != nullptr && *e != 0) ? atoi(e) : 1;
+      return (e != nullptr && *e != 0) ? atoi(e) : 0;
     }();
     epi.tiled = tiled_env;
   }
