@@ -475,8 +475,15 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
   // that overlap the collective, instead of kernels reading and writing host memory word by word.
   const bool host_in = !in_seg && classify(send, true) == MemKind::PinnedHost;
   const bool host_out = !out_seg && classify(recv, true) == MemKind::PinnedHost;
-  const bool host_pipe = mode == Mode::AllReduce && (host_in || host_out) && cfg_.host_pipeline_min_bytes != 0 &&
-                         std::max(in_bytes, out_bytes) >= cfg_.host_pipeline_min_bytes;
+  bool host_pipe = mode == Mode::AllReduce && (host_in || host_out) && cfg_.host_pipeline_min_bytes != 0 &&
+                   std::max(in_bytes, out_bytes) >= cfg_.host_pipeline_min_bytes;
+  if (host_pipe && (!pipe_ || (size_ == 1 && solo_stage_ == nullptr))) {
+    // The first pipelined call creates streams, events and (one rank) device staging: not while a
+    // graph is being captured.  Such a call takes the direct kernel instead.
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess) (void)cudaGetLastError();
+    if (cs == cudaStreamCaptureStatusActive) host_pipe = false;
+  }
   if (host_pipe && size_ == 1) {
     launch_solo_host(send, send_t, recv, recv_t, count, scale, stream, host_in, host_out);  // one rank: Avg == Sum
     stats_.calls++;
@@ -685,7 +692,7 @@ void Comm::launch_solo_host(const void* send, DType send_t, void* recv, DType re
   size_t chunk = cfg_.host_chunk_bytes / std::max(isz, osz);
   chunk &= ~size_t(4095);
   if (chunk == 0) chunk = 4096;
-  const size_t half = chunk * std::max(isz, osz);
+  const size_t half = (std::max(cfg_.host_chunk_bytes, chunk * std::max(isz, osz)) + 255) & ~size_t(255);  // the same for every type
   if (solo_stage_ == nullptr || solo_stage_half_ < half) {
     if (solo_stage_) {
       RT_CHECK(cudaDeviceSynchronize(), "cudaDeviceSynchronize");

@@ -6,6 +6,9 @@
 // numbers raise InvalidArgument instead of an uncaught std::invalid_argument.
 // The banner "[Config] Loaded: SLICE_SIZE=... B, WINDOW=..., BATCH=..." is
 // printed once per process.
+// Two switches of the GEMM kernels are read where they are used (csrc/kernels):
+// MINI_NCCL_GEMM_PAIR = -1|0|1 (automatic / single-CTA tiles / CTA pairs) and
+// MINI_NCCL_RS_TILED = 0|1 (staging layout of GEMM -> reduce-scatter).
 #pragma once
 #include <cstddef>
 #include <cstdint>

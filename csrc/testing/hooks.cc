@@ -96,6 +96,8 @@ MNCCL_EXPORT int mnccl_test_config(const char* env, char* out, size_t len) {
     o << "{\"slice_size\":" << c.slice_size << ",\"window_size\":" << c.window_size << ",\"signal_batch\":" << c.signal_batch
       << ",\"net_device\":\"" << c.net_device << "\",\"watchdog_timeout_ms\":" << c.watchdog_timeout_ms
       << ",\"bootstrap_port\":" << c.bootstrap_port << ",\"hera_port\":" << c.hera_port << ",\"staging_bytes\":" << c.staging_bytes
+      << ",\"pipeline_min_bytes\":" << c.pipeline_min_bytes << ",\"host_pipeline_min_bytes\":" << c.host_pipeline_min_bytes
+      << ",\"host_chunk_bytes\":" << c.host_chunk_bytes
       << ",\"algo\":\"" << c.algo << "\",\"nvls_enable\":" << (c.nvls_enable ? "true" : "false") << ",\"banner\":\"" << c.banner() << "\"}";
     copy_out(o.str(), out, len);
     return 0;

@@ -38,6 +38,17 @@ def test_config_values_and_suffixes(lib):
     assert c["net_device"] == "mlx5_1" and c["watchdog_timeout_ms"] == 250 and c["algo"] == "nvls" and c["nvls_enable"] is False
 
 
+def test_config_pipeline_knobs(lib):
+    rc, c = cfg(lib, "")
+    assert rc == 0
+    assert c["pipeline_min_bytes"] == 48 << 20 and c["host_pipeline_min_bytes"] == 4 << 20 and c["host_chunk_bytes"] == 8 << 20
+    rc, c = cfg(lib, "MINI_NCCL_HOST_PIPELINE_MIN_BYTES=0;MINI_NCCL_HOST_CHUNK_BYTES=1K;MINI_NCCL_PIPELINE_MIN_BYTES=1M")
+    assert rc == 0
+    assert c["host_pipeline_min_bytes"] == 0          # 0 switches the host pipeline off
+    assert c["host_chunk_bytes"] == 64 << 10          # clamped: tiny chunks would be all launch overhead
+    assert c["pipeline_min_bytes"] == 1 << 20
+
+
 @pytest.mark.parametrize("bad", ["MINI_NCCL_SLICE_SIZE=abc", "MINI_NCCL_WINDOW_SIZE=1.5x", "MINI_NCCL_NVLS_ENABLE=maybe",
                                  "MINI_NCCL_BOOTSTRAP_PORT=70000", "MINI_NCCL_SLICE_SIZE=-5"])
 def test_config_malformed_is_invalid_argument(lib, bad):
