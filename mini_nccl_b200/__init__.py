@@ -15,3 +15,13 @@ from .comm import Communicator
 
 __all__ = ["Communicator", "MiniNcclError", "lib", "lib_file"]
 __version__ = "0.1.0"
+
+
+def __getattr__(name):
+    # Submodules on first use (`mn.ops.gemm_bf16`, `mn.parallel.DistributedDataParallel`, ...): they pull in
+    # torch, which the ctypes binding itself does not need.
+    if name in ("ops", "parallel", "models", "utils", "build"):
+        import importlib
+
+        return importlib.import_module("." + name, __name__)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
