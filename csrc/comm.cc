@@ -17,6 +17,7 @@
 #include "bootstrap/hera.h"
 #include "bootstrap/store.h"
 #include "core/log.h"
+#include "core/nvtx.h"
 #include "mem/cuda_driver.h"
 #include "mem/symmetric.h"
 #include "net/ring.h"
@@ -471,6 +472,11 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
   Plan plan = make_plan(pi, caps_, cfg_);
   if (!plan.valid) fail(Result::InvalidArgument, std::string("no kernel for this request: ") + plan.reason);
   if (!kernel_exists(plan.spec)) fail(Result::InvalidArgument, "no kernel for this type / operator combination");
+  // range in the library's NVTX domain: "<collective>/<algorithm>", payload = bytes
+  static const char* const kModeNames[] = {"allreduce", "reducescatter", "allgather"};
+  char range_name[48];
+  snprintf(range_name, sizeof(range_name), "%s/%s", kModeNames[static_cast<int>(mode) % 3], algo_name(plan.spec.algo));
+  NvtxDomainRange nvtx_range(range_name, in_bytes);
   // Pinned host buffers: the copy engines move them (both directions at once over PCIe) in chunks
   // that overlap the collective, instead of kernels reading and writing host memory word by word.
   const bool host_in = !in_seg && classify(send, true) == MemKind::PinnedHost;
