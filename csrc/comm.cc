@@ -625,8 +625,8 @@ void Comm::launch_pipelined(const void* send, DType send_t, void* recv, DType re
     char* b_h = dev_.ctrl[rank_] + dev_.off_stage_b + h * half;
     // copy-in (after the collective that last read this half)
     if (i >= 2) RT_CHECK(cudaStreamWaitEvent(pipe_->s_in, pipe_->ev_comm[h], 0), "cudaStreamWaitEvent");
-    if (host_in && send_t == wire_t)
-      RT_CHECK(cudaMemcpyAsync(a_h, static_cast<const char*>(send) + off * isz, n * isz, cudaMemcpyHostToDevice, pipe_->s_in), "cudaMemcpyAsync");
+    if ((host_in || cfg_.pipeline_copy_engine) && send_t == wire_t)
+      RT_CHECK(cudaMemcpyAsync(a_h, static_cast<const char*>(send) + off * isz, n * isz, cudaMemcpyDefault, pipe_->s_in), "cudaMemcpyAsync");
     else
       local_copy(static_cast<const char*>(send) + off * isz, send_t, a_h, wire_t, n, pipe_->s_in);
     RT_CHECK(cudaEventRecord(pipe_->ev_in[h], pipe_->s_in), "cudaEventRecord");
@@ -678,8 +678,8 @@ void Comm::launch_pipelined(const void* send, DType send_t, void* recv, DType re
     stats_.by_algo[static_cast<int>(plan.spec.algo)]++;
     // copy-out
     RT_CHECK(cudaStreamWaitEvent(pipe_->s_out, pipe_->ev_comm[h], 0), "cudaStreamWaitEvent");
-    if (host_out)
-      RT_CHECK(cudaMemcpyAsync(static_cast<char*>(recv) + off * osz, b_h, n * osz, cudaMemcpyDeviceToHost, pipe_->s_out), "cudaMemcpyAsync");
+    if (host_out || cfg_.pipeline_copy_engine)
+      RT_CHECK(cudaMemcpyAsync(static_cast<char*>(recv) + off * osz, b_h, n * osz, cudaMemcpyDefault, pipe_->s_out), "cudaMemcpyAsync");
     else
       local_copy(b_h, recv_t, static_cast<char*>(recv) + off * osz, recv_t, n, pipe_->s_out);
     RT_CHECK(cudaEventRecord(pipe_->ev_out[h], pipe_->s_out), "cudaEventRecord");
