@@ -466,8 +466,11 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
       if (out_seg && !out_seg->mc) pi.out_symmetric = false;
     }
   }
-  // Kernels dereference these pointers: pageable host memory would fault.
-  if ((!in_seg && classify(send, true) == MemKind::PlainHost) || (!out_seg && send != recv && classify(recv, true) == MemKind::PlainHost))
+  // Kernels dereference these pointers: pageable host memory would fault.  (One driver query per
+  // buffer that is not in symmetric memory; the result also decides on the host pipeline below.)
+  const MemKind send_kind = in_seg ? MemKind::Device : classify(send, true);
+  const MemKind recv_kind = out_seg ? MemKind::Device : (recv == send ? send_kind : classify(recv, true));
+  if (send_kind == MemKind::PlainHost || recv_kind == MemKind::PlainHost)
     fail(Result::InvalidArgument, "buffers must be device memory or pinned host memory on the GPU data plane");
   Plan plan = make_plan(pi, caps_, cfg_);
   if (!plan.valid) fail(Result::InvalidArgument, std::string("no kernel for this request: ") + plan.reason);
@@ -479,8 +482,8 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
   NvtxDomainRange nvtx_range(range_name, in_bytes);
   // Pinned host buffers: the copy engines move them (both directions at once over PCIe) in chunks
   // that overlap the collective, instead of kernels reading and writing host memory word by word.
-  const bool host_in = !in_seg && classify(send, true) == MemKind::PinnedHost;
-  const bool host_out = !out_seg && classify(recv, true) == MemKind::PinnedHost;
+  const bool host_in = send_kind == MemKind::PinnedHost;
+  const bool host_out = recv_kind == MemKind::PinnedHost;
   bool host_pipe = mode == Mode::AllReduce && (host_in || host_out) && cfg_.host_pipeline_min_bytes != 0 &&
                    std::max(in_bytes, out_bytes) >= cfg_.host_pipeline_min_bytes;
   if (host_pipe && (!pipe_ || (size_ == 1 && solo_stage_ == nullptr))) {

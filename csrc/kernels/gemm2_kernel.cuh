@@ -242,8 +242,11 @@ template <typename Epilogue>
 inline cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const Epilogue& epi,
                                int grid, cudaStream_t stream, int* grid_used = nullptr) {
   auto kernel = gemm2_bf16_kernel<Epilogue>;
-  static bool configured = false;
-  static int max_clusters = 0;
+  static bool configured_dev[kMaxDevices] = {};
+  static int max_clusters_dev[kMaxDevices] = {};
+  const int dev = current_device_slot();
+  bool& configured = configured_dev[dev];
+  int& max_clusters = max_clusters_dev[dev];
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kThreads);
@@ -276,7 +279,8 @@ inline cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, con
 // Number of CTA pairs of this kernel the device can hold at once (asked once per kernel).
 template <typename Epilogue>
 inline int max_pairs() {
-  static int cached = 0;
+  static int cached_dev[kMaxDevices] = {};
+  int& cached = cached_dev[current_device_slot()];
   if (cached > 0) return cached;
   auto kernel = gemm2_bf16_kernel<Epilogue>;
   cudaLaunchConfig_t cfg = {};

@@ -241,6 +241,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   }
 }
 
+constexpr int kMaxDevices = 64;
+inline int current_device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) (void)cudaGetLastError();
+  return (dev >= 0 && dev < kMaxDevices) ? dev : 0;
+}
+
 template <typename Epilogue, int BN>
 inline cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, const Epilogue& epi, int grid,
                              cudaStream_t stream) {
@@ -248,11 +255,12 @@ inline cudaError_t launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const
   constexpr int smem_bytes = Epilogue::kSingleStages * kStageBytes + 1024 /*alignment slack*/ + kCtlBytes +
                              kEpilogueWarps * Epilogue::kWarpSmemBytes;
   static_assert(smem_bytes <= 227 * 1024, "shared memory of the single-CTA kernel");
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[kMaxDevices] = {};  // the attribute belongs to the function on ONE device
+  const int dev = current_device_slot();
+  if (!configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) return e;
-    configured = true;
+    configured[dev] = true;
   }
   kernel<<<grid, kThreads, smem_bytes, stream>>>(ta, tb, g, epi);
   return cudaGetLastError();

@@ -41,8 +41,7 @@ int pair_mode_from_env() {
   return v < 0 ? -1 : (v > 0 ? 1 : 0);
 }
 int g_use_pair = pair_mode_from_env();
-uint32_t* g_err_dev = nullptr;  // one error word per process and device (device 0..15)
-int g_err_device = -1;
+uint32_t* g_err_dev[kMaxDevices] = {};  // one error word per device of the process
 
 }  // namespace
 
@@ -75,14 +74,14 @@ uint32_t* error_word() {
   std::lock_guard<std::mutex> lk(g_mu);
   int dev = 0;
   cudaGetDevice(&dev);
-  if (g_err_dev == nullptr || g_err_device != dev) {
+  if (dev < 0 || dev >= kMaxDevices) dev = 0;
+  if (g_err_dev[dev] == nullptr) {
     uint32_t* p = nullptr;
     if (cudaMalloc(&p, 64) != cudaSuccess) return nullptr;
     cudaMemset(p, 0, 64);
-    g_err_dev = p;  // (a word allocated for another device stays allocated; processes here use one device)
-    g_err_device = dev;
+    g_err_dev[dev] = p;
   }
-  return g_err_dev;
+  return g_err_dev[dev];
 }
 
 int pick_tile_n(int M, int N, int ctas, bool allow_224) {
