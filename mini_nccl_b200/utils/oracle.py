@@ -115,3 +115,41 @@ def tolerance(dtype: int, nranks: int) -> float:
     if dtype == _lib.FLOAT64:
         return 1e-12 * nranks
     return 0.0
+
+
+# --------------------------------------------------------------------------- tensor-parallel fusions
+# Host restatements of the three GEMM kernels, in the kernels' own arithmetic: bf16 operands (as
+# uint16 bit patterns), products and sums in fp32, ONE rounding to bf16 where the kernel rounds.
+# The tensor cores add the K products of a tile in an order of their own, so GPU results are
+# compared with a tolerance; the roundings and the rank order of the reduction are exact.
+
+def oracle_gemm_bf16(a_bits: np.ndarray, b_bits: np.ndarray, out_fp32: bool = False) -> np.ndarray:
+    """``C[M, N] = A[M, K] @ B[N, K].T``: bf16 bit patterns in, fp32 accumulation, bf16 bit patterns
+    (or fp32 values) out."""
+    acc = bf16_bits_to_f32(np.ascontiguousarray(a_bits)) @ bf16_bits_to_f32(np.ascontiguousarray(b_bits)).T
+    acc = acc.astype(np.float32)
+    return acc if out_fp32 else f32_to_bf16_bits(acc)
+
+
+def oracle_gemm_reduce_scatter(a_bits: list[np.ndarray], b_bits: list[np.ndarray], rank: int) -> np.ndarray:
+    """GEMM -> reduce-scatter as the fused kernel computes it: every rank's partial product is rounded
+    to bf16 before it travels, the owner adds the partial tiles in RANK ORDER in fp32 and rounds the sum
+    once.  ``a_bits[r]`` is ``[M, K_r]``, ``b_bits[r]`` is ``[N, K_r]``; returns the rows ``rank`` owns."""
+    n = len(a_bits)
+    M = a_bits[0].shape[0]
+    if M % n:
+        raise ValueError("M must divide by the number of ranks")
+    per = M // n
+    rows = slice(rank * per, (rank + 1) * per)
+    acc = None
+    for r in range(n):
+        partial = bf16_bits_to_f32(oracle_gemm_bf16(a_bits[r][rows], b_bits[r]))  # what rank r sends
+        acc = partial.copy() if acc is None else (acc + partial).astype(np.float32)
+    return f32_to_bf16_bits(acc)
+
+
+def oracle_all_gather_gemm(x_shards_bits: list[np.ndarray], b_bits: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    """all-gather -> GEMM: the gathered activations (row-wise concatenation of the shards, which must be
+    bit-identical on every rank) and their product with this rank's weight slice ``b [N_r, K]``."""
+    gathered = np.concatenate([np.ascontiguousarray(s) for s in x_shards_bits], axis=0)
+    return gathered, oracle_gemm_bf16(gathered, b_bits)

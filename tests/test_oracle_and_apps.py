@@ -109,3 +109,31 @@ def test_dual_process_demo(free_port):
     assert all(p.returncode == 0 for p in ps), outs
     assert 'received: "Hello from the client' in outs[0][0] and 'received: "Hello from the server' in outs[1][0]
     assert subprocess.run([_bin("demo_dual_process")], capture_output=True).returncode == 1
+
+
+def test_tensor_parallel_oracles_restates_the_kernels_arithmetic():
+    """GEMM -> reduce-scatter and all-gather -> GEMM on the host: bf16 roundings where the kernels
+    round, rank-ordered fp32 sum, rows partitioned by owner."""
+    from mini_nccl_b200.utils import oracle as O
+
+    rng = np.random.default_rng(7)
+    n, M, N, K = 4, 64, 48, 96
+    a = [O.f32_to_bf16_bits(rng.standard_normal((M, K // n)).astype(np.float32)) for _ in range(n)]
+    b = [O.f32_to_bf16_bits(rng.standard_normal((N, K // n)).astype(np.float32)) for _ in range(n)]
+    wide = sum(O.bf16_bits_to_f32(a[r]).astype(np.float64) @ O.bf16_bits_to_f32(b[r]).astype(np.float64).T for r in range(n))
+    got = np.concatenate([O.bf16_bits_to_f32(O.oracle_gemm_reduce_scatter(a, b, r)) for r in range(n)])
+    assert got.shape == (M, N)
+    # n + 1 bf16 roundings of values of magnitude ~ sqrt(K): relative 2^-8 each
+    assert np.abs(got - wide).max() <= (n + 1) * 2.0 ** -8 * np.abs(wide).max()
+    # the partial products really are rounded before the sum: exact fp32 sums differ somewhere
+    exact = O.bf16_bits_to_f32(O.f32_to_bf16_bits(wide.astype(np.float32)))
+    assert np.any(got != exact)
+    # one rank: reduce-scatter of one operand is the rounded product itself
+    assert np.array_equal(O.oracle_gemm_reduce_scatter(a[:1], b[:1], 0), O.oracle_gemm_bf16(a[0], b[0]))
+    # all-gather -> GEMM: gathered rows are the shards in rank order, product equals the plain GEMM
+    x = [O.f32_to_bf16_bits(rng.standard_normal((M // n, K)).astype(np.float32)) for _ in range(n)]
+    w = O.f32_to_bf16_bits(rng.standard_normal((N, K)).astype(np.float32))
+    gathered, c = O.oracle_all_gather_gemm(x, w)
+    assert gathered.shape == (M, K) and np.array_equal(gathered[M // n:2 * M // n], x[1])
+    assert np.array_equal(c, O.oracle_gemm_bf16(np.concatenate(x), w))
+    assert O.oracle_gemm_bf16(x[0], w, out_fp32=True).dtype == np.float32
