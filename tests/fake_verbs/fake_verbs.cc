@@ -87,6 +87,14 @@ int ibv_dereg_mr(ibv_mr* mr) { delete mr; return 0; }
 
 int ibv_post_send(ibv_qp* qp, ibv_send_wr* wr, ibv_send_wr** bad) {
   for (; wr; wr = wr->next) {
+    if (qp->state == IBV_QPS_ERR) {
+      // as on real hardware: after a failed request the queue pair is in the error state and every
+      // later request is flushed with an error completion; nothing reaches the peer any more
+      CqImpl* cq = static_cast<CqImpl*>(qp->send_cq->impl);
+      std::lock_guard<std::mutex> lk(cq->mu);
+      cq->q.push_back(ibv_wc{wr->wr_id, IBV_WC_WR_FLUSH_ERR, qp->qp_num});
+      continue;
+    }
     if (qp->state != IBV_QPS_RTS || wr->opcode != IBV_WR_RDMA_WRITE || wr->num_sge != 1) {
       if (bad) *bad = wr;
       return EINVAL;
@@ -94,14 +102,25 @@ int ibv_post_send(ibv_qp* qp, ibv_send_wr* wr, ibv_send_wr** bad) {
     iovec l{reinterpret_cast<void*>(wr->sg_list[0].addr), wr->sg_list[0].length};
     iovec r{reinterpret_cast<void*>(wr->wr.rdma.remote_addr), wr->sg_list[0].length};
     ibv_wc_status st = IBV_WC_SUCCESS;
+    // Fault injection for the tests, on the host: the n-th signalled work request of the process
+    // (FAKE_VERBS_FAIL_SIGNALED_AT=n) moves nothing and completes with a remote access error.
+    if (wr->send_flags & IBV_SEND_SIGNALED) {
+      static std::atomic<long> signaled{0};
+      static const long fail_at = [] {
+        const char* e = std::getenv("FAKE_VERBS_FAIL_SIGNALED_AT");
+        return e ? std::atol(e) : 0L;
+      }();
+      if (fail_at > 0 && ++signaled == fail_at) st = IBV_WC_REM_ACCESS_ERR;
+    }
     size_t done = 0;
-    while (done < l.iov_len) {
+    while (st == IBV_WC_SUCCESS && done < l.iov_len) {
       iovec l2{static_cast<char*>(l.iov_base) + done, l.iov_len - done};
       iovec r2{static_cast<char*>(r.iov_base) + done, l.iov_len - done};
       ssize_t n = process_vm_writev(qp->dest_pid, &l2, 1, &r2, 1, 0);
       if (n <= 0) { st = IBV_WC_REM_ACCESS_ERR; break; }
       done += static_cast<size_t>(n);
     }
+    if (st != IBV_WC_SUCCESS) qp->state = IBV_QPS_ERR;
     if ((wr->send_flags & IBV_SEND_SIGNALED) || st != IBV_WC_SUCCESS) {
       CqImpl* cq = static_cast<CqImpl*>(qp->send_cq->impl);
       std::lock_guard<std::mutex> lk(cq->mu);

@@ -27,7 +27,7 @@ enum ibv_mtu { IBV_MTU_256 = 1, IBV_MTU_512, IBV_MTU_1024, IBV_MTU_2048, IBV_MTU
 enum ibv_access_flags { IBV_ACCESS_LOCAL_WRITE = 1, IBV_ACCESS_REMOTE_WRITE = 2, IBV_ACCESS_REMOTE_READ = 4 };
 enum ibv_send_flags { IBV_SEND_FENCE = 1, IBV_SEND_SIGNALED = 2, IBV_SEND_SOLICITED = 4, IBV_SEND_INLINE = 8 };
 enum ibv_wr_opcode { IBV_WR_RDMA_WRITE = 0, IBV_WR_SEND = 2 };
-enum ibv_wc_status { IBV_WC_SUCCESS = 0, IBV_WC_REM_ACCESS_ERR = 10, IBV_WC_GENERAL_ERR = 21 };
+enum ibv_wc_status { IBV_WC_SUCCESS = 0, IBV_WC_WR_FLUSH_ERR = 5, IBV_WC_REM_ACCESS_ERR = 10, IBV_WC_GENERAL_ERR = 21 };
 enum ibv_qp_attr_mask {
   IBV_QP_STATE = 1 << 0, IBV_QP_ACCESS_FLAGS = 1 << 3, IBV_QP_PKEY_INDEX = 1 << 4, IBV_QP_PORT = 1 << 5,
   IBV_QP_AV = 1 << 7, IBV_QP_PATH_MTU = 1 << 8, IBV_QP_TIMEOUT = 1 << 9, IBV_QP_RETRY_CNT = 1 << 10,

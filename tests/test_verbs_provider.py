@@ -74,3 +74,20 @@ def test_normal_build_reports_missing_verbs(free_port):
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=60,
                          cwd=str(Path(__file__).resolve().parent.parent))
     assert "RC 2" in out.stdout and "no libibverbs support" in out.stderr
+
+
+def test_failed_completion_is_an_error_not_a_hang(fake_lib, free_port):
+    # Rank 0's first signalled work request completes with a remote access error (made on the host,
+    # in the stand-in verbs library).  The reference ignores completion status
+    # (src/transport/RDMATransport.h:349-353); here the status surfaces as ncclRemoteError on the
+    # posting rank, and its peer, which never gets the flag, fails within the watchdog bound.
+    env = {"MINI_NCCL_BOOTSTRAP_PORT": free_port, "MINI_NCCL_LIB": fake_lib, "MINI_NCCL_TRANSPORT": "verbs",
+           "MINI_NCCL_WATCHDOG_TIMEOUT_MS": 400, "MINI_NCCL_SOCKET_TIMEOUT_MS": 3000}
+    res = run_ranks("cpu_ring_fault", 2, {}, env, per_rank_env={0: {"FAKE_VERBS_FAIL_SIGNALED_AT": 1}})
+    by_rank = {r["rank"]: r for r in res}
+    assert by_rank[0]["rc"] in (_lib.REMOTE_ERROR, _lib.INTERNAL_ERROR), by_rank[0]
+    assert by_rank[1]["rc"] == _lib.INTERNAL_ERROR, by_rank[1]
+    assert any(r["rc"] == _lib.REMOTE_ERROR for r in res) or "error status" in by_rank[0]["_stderr"]
+    for r in res:
+        assert r["rc2"] != 0, "the failure is sticky"
+        assert r["seconds"] < 5.0, "bounded"
