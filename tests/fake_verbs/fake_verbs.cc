@@ -17,9 +17,14 @@
 #include <vector>
 
 namespace {
+struct Completion {
+  ibv_wc wc;
+  ibv_qp* qp;        // the queue pair whose send queue this completion retires
+  uint64_t upto;     // ... up to and including this request (1-based count of posts)
+};
 struct CqImpl {
   std::mutex mu;
-  std::deque<ibv_wc> q;
+  std::deque<Completion> q;
 };
 std::atomic<uint32_t> g_qpn{100}, g_key{0x5000};
 std::vector<ibv_device> g_devs;
@@ -55,7 +60,7 @@ ibv_cq* ibv_create_cq(ibv_context* ctx, int, void*, void*, int) { return new ibv
 int ibv_destroy_cq(ibv_cq* cq) { delete static_cast<CqImpl*>(cq->impl); delete cq; return 0; }
 ibv_qp* ibv_create_qp(ibv_pd*, ibv_qp_init_attr* a) {
   if (a->qp_type != IBV_QPT_RC || a->cap.max_send_wr == 0) return nullptr;
-  return new ibv_qp{g_qpn.fetch_add(1), a->send_cq, IBV_QPS_RESET, 0, 0};
+  return new ibv_qp{g_qpn.fetch_add(1), a->send_cq, IBV_QPS_RESET, 0, 0, a->cap.max_send_wr, 0, 0};
 }
 int ibv_destroy_qp(ibv_qp* qp) { delete qp; return 0; }
 int ibv_modify_qp(ibv_qp* qp, ibv_qp_attr* a, int mask) {
@@ -92,13 +97,20 @@ int ibv_post_send(ibv_qp* qp, ibv_send_wr* wr, ibv_send_wr** bad) {
       // later request is flushed with an error completion; nothing reaches the peer any more
       CqImpl* cq = static_cast<CqImpl*>(qp->send_cq->impl);
       std::lock_guard<std::mutex> lk(cq->mu);
-      cq->q.push_back(ibv_wc{wr->wr_id, IBV_WC_WR_FLUSH_ERR, qp->qp_num});
+      cq->q.push_back(Completion{ibv_wc{wr->wr_id, IBV_WC_WR_FLUSH_ERR, qp->qp_num}, qp, ++qp->posted});
       continue;
     }
     if (qp->state != IBV_QPS_RTS || wr->opcode != IBV_WR_RDMA_WRITE || wr->num_sge != 1) {
       if (bad) *bad = wr;
       return EINVAL;
     }
+    // A send-queue slot is free again only when a LATER signalled completion has been polled:
+    // a poster that never signals (or never polls) overruns the queue, as on real hardware.
+    if (qp->posted - qp->retired >= qp->max_send_wr) {
+      if (bad) *bad = wr;
+      return ENOMEM;
+    }
+    const uint64_t my_index = ++qp->posted;
     iovec l{reinterpret_cast<void*>(wr->sg_list[0].addr), wr->sg_list[0].length};
     iovec r{reinterpret_cast<void*>(wr->wr.rdma.remote_addr), wr->sg_list[0].length};
     ibv_wc_status st = IBV_WC_SUCCESS;
@@ -124,7 +136,7 @@ int ibv_post_send(ibv_qp* qp, ibv_send_wr* wr, ibv_send_wr** bad) {
     if ((wr->send_flags & IBV_SEND_SIGNALED) || st != IBV_WC_SUCCESS) {
       CqImpl* cq = static_cast<CqImpl*>(qp->send_cq->impl);
       std::lock_guard<std::mutex> lk(cq->mu);
-      cq->q.push_back(ibv_wc{wr->wr_id, st, qp->qp_num});
+      cq->q.push_back(Completion{ibv_wc{wr->wr_id, st, qp->qp_num}, qp, my_index});
     }
   }
   return 0;
@@ -134,7 +146,9 @@ int ibv_poll_cq(ibv_cq* cq, int n, ibv_wc* wc) {
   std::lock_guard<std::mutex> lk(c->mu);
   int got = 0;
   while (got < n && !c->q.empty()) {
-    wc[got++] = c->q.front();
+    const Completion& done = c->q.front();
+    wc[got++] = done.wc;
+    if (done.upto > done.qp->retired) done.qp->retired = done.upto;
     c->q.pop_front();
   }
   return got;

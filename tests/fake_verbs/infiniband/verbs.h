@@ -17,7 +17,11 @@ struct ibv_context { struct ibv_device* device; };
 struct ibv_pd { struct ibv_context* context; };
 struct ibv_cq { struct ibv_context* context; void* impl; };
 struct ibv_mr { void* addr; size_t length; uint32_t lkey; uint32_t rkey; };
-struct ibv_qp { uint32_t qp_num; struct ibv_cq* send_cq; int state; int dest_pid; uint32_t dest_qpn; };
+struct ibv_qp {
+  uint32_t qp_num; struct ibv_cq* send_cq; int state; int dest_pid; uint32_t dest_qpn;
+  /* send-queue model of the stand-in: depth, requests posted, requests retired by a polled completion */
+  uint32_t max_send_wr; uint64_t posted; uint64_t retired;
+};
 union ibv_gid { uint8_t raw[16]; };
 struct ibv_port_attr { uint16_t lid; int state; };
 

@@ -32,7 +32,10 @@ def test_ring_over_verbs_provider(fake_lib, free_port):
 
 
 def test_verbs_device_override_and_tiny_slices(fake_lib, free_port):
-    # many small slices: exercises the forced signalling that keeps the send queue from overflowing
+    # many small slices with a huge signal batch: more than max_send_wr requests per phase.  The stand-in
+    # frees a send-queue slot only when a later signalled completion has been polled and answers ENOMEM
+    # to a post into a full queue, so this passes only because the provider forces a signal in time
+    # (the reference can overrun its queue: src/mini_nccl.cu:119,141-148 against max_send_wr 1024).
     env = {"MINI_NCCL_BOOTSTRAP_PORT": free_port, "MINI_NCCL_LIB": fake_lib, "MINI_NCCL_TRANSPORT": "verbs",
            "FAKE_VERBS_DEVICES": "mlx5_0,rxe0,mlx5_1", "MINI_NCCL_NET_DEVICE": "mlx5_1", "MINI_NCCL_SLICE_SIZE": 256,
            "MINI_NCCL_SIGNAL_BATCH": 1000, "MINI_NCCL_WINDOW_SIZE": 4}
