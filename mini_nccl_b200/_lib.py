@@ -97,6 +97,8 @@ def lib() -> C.CDLL:
             sig("mncclGemmSetPairMode", None, i32)
         if hasattr(L, "mncclGemmPlan"):
             sig("mncclGemmPlan", None, i32, i32, i32, i32, C.POINTER(C.c_int), C.POINTER(C.c_int))
+    if hasattr(L, "mncclSwiGluBf16"):
+        sig("mncclSwiGluBf16", i32, vp, vp, i32, i32, C.c_long, C.c_long, vp)
     if hasattr(L, "mncclGemmReduceScatterBf16"):
         sig("mncclGemmRsStageBytes", sz, i32, i32, i32)
         sig("mncclGemmRsFlagWords", sz, i32, i32, i32)

@@ -46,7 +46,7 @@ CUDA_SOURCES = [
     "kernels/launch.cu", "emu/emu_world.cu",
 ]
 # Optional translation units: compiled when present (later build stages add them).
-OPTIONAL_CUDA = ["kernels/gemm_sm100.cu", "kernels/gemm_fused.cu", "kernels/noalloc.cu"]
+OPTIONAL_CUDA = ["kernels/gemm_sm100.cu", "kernels/gemm_fused.cu", "kernels/noalloc.cu", "kernels/elementwise.cu"]
 OPTIONAL_HOST = ["net/verbs_transport.cc"]
 
 _HERA_SRCS = ["csrc/bootstrap/hera.cc", "csrc/bootstrap/socket.cc", "csrc/core/log.cc"]

@@ -2,3 +2,4 @@
 with the collectives (GEMM -> reduce-scatter, all-gather -> GEMM)."""
 from .gemm import gemm_bf16, gemm_status  # noqa: F401
 from .fused import AllGatherGemm, GemmReduceScatter  # noqa: F401,E402
+from .elementwise import swiglu_bf16  # noqa: F401,E402

@@ -10,9 +10,12 @@ The reference has no model or parallelism code; the shapes are those of the tens
 benchmark configuration (Llama-3-8B: H = 4096, F = 14336, TP = 8, 4096 tokens)."""
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.nn.functional as F
 
+from ..ops.elementwise import swiglu_bf16
 from ..ops.fused import AllGatherGemm, GemmReduceScatter
 
 
@@ -31,6 +34,9 @@ class TensorParallelMLP:
         self.gemm_rs = GemmReduceScatter(comm, tokens, hidden)
         self._h = torch.empty(tokens, 2 * self.ffn_local, dtype=torch.bfloat16, device="cuda")
         self._act = torch.empty(tokens, self.ffn_local, dtype=torch.bfloat16, device="cuda")
+        # SwiGLU between the two fused kernels: the library's one-pass kernel (MINI_NCCL_TP_FUSED_SWIGLU=1)
+        # or the framework's silu and mul (default)
+        self.fused_swiglu = os.environ.get("MINI_NCCL_TP_FUSED_SWIGLU", "0") == "1" and self.ffn_local % 8 == 0
 
     @property
     def input_shard(self):
@@ -39,8 +45,11 @@ class TensorParallelMLP:
 
     def forward(self, out=None):
         h = self.ag_gemm(self.w_gate_up, out=self._h)
-        gate, up = h[:, :self.ffn_local], h[:, self.ffn_local:]
-        torch.mul(F.silu(gate), up, out=self._act)
+        if self.fused_swiglu:
+            swiglu_bf16(h, out=self._act)  # one pass, one rounding
+        else:
+            gate, up = h[:, :self.ffn_local], h[:, self.ffn_local:]
+            torch.mul(F.silu(gate), up, out=self._act)
         return self.gemm_rs(self._act, self.w_down, out=out)
 
     def forward_unfused(self, x_shard, group=None):
