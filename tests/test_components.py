@@ -189,3 +189,14 @@ def test_gemm_host_plan_picks_tiles_and_cta_pairs():
         assert gemm_plan(128, 4096)[1] is False          # pinned on, but the shape has no pair tile
     finally:
         set_pair_mode(-1)
+
+
+def test_swiglu_entry_validates_arguments_before_touching_the_gpu(lib):
+    if not hasattr(lib, "mncclSwiGluBf16"):
+        pytest.skip("library built without csrc/kernels/elementwise.cu")
+    assert lib.mncclSwiGluBf16(None, None, 4, 8, 0, 0, None) == -1      # null pointers
+    assert lib.mncclSwiGluBf16(16, 32, 0, 8, 0, 0, None) == -1          # empty
+    assert lib.mncclSwiGluBf16(16, 32, 4, 6, 0, 0, None) == -2          # F no multiple of 8
+    assert lib.mncclSwiGluBf16(8, 32, 4, 8, 0, 0, None) == -2           # input not 16-byte aligned
+    assert lib.mncclSwiGluBf16(16, 32, 4, 8, 8, 0, None) == -2          # input row stride shorter than 2F
+    assert lib.mncclSwiGluBf16(16, 32, 4, 8, 0, 4, None) == -2          # output row stride no multiple of 8
