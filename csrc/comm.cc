@@ -81,6 +81,51 @@ MemKind classify(const void* p, bool has_gpu) {
 
 }  // namespace
 
+std::vector<size_t> pipeline_chunks(size_t count, size_t elem_bytes, size_t uniform_elems, size_t cap_elems, bool taper) {
+  std::vector<size_t> out;
+  if (count == 0) return out;
+  const size_t kAlign = 4096;
+  if (uniform_elems < kAlign) uniform_elems = kAlign;
+  uniform_elems &= ~(kAlign - 1);
+  const size_t total_bytes = count * elem_bytes;
+  if (!taper || total_bytes < (size_t(128) << 20) || cap_elems < 2 * kAlign) {
+    for (size_t off = 0; off < count; off += uniform_elems) out.push_back(std::min(uniform_elems, count - off));
+    return out;
+  }
+  size_t edge_bytes = std::min<size_t>(std::max<size_t>(total_bytes / 8, size_t(8) << 20), size_t(32) << 20);
+  size_t edge = (edge_bytes / elem_bytes) & ~(kAlign - 1);
+  const size_t cap = cap_elems & ~(kAlign - 1);
+  if (edge > cap) edge = cap;
+  if (edge == 0 || 2 * edge >= count) {
+    for (size_t off = 0; off < count; off += uniform_elems) out.push_back(std::min(uniform_elems, count - off));
+    return out;
+  }
+  out.push_back(edge);
+  size_t left = count - 2 * edge;        // what the large chunks carry; the last small chunk takes the ragged end
+  const size_t n_mid = (left + cap - 1) / cap;
+  size_t mid = ((left + n_mid - 1) / n_mid + kAlign - 1) & ~(kAlign - 1);  // equal large chunks
+  if (mid > cap) mid = cap;
+  while (left > 0) {
+    const size_t n = std::min(mid, left);
+    if (n < mid && (n & (kAlign - 1)) != 0) {
+      // a ragged piece in the middle would break the alignment of what follows: give it to the tail
+      const size_t whole = n & ~(kAlign - 1);
+      if (whole) out.push_back(whole);
+      left -= whole;
+      break;
+    }
+    out.push_back(n);
+    left -= n;
+  }
+  out.push_back(edge + left);            // last chunk: small, plus the ragged remainder (< 4096 elements)
+  if (out.back() > cap) {                // cannot happen with edge <= cap - 4096; keep the invariant anyway
+    const size_t extra = out.back() - cap;
+    out.back() = cap;
+    out.push_back(extra);
+  }
+  return out;
+}
+
 Comm* Comm::create(int nranks, int rank, const char* ip) {
   std::unique_ptr<Comm> c(new Comm());
   c->init(nranks, rank, ip);
@@ -591,6 +636,8 @@ void Comm::launch_pipelined(const void* send, DType send_t, void* recv, DType re
   chunk = std::min(chunk, half / std::max(wsz, osz));
   chunk &= ~size_t(4095);
   if (chunk == 0) fail(Result::InternalError, "staging too small for the chunk pipeline");
+  const std::vector<size_t> chunks = pipeline_chunks(count, wsz, chunk, (half / std::max(wsz, osz)) & ~size_t(4095),
+                                                     cfg_.pipeline_taper && !host_in && !host_out);
   const bool is_float = send_t != DType::Int8 && send_t != DType::Uint8 && send_t != DType::Int32 &&
                         send_t != DType::Uint32 && send_t != DType::Int64 && send_t != DType::Uint64;
   const double factor = scale * (op == RedOp::Avg ? 1.0 / static_cast<double>(size_) : 1.0);
@@ -621,9 +668,9 @@ void Comm::launch_pipelined(const void* send, DType send_t, void* recv, DType re
   RT_CHECK(cudaStreamWaitEvent(pipe_->s_in, pipe_->ev_start, 0), "cudaStreamWaitEvent");
   RT_CHECK(cudaStreamWaitEvent(pipe_->s_out, pipe_->ev_start, 0), "cudaStreamWaitEvent");
   size_t i = 0;
-  for (size_t off = 0; off < count; off += chunk, ++i) {
+  for (size_t off = 0; i < chunks.size(); off += chunks[i], ++i) {
     const int h = static_cast<int>(i & 1);
-    const size_t n = std::min(chunk, count - off);
+    const size_t n = chunks[i];
     char* a_h = dev_.ctrl[rank_] + dev_.off_stage_a + h * half;
     char* b_h = dev_.ctrl[rank_] + dev_.off_stage_b + h * half;
     // copy-in (after the collective that last read this half)

@@ -103,6 +103,7 @@ Config Config::from_getter(Getter get, void* ctx) {
   r.str("MINI_NCCL_JOB_ID", c.job_id);
   r.boolean("MINI_NCCL_BLOCKING", c.blocking);
   r.boolean("MINI_NCCL_PIPELINE_COPY_ENGINE", c.pipeline_copy_engine);
+  r.boolean("MINI_NCCL_PIPELINE_TAPER", c.pipeline_taper);
   r.boolean("MINI_NCCL_AUTO_DEVICE", c.auto_device);
 
   if (c.bootstrap_port <= 0 || c.bootstrap_port > 65535) fail(Result::InvalidArgument, "MINI_NCCL_BOOTSTRAP_PORT out of range");

@@ -16,6 +16,7 @@
 #include "bootstrap/fdpass.h"
 #include "bootstrap/hera.h"
 #include "bootstrap/store.h"
+#include "comm.h"
 #include "core/config.h"
 #include "core/error.h"
 #include "core/log.h"
@@ -102,6 +103,20 @@ MNCCL_EXPORT int mnccl_test_config(const char* env, char* out, size_t len) {
     copy_out(o.str(), out, len);
     return 0;
   });
+}
+
+// ---- chunk schedule of the pipeline -------------------------------------------
+// Writes up to `max` chunk sizes (elements) to `out`; returns the number of chunks or a negative code.
+MNCCL_EXPORT int mnccl_test_pipeline_chunks(size_t count, size_t elem_bytes, size_t uniform_elems, size_t cap_elems, int taper,
+                                            size_t* out, int max) {
+  int n = -1;
+  int rc = guarded([&] {
+    std::vector<size_t> c = pipeline_chunks(count, elem_bytes, uniform_elems, cap_elems, taper != 0);
+    n = static_cast<int>(c.size());
+    for (int i = 0; i < n && i < max; ++i) out[i] = c[i];
+    return 0;
+  });
+  return rc == 0 ? n : -rc;
 }
 
 // ---- SPSC queue -----------------------------------------------------------

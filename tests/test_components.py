@@ -200,3 +200,43 @@ def test_swiglu_entry_validates_arguments_before_touching_the_gpu(lib):
     assert lib.mncclSwiGluBf16(8, 32, 4, 8, 0, 0, None) == -2           # input not 16-byte aligned
     assert lib.mncclSwiGluBf16(16, 32, 4, 8, 8, 0, None) == -2          # input row stride shorter than 2F
     assert lib.mncclSwiGluBf16(16, 32, 4, 8, 0, 4, None) == -2          # output row stride no multiple of 8
+
+
+def _chunks(lib, count, elem_bytes, uniform, cap, taper):
+    out = (C.c_size_t * 256)()
+    lib.mnccl_test_pipeline_chunks.restype = C.c_int
+    lib.mnccl_test_pipeline_chunks.argtypes = [C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int, C.POINTER(C.c_size_t), C.c_int]
+    n = lib.mnccl_test_pipeline_chunks(count, elem_bytes, uniform, cap, taper, out, 256)
+    assert 0 <= n <= 256, n
+    return [out[i] for i in range(n)]
+
+
+def test_pipeline_chunk_schedule(lib):
+    import random
+
+    MB = 1 << 20
+    cap = 128 * MB // 4                       # elements of fp32 that fit one half of the staging
+    # the regular schedule: equal chunks, the last one takes the rest
+    assert _chunks(lib, 64 * MB // 4 + 12345, 4, 32 * MB // 4, cap, 0) == [8 * MB, 8 * MB, 12345]
+    assert _chunks(lib, 0, 4, 32 * MB // 4, cap, 0) == []
+    # tapering leaves messages below 128 MB alone
+    assert _chunks(lib, 64 * MB // 4, 4, 32 * MB // 4, cap, 1) == [8 * MB, 8 * MB]
+    # 256 MiB of fp32: 32 MB edges, two equal large chunks between them
+    assert _chunks(lib, 256 * MB // 4, 4, 64 * MB // 4, cap, 1) == [8 * MB, 24 * MB, 24 * MB, 8 * MB]
+    # 1 GiB: the large chunks fill a staging half or nearly so
+    c = _chunks(lib, 1024 * MB // 4, 4, cap, cap, 1)
+    assert c[0] == c[-1] == 8 * MB and len(c) == 10 and max(c) <= cap
+    # invariants on arbitrary sizes and types
+    rng = random.Random(5)
+    for _ in range(300):
+        esz = rng.choice([1, 2, 4, 8])
+        count = rng.randrange(1, (3 << 30) // esz)
+        cap_e = (128 * MB // esz) & ~4095
+        uni = min(max((count // 4) & ~4095, (32 * MB // esz) & ~4095), cap_e)
+        for taper in (0, 1):
+            c = _chunks(lib, count, esz, uni, cap_e, taper)
+            assert sum(c) == count and all(x > 0 for x in c)
+            assert all(x % 4096 == 0 for x in c[:-1]), "every chunk but the last keeps vector alignment of the next"
+            assert max(c) <= cap_e + 4095
+            if taper and count * esz >= 128 * MB and len(c) >= 3:
+                assert c[0] * esz <= 32 * MB and c[-1] * esz <= 32 * MB + 4096 * esz
