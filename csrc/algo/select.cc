@@ -169,4 +169,50 @@ Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
   return p;
 }
 
+std::vector<size_t> pipeline_chunks(size_t count, size_t elem_bytes, size_t uniform_elems, size_t cap_elems, bool taper) {
+  std::vector<size_t> out;
+  if (count == 0) return out;
+  const size_t kAlign = 4096;
+  if (uniform_elems < kAlign) uniform_elems = kAlign;
+  uniform_elems &= ~(kAlign - 1);
+  const size_t total_bytes = count * elem_bytes;
+  if (!taper || total_bytes < (size_t(128) << 20) || cap_elems < 2 * kAlign) {
+    for (size_t off = 0; off < count; off += uniform_elems) out.push_back(std::min(uniform_elems, count - off));
+    return out;
+  }
+  size_t edge_bytes = std::min<size_t>(std::max<size_t>(total_bytes / 8, size_t(8) << 20), size_t(32) << 20);
+  size_t edge = (edge_bytes / elem_bytes) & ~(kAlign - 1);
+  const size_t cap = cap_elems & ~(kAlign - 1);
+  if (edge > cap) edge = cap;
+  if (edge == 0 || 2 * edge >= count) {
+    for (size_t off = 0; off < count; off += uniform_elems) out.push_back(std::min(uniform_elems, count - off));
+    return out;
+  }
+  out.push_back(edge);
+  size_t left = count - 2 * edge;        // what the large chunks carry; the last small chunk takes the ragged end
+  const size_t n_mid = (left + cap - 1) / cap;
+  size_t mid = ((left + n_mid - 1) / n_mid + kAlign - 1) & ~(kAlign - 1);  // equal large chunks
+  if (mid > cap) mid = cap;
+  while (left > 0) {
+    const size_t n = std::min(mid, left);
+    if (n < mid && (n & (kAlign - 1)) != 0) {
+      // a ragged piece in the middle would break the alignment of what follows: give it to the tail
+      const size_t whole = n & ~(kAlign - 1);
+      if (whole) out.push_back(whole);
+      left -= whole;
+      break;
+    }
+    out.push_back(n);
+    left -= n;
+  }
+  out.push_back(edge + left);            // last chunk: small, plus the ragged remainder (< 4096 elements)
+  if (out.back() > cap) {                // cannot happen with edge <= cap - 4096; keep the invariant anyway
+    const size_t extra = out.back() - cap;
+    out.back() = cap;
+    out.push_back(extra);
+  }
+  return out;
+}
+
+
 }  // namespace mnccl

@@ -6,6 +6,7 @@
 // (MINI_NCCL_ALGO, MINI_NCCL_LL_MAX_BYTES, MINI_NCCL_ONESHOT_MAX_BYTES,
 // MINI_NCCL_NVLS_MIN_BYTES, MINI_NCCL_MAX_BLOCKS).
 #pragma once
+#include <vector>
 #include <cstddef>
 #include <cstdint>
 
@@ -62,5 +63,14 @@ struct Plan {
 Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg);
 
 Algo parse_algo(const std::string& s);
+
+// Element counts of the chunks the pipeline cuts a message of `count` elements into.
+// `uniform_elems`: the regular chunk (a multiple of 4096 elements, > 0).  `taper`: the first and the
+// last chunk are small (an eighth of the message, 8 to 32 MB) so that the copy-in nobody can hide
+// and the copy-out after the last collective are short, and the chunks between them are as large as
+// `cap_elems` allows (large collectives run closer to the link rate).  Every chunk but the last is a
+// multiple of 4096 elements; the sum is `count`.
+std::vector<size_t> pipeline_chunks(size_t count, size_t elem_bytes, size_t uniform_elems, size_t cap_elems, bool taper);
+
 
 }  // namespace mnccl

@@ -38,14 +38,6 @@ struct CommStats {
   uint64_t graph_captures_seen = 0, errors = 0;
 };
 
-// Element counts of the chunks the pipeline cuts a message of `count` elements into.
-// `uniform_elems`: the regular chunk (a multiple of 4096 elements, > 0).  `taper`: the first and the
-// last chunk are small (an eighth of the message, 8 to 32 MB) so that the copy-in nobody can hide
-// and the copy-out after the last collective are short, and the chunks between them are as large as
-// `cap_elems` allows (large collectives run closer to the link rate).  Every chunk but the last is a
-// multiple of 4096 elements; the sum is `count`.
-std::vector<size_t> pipeline_chunks(size_t count, size_t elem_bytes, size_t uniform_elems, size_t cap_elems, bool taper);
-
 class Comm {
  public:
   // rank == -1: Hera auto-bootstrap, `ip` names the master.  Throws Error.
