@@ -105,3 +105,31 @@ def test_init_failure_is_an_error_code_not_an_exception(lib, free_port):
     assert "RC 2" in out.stdout, out.stdout + out.stderr  # ncclSystemError
     assert "Init failed" in out.stderr
     os.environ.pop("MINI_NCCL_CONNECT_RETRIES")
+
+
+def test_public_headers_compile_as_c_and_cpp_and_match_the_library(lib, tmp_path):
+    """include/mini_nccl_api.h and include/mini_nccl_ops.h are self-contained in C and in C++, and every
+    function they declare is exported by the library."""
+    import re
+    import shutil
+    import subprocess
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    cuda_inc = "/usr/local/cuda/include"
+    if not (Path(cuda_inc) / "cuda_runtime.h").exists() or shutil.which("gcc") is None:
+        pytest.skip("needs gcc and the CUDA headers")
+    src = tmp_path / "hdr.c"
+    src.write_text('#include "mini_nccl_api.h"\n#include "mini_nccl_ops.h"\nint main(void) { return 0; }\n')
+    for cc, extra in (("gcc", []), ("g++", ["-x", "c++"])):
+        r = subprocess.run([cc, "-fsyntax-only", "-Wall", "-Werror", *extra, f"-I{root / 'include'}", f"-I{cuda_inc}", str(src)],
+                           capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+    declared = set()
+    for name in ("mini_nccl_api.h", "mini_nccl_ops.h"):
+        text = (root / "include" / name).read_text()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        declared |= set(re.findall(r"\b((?:nccl|mnccl)[A-Za-z0-9]+)\s*\(", text))
+    assert {"ncclAllReduce", "ncclCommInitRank", "mncclGemmBf16", "mncclSwiGluBf16"} <= declared
+    missing = [f for f in sorted(declared) if not hasattr(lib, f)]
+    assert not missing, f"declared but not exported: {missing}"
