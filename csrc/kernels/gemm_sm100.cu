@@ -205,6 +205,41 @@ MNCCL_EXPORT void mncclGemmPlan(int M, int N, int ctas, int narrow, int* tile_n,
   if (pair) *pair = want_pair(M, N, ctas) ? 1 : 0;
 }
 
+// The tiles worker `worker` of `n_workers` visits, in order, exactly as the kernels walk them (host
+// arithmetic only, for tests): single-CTA kernel: worker = CTA, tiles of 128 x bn; pair kernel
+// (`pair` = 1): worker = CTA pair, 256 x 256 tiles, reported as the two 128-row tiles (tm, tm + 1)
+// of its CTAs.  group_m / rotate are the values the entry points put into GemmArgs (in 128-row
+// tiles).  Writes up to `max` (tm, tn) pairs; returns the number of 128-row tiles visited.
+MNCCL_EXPORT int mncclGemmTileOrder(int M, int N, int bn, int group_m, int rotate, int pair, int n_workers, int worker,
+                                    int* out_tm, int* out_tn, int max) {
+  if (M <= 0 || N <= 0 || bn <= 0 || n_workers <= 0 || worker < 0 || worker >= n_workers) return -1;
+  GemmArgs g{};
+  g.M = M;
+  g.N = N;
+  int n = 0;
+  if (pair) {
+    g.group_m = group_m > 1 ? group_m / 2 : 1;          // as gemm2_bf16_kernel derives them
+    g.m_tile_rotate = rotate / 2;
+    const int tiles_m2 = (M + 2 * kBM - 1) / (2 * kBM), tiles_n = (N + kBN - 1) / kBN;
+    for (int t = worker; t < tiles_m2 * tiles_n; t += n_workers) {
+      int tm2, tn;
+      tile_coords(g, t, tiles_m2, tiles_n, &tm2, &tn);
+      for (int cta = 0; cta < 2; ++cta, ++n)
+        if (n < max) { out_tm[n] = tm2 * 2 + cta; out_tn[n] = tn; }
+    }
+  } else {
+    g.group_m = group_m;
+    g.m_tile_rotate = rotate;
+    const int tiles_m = (M + kBM - 1) / kBM, tiles_n = (N + bn - 1) / bn;
+    for (int t = worker; t < tiles_m * tiles_n; t += n_workers, ++n) {
+      int tm, tn;
+      tile_coords(g, t, tiles_m, tiles_n, &tm, &tn);
+      if (n < max) { out_tm[n] = tm; out_tn[n] = tn; }
+    }
+  }
+  return n;
+}
+
 // Reads and clears the GEMM error word of the current device (0 = no bounded
 // wait ever ran out).  Synchronises the device.
 MNCCL_EXPORT int mncclGemmStatus(uint32_t* status) {

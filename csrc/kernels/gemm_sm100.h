@@ -53,7 +53,7 @@ struct GemmArgs {
 // Tile index -> (tm, tn).  m-tiles are visited in groups of `group_m` so that a
 // wave of CTAs reuses the same B tiles from L2; `m_tile_rotate` rotates the
 // m order (fused all-gather: rows that are already local first).
-__device__ __forceinline__ void tile_coords(const GemmArgs& g, int t, int tiles_m, int tiles_n, int* tm, int* tn) {
+__host__ __device__ __forceinline__ void tile_coords(const GemmArgs& g, int t, int tiles_m, int tiles_n, int* tm, int* tn) {
   const int gm = g.group_m > 0 ? g.group_m : 1;
   const int per_group = gm * tiles_n;
   const int group = t / per_group;

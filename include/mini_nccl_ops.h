@@ -37,6 +37,11 @@ void mncclGemmSetPairMode(int mode);
 /* The host-side choice for an M x N product on `ctas` CTAs, without a launch (needs no GPU). */
 void mncclGemmPlan(int M, int N, int ctas, int narrow, int* tile_n, int* pair);
 
+/* The tiles worker `worker` of `n_workers` (CTAs, or CTA pairs with pair = 1) visits, in the kernels'
+ * own order, as (tm, tn) in 128-row tiles; host arithmetic only.  Returns the number of tiles. */
+int mncclGemmTileOrder(int M, int N, int bn, int group_m, int rotate, int pair, int n_workers, int worker, int* out_tm,
+                       int* out_tn, int max);
+
 /* CTA pairs of the pair kernel that the current device holds at once. */
 int mncclGemmMaxPairs(void);
 

@@ -240,3 +240,49 @@ def test_pipeline_chunk_schedule(lib):
             assert max(c) <= cap_e + 4095
             if taper and count * esz >= 128 * MB and len(c) >= 3:
                 assert c[0] * esz <= 32 * MB and c[-1] * esz <= 32 * MB + 4096 * esz
+
+
+def _tile_walk(lib, M, N, bn, group_m, rotate, pair, n_workers):
+    f = lib.mncclGemmTileOrder
+    f.restype = C.c_int
+    f.argtypes = [C.c_int] * 8 + [C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int]
+    walks = []
+    for w in range(n_workers):
+        tm, tn = (C.c_int * 8192)(), (C.c_int * 8192)()
+        n = f(M, N, bn, group_m, rotate, pair, n_workers, w, tm, tn, 8192)
+        assert 0 <= n <= 8192
+        walks.append([(tm[i], tn[i]) for i in range(n)])
+    return walks
+
+
+@pytest.mark.parametrize("pair", [0, 1])
+@pytest.mark.parametrize("nranks,rank", [(1, 0), (2, 1), (8, 2), (8, 7)])
+def test_gemm_tile_walk_covers_every_tile_once_in_owner_order(lib, pair, nranks, rank):
+    """The tile order of the fused kernels, computed by the kernels' own index arithmetic on the host:
+    every 128-row tile exactly once, work spread evenly, GEMM -> reduce-scatter visits the owners
+    starting with the next rank and its own rows last, all-gather -> GEMM starts with the local rows."""
+    if not hasattr(lib, "mncclGemmTileOrder"):
+        pytest.skip("library built without the GEMM translation unit")
+    M, N, bn = 4096, 3584 if pair else 4096, 256
+    tiles_m, tiles_n = M // 128, (N + bn - 1) // bn
+    local = tiles_m // nranks
+    n_workers = 56 if pair else 132
+    for name, rotate in (("reduce-scatter", ((rank + 1) % nranks) * local), ("all-gather", rank * local)):
+        walks = _tile_walk(lib, M, N, bn, local, rotate, pair, n_workers)
+        flat = [t for w in walks for t in w]
+        assert sorted(flat) == sorted((m, n) for m in range(tiles_m) for n in range(tiles_n)), name
+        sizes = [len(w) for w in walks]
+        assert max(sizes) - min(sizes) <= (2 if pair else 1), name
+        # global order = round-robin over the workers; the owner of a tile is tm // local
+        step = 2 if pair else 1
+        order = []
+        for k in range(0, max(sizes), step):
+            for w in walks:
+                order.extend(w[k:k + step])
+        owners = [tm // local for tm, _ in order]
+        seen = []
+        for o in owners:
+            if not seen or seen[-1] != o:
+                seen.append(o)
+        first = (rank + 1) % nranks if name == "reduce-scatter" else rank
+        assert seen == [(first + i) % nranks for i in range(nranks)], (name, seen)
