@@ -27,8 +27,8 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank, n, port, sizes, iters, warmup, q):
-    os.environ["MINI_NCCL_TRANSPORT"] = "soft"
+def _worker(rank, n, port, sizes, iters, warmup, q, transport):
+    os.environ["MINI_NCCL_TRANSPORT"] = transport
     os.environ["MINI_NCCL_BOOTSTRAP_PORT"] = str(port)
     import numpy as np
 
@@ -65,12 +65,14 @@ def main():
     ap.add_argument("--sizes-mib", type=float, nargs="+", default=[1, 4, 16, 64, 128])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--transport", default="soft", choices=["soft", "verbs"],
+                    help="verbs needs a library built with libibverbs (or the test stand-in: MINI_NCCL_LIB)")
     args = ap.parse_args()
     sizes = [int(s * (1 << 20)) for s in args.sizes_mib]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, args.ranks, port, sizes, args.iters, args.warmup, q)) for r in range(args.ranks)]
+    procs = [ctx.Process(target=_worker, args=(r, args.ranks, port, sizes, args.iters, args.warmup, q, args.transport)) for r in range(args.ranks)]
     for p in procs:
         p.start()
     got = [q.get(timeout=600) for _ in procs]
@@ -85,7 +87,7 @@ def main():
         bus = alg * 2 * (n - 1) / n
         print(f"{nbytes:>12} {t * 1e6:>12.1f} {alg:>12.3f} {bus:>12.3f}")
         out.append({"bytes": nbytes, "us": round(t * 1e6, 1), "algbw_GBps": round(alg, 3), "busbw_GBps": round(bus, 3)})
-    print(json.dumps({"ranks": n, "provider": "soft (TCP loopback)", "rows": out}))
+    print(json.dumps({"ranks": n, "provider": args.transport, "rows": out}))
 
 
 if __name__ == "__main__":

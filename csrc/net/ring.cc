@@ -141,12 +141,18 @@ void RingAllReduce::run(void* data, size_t count, DType dtype, RedOp op) {
     const size_t ns_send = (send_len + slice_elems - 1) / slice_elems;
     const size_t ns_recv = (recv_len + slice_elems - 1) / slice_elems;
     const size_t ns = std::max(ns_send, ns_recv);
+    // Sends run a few slices ahead of the receives (never more than half the scratch slots), so
+    // that the peer always has a slice to work on instead of one slice per round trip.  The chunk
+    // sent in a step was completed in the step before, so sending ahead reads final data.
+    const size_t ahead = std::min<size_t>(4, static_cast<size_t>(nslots_) / 2);
+    size_t sent = 0;
     for (size_t s = 0; s < ns; ++s) {
-      if (s < ns_send) {
-        size_t off = s * slice_elems;
+      while (sent < ns_send && sent <= s + ahead) {
+        size_t off = sent * slice_elems;
         size_t ne = std::min(slice_elems, send_len - off);
-        bool signaled = (s % static_cast<size_t>(cfg_.signal_batch) == 0) || (s + 1 == ns_send);
+        bool signaled = (sent % static_cast<size_t>(cfg_.signal_batch) == 0) || (sent + 1 == ns_send);
         send_slice(bytes + (chunk_off(send_chunk) + off) * esz, *mr, ne * esz, signaled);
+        ++sent;
       }
       if (s < ns_recv) {
         size_t off = s * slice_elems;

@@ -1,8 +1,15 @@
 #include "net/soft_transport.h"
 
+#include <chrono>
 #include <cstdlib>
 #include <cstring>
 #include <poll.h>
+#include <sys/uio.h>
+#include <unistd.h>
+
+#include <fstream>
+#include <functional>
+#include <string>
 
 #include "bootstrap/store.h"
 #include "core/config.h"
@@ -29,6 +36,25 @@ struct Hello {
   uint32_t magic;
   int32_t rank;
 };
+struct CmaInfo {      // what a rank tells the others about its address space
+  uint64_t host_id;   // same value = same boot of the same host and the same pid namespace
+  uint64_t table_addr;
+  int32_t pid;
+  int32_t enabled;
+};
+
+uint64_t cma_host_id() {
+  std::string key;
+  char name[256] = {0};
+  if (gethostname(name, sizeof(name) - 1) == 0) key += name;
+  std::ifstream boot("/proc/sys/kernel/random/boot_id");
+  std::string line;
+  if (boot && std::getline(boot, line)) key += line;
+  char buf[128];
+  ssize_t n = readlink("/proc/self/ns/pid", buf, sizeof(buf) - 1);
+  if (n > 0) key.append(buf, static_cast<size_t>(n));
+  return std::hash<std::string>{}(key) | 1ull;
+}
 }  // namespace
 
 SoftTransport::Region::~Region() {
@@ -39,6 +65,8 @@ SoftTransport::SoftTransport(int rank, int size) : rank_(rank), size_(size) {
   timeout_ms_ = Config::get().socket_timeout_ms;
   flags_.reset(new uint32_t[kNumFlags]);
   memset(flags_.get(), 0, sizeof(uint32_t) * kNumFlags);
+  table_.reset(new KeyTable());
+  memset(table_.get(), 0, sizeof(KeyTable));
   if (const char* e = std::getenv("MINI_NCCL_SOFT_DROP_FLAG_AT")) drop_at_.store(std::strtoull(e, nullptr, 10));
 }
 
@@ -79,6 +107,23 @@ void SoftTransport::connect(BootstrapStore& store) {
         fail(Result::SystemError, "soft transport: unexpected peer hello");
       socks_[h.rank] = std::move(s);
     }
+    // Same-host fast path: who shares this host's memory, and may we touch it?
+    const char* env = std::getenv("MINI_NCCL_SOFT_CMA");
+    CmaInfo mine{cma_host_id(), reinterpret_cast<uint64_t>(table_.get()), static_cast<int32_t>(getpid()),
+                 (env && env[0] == '0') ? 0 : 1};
+    std::vector<CmaInfo> infos(size_);
+    store.all_gather(&mine, infos.data(), sizeof(mine));
+    cma_.assign(size_, CmaPeer());
+    int n_cma = 0;
+    for (int p = 0; p < size_; ++p) {
+      if (p == rank_ || !mine.enabled || !infos[p].enabled || infos[p].host_id != mine.host_id) continue;
+      cma_[p].pid = infos[p].pid;
+      cma_[p].table_addr = infos[p].table_addr;
+      cma_[p].ok = true;
+      if (!cma_refresh(cma_[p])) cma_[p].ok = false;  // the probe: not permitted here (ptrace policy) -> sockets
+      if (cma_[p].ok) ++n_cma;
+    }
+    if (n_cma) MNCCL_INFO("Mini-NCCL", "soft transport: cross-memory attach to %d same-host peer(s)", n_cma);
     store.barrier();
   }
   run_.store(true);
@@ -95,6 +140,7 @@ std::shared_ptr<MemoryRegion> SoftTransport::register_memory(void* ptr, size_t s
     std::lock_guard<std::mutex> lk(key_mu_);
     r->lkey = r->rkey = next_key_++;
     keys_[r->rkey] = {reinterpret_cast<uintptr_t>(base), sz};
+    table_add(r->rkey, reinterpret_cast<uintptr_t>(base), sz);
     return std::static_pointer_cast<MemoryRegion>(r);
   });
   if (cache_.misses() != before) stats_.reg_misses++; else stats_.reg_hits++;
@@ -106,6 +152,86 @@ void SoftTransport::invalidate(void* ptr, size_t size) { cache_.invalidate(ptr, 
 void SoftTransport::unregister_key(uint32_t rkey) {
   std::lock_guard<std::mutex> lk(key_mu_);
   keys_.erase(rkey);
+  table_remove(rkey);
+}
+
+// ---- same-host fast path ------------------------------------------------------------------------
+
+// Callers hold key_mu_.  Entry fields are written before the key that makes the entry valid, and a
+// key is only handed to a peer after the registration returned, so a reader never needs a lock.
+void SoftTransport::table_add(uint32_t rkey, uintptr_t base, size_t size) {
+  KeyTable* t = table_.get();
+  const uint32_t cap = static_cast<uint32_t>(sizeof(t->entry) / sizeof(t->entry[0]));
+  uint32_t slot = t->count;
+  for (uint32_t i = 0; i < t->count; ++i)
+    if (__atomic_load_n(&t->entry[i].rkey, __ATOMIC_RELAXED) == 0) { slot = i; break; }
+  if (slot >= cap) return;  // table full: writes with this key fall back to the socket (key not found)
+  t->entry[slot].base = base;
+  t->entry[slot].size = size;
+  __atomic_store_n(&t->entry[slot].rkey, rkey, __ATOMIC_RELEASE);
+  if (slot == t->count) __atomic_store_n(&t->count, t->count + 1, __ATOMIC_RELEASE);
+}
+
+void SoftTransport::table_remove(uint32_t rkey) {
+  KeyTable* t = table_.get();
+  for (uint32_t i = 0; i < t->count; ++i)
+    if (t->entry[i].rkey == rkey) {
+      __atomic_store_n(&t->entry[i].rkey, 0u, __ATOMIC_RELEASE);
+      __atomic_store_n(&t->generation, t->generation + 1, __ATOMIC_RELEASE);
+      return;
+    }
+}
+
+bool SoftTransport::cma_read(const CmaPeer& p, uint64_t remote_addr, void* dst, size_t len) const {
+  size_t done = 0;
+  while (done < len) {
+    struct iovec l{static_cast<char*>(dst) + done, len - done};
+    struct iovec r{reinterpret_cast<void*>(remote_addr + done), len - done};
+    ssize_t n = process_vm_readv(p.pid, &l, 1, &r, 1, 0);
+    if (n <= 0) return false;
+    done += static_cast<size_t>(n);
+  }
+  return true;
+}
+
+// Fetch the peer's region table (header first, then the live entries) into the cache.
+bool SoftTransport::cma_refresh(CmaPeer& p) {
+  struct { uint64_t generation; uint32_t count, pad; } head;
+  if (!cma_read(p, p.table_addr, &head, sizeof(head))) return false;
+  const uint32_t cap = static_cast<uint32_t>(sizeof(KeyTable::entry) / sizeof(KeyEntry));
+  if (head.count > cap) return false;
+  std::vector<KeyEntry> entries(head.count);
+  if (head.count && !cma_read(p, p.table_addr + offsetof(KeyTable, entry), entries.data(), sizeof(KeyEntry) * head.count))
+    return false;
+  p.keys.clear();
+  for (const KeyEntry& e : entries)
+    if (e.rkey != 0) p.keys[e.rkey] = {e.base, e.size};
+  p.generation = head.generation;
+  return true;
+}
+
+int SoftTransport::cma_write(int peer, const void* local, uint32_t rkey, uint64_t addr, size_t len) {
+  CmaPeer& p = cma_[peer];
+  // A removed region bumps the generation: one 8-byte read tells whether the cached table is current.
+  uint64_t gen = 0;
+  if (!cma_read(p, p.table_addr, &gen, sizeof(gen))) return -1;
+  auto it = p.keys.find(rkey);
+  if (gen != p.generation || it == p.keys.end()) {
+    if (!cma_refresh(p)) return -1;
+    it = p.keys.find(rkey);
+  }
+  if (it == p.keys.end()) return 0;
+  const uint64_t base = it->second.first, size = it->second.second;
+  if (addr < base || addr + len > base + size || addr + len < addr) return 0;
+  size_t done = 0;
+  while (done < len) {
+    struct iovec l{const_cast<char*>(static_cast<const char*>(local)) + done, len - done};
+    struct iovec r{reinterpret_cast<void*>(addr + done), len - done};
+    ssize_t n = process_vm_writev(p.pid, &l, 1, &r, 1, 0);
+    if (n <= 0) return done == 0 ? -1 : 0;  // nothing moved: try the socket; partly moved: report an error
+    done += static_cast<size_t>(n);
+  }
+  return 1;
 }
 
 void SoftTransport::send_frame(int peer, uint32_t kind, uint32_t rkey, uint32_t value, uint64_t addr,
@@ -128,8 +254,27 @@ Request* SoftTransport::write(int peer, const void* local, const MemoryRegion& l
     req = pool_.acquire(stats_.writes.load());
     if (!req) fail(Result::InternalError, "request pool exhausted");
   }
+  int status = 0;
   try {
-    send_frame(peer, kWrite, remote.rkey, 0, remote.addr + remote_offset, local, len);
+    int fast = -1;
+    if (len && peer >= 0 && peer < static_cast<int>(cma_.size()) && cma_[peer].ok) {
+      if (aborted()) fail(Result::InternalError, "transport aborted");
+      std::lock_guard<std::mutex> lk(*send_mu_[peer]);  // the cached table copy belongs to one poster at a time
+      fast = cma_write(peer, local, remote.rkey, remote.addr + remote_offset, len);
+      if (fast < 0) cma_[peer].ok = false;              // not permitted after all: sockets from now on
+    }
+    if (fast == 1) {
+      cma_writes_++;
+      stats_.direct_writes++;
+    } else if (fast == 0) {
+      // what the receiver's check would have found: a remote access error, seen by the poster
+      access_errors_++;
+      stats_.completion_errors++;
+      status = 10;
+      MNCCL_WARN("Mini-NCCL", "soft transport: write to rank %d rejected (bad key or range)", peer);
+    } else {
+      send_frame(peer, kWrite, remote.rkey, 0, remote.addr + remote_offset, local, len);
+    }
   } catch (...) {
     if (req) pool_.release(req);
     throw;
@@ -138,7 +283,7 @@ Request* SoftTransport::write(int peer, const void* local, const MemoryRegion& l
   stats_.bytes_written += len;
   if (req) {
     stats_.signaled++;
-    req->complete(0);
+    req->complete(status);
     reaped_.fetch_add(1);
   }
   return req;
@@ -219,6 +364,7 @@ bool SoftTransport::handle_frame(int peer) {
 void SoftTransport::nic_loop() {
   std::vector<struct pollfd> fds;
   std::vector<int> who;
+  auto last_frame = std::chrono::steady_clock::now() - std::chrono::seconds(1);
   while (run_.load()) {
     fds.clear();
     who.clear();
@@ -232,8 +378,16 @@ void SoftTransport::nic_loop() {
       std::this_thread::sleep_for(std::chrono::milliseconds(20));
       continue;
     }
-    int r = ::poll(fds.data(), fds.size(), 20);
-    if (r <= 0) continue;
+    // While frames keep coming the thread looks again at once: waking a sleeping thread costs more
+    // than a whole slice takes.  After kSpinUs without traffic it blocks in poll() again.
+    constexpr int kSpinUs = 100;
+    int r = ::poll(fds.data(), fds.size(), 0);
+    if (r <= 0) {
+      if (std::chrono::steady_clock::now() - last_frame < std::chrono::microseconds(kSpinUs)) continue;
+      r = ::poll(fds.data(), fds.size(), 20);
+      if (r <= 0) continue;
+    }
+    last_frame = std::chrono::steady_clock::now();
     for (size_t i = 0; i < fds.size(); ++i) {
       if (!(fds[i].revents & (POLLIN | POLLHUP | POLLERR))) continue;
       try {

@@ -7,6 +7,15 @@
 // flag" guarantee that the reference takes from RC queue pairs (reference:
 // src/transport/RDMATransport.h:259-311).  Works between hosts as well as on
 // loopback, needs no RDMA hardware, and is the provider the CPU tests use.
+//
+// Same-host fast path: when a peer runs on this host (same boot, same pid namespace) and the kernel
+// permits it, the PAYLOAD of a write goes straight into the peer's memory with process_vm_writev
+// (cross-memory attach: one copy instead of two through a socket), after the sender has checked key
+// and range against a copy of the peer's region table.  Flags still travel as frames, after the
+// payload is in place, so the receiver's release store and the ordering are unchanged.
+// MINI_NCCL_SOFT_CMA=0 switches the fast path off.  (The reference's same-host path is CUDA IPC,
+// reference: src/transport/RDMATransport.h:583-590; between processes without a GPU this is its
+// counterpart.)
 #pragma once
 #include <atomic>
 #include <map>
@@ -45,6 +54,8 @@ class SoftTransport : public OneSidedTransport {
   // the next one: flags are monotonic counters.)
   void drop_flag_write_at(uint64_t n) { drop_at_.store(n); flag_posts_.store(0); }
   uint64_t remote_access_errors() const { return access_errors_.load(); }
+  uint64_t cma_writes() const { return cma_writes_.load(); }
+  bool cma_enabled(int peer) const { return peer >= 0 && peer < static_cast<int>(cma_.size()) && cma_[peer].ok; }
 
  private:
   struct Region : MemoryRegion {
@@ -70,6 +81,33 @@ class SoftTransport : public OneSidedTransport {
   std::map<uint32_t, std::pair<uintptr_t, size_t>> keys_;
   uint32_t next_key_ = 0x1000;
   RegistrationCache<MemoryRegion> cache_{4096};
+
+  // ---- same-host fast path (cross-memory attach)
+  struct KeyEntry {            // one registered region, as peers read it
+    uint64_t base, size;
+    uint32_t rkey, pad;
+  };
+  struct KeyTable {            // lives at a fixed address for the life of the transport
+    uint64_t generation;       // bumped whenever an entry is removed
+    uint32_t count, pad;       // entries [0, count) may be valid (rkey != 0)
+    KeyEntry entry[4096 + 64];
+  };
+  struct CmaPeer {
+    bool ok = false;
+    int pid = 0;
+    uint64_t table_addr = 0;
+    uint64_t generation = ~0ull;                              // of the cached copy
+    std::map<uint32_t, std::pair<uint64_t, uint64_t>> keys;   // cached: rkey -> (base, size)
+  };
+  bool cma_read(const CmaPeer& p, uint64_t remote_addr, void* dst, size_t len) const;
+  bool cma_refresh(CmaPeer& p);
+  // 1: written; 0: rejected (bad key or range); -1: the fast path failed, use the socket
+  int cma_write(int peer, const void* local, uint32_t rkey, uint64_t addr, size_t len);
+  void table_add(uint32_t rkey, uintptr_t base, size_t size);
+  void table_remove(uint32_t rkey);
+  std::unique_ptr<KeyTable> table_;
+  std::vector<CmaPeer> cma_;
+  std::atomic<uint64_t> cma_writes_{0};
 
   std::atomic<bool> run_{false};
   std::thread nic_;

@@ -73,7 +73,9 @@ void VerbsTransport::connect(BootstrapStore& store) {
   flags_remote_.rkey = flags_mr_->rkey;
   qps_.assign(size_, nullptr);
   unsignaled_.assign(size_, 0);
-  in_flight_.assign(size_, 0);
+  posted_.assign(size_, 0);
+  retired_.assign(size_, 0);
+  signaled_at_.assign(size_, std::deque<uint64_t>());
   ibv_port_attr pattr;
   memset(&pattr, 0, sizeof(pattr));
   if (ibv_query_port(ctx_, port_, &pattr) != 0) fail(Result::SystemError, "ibv_query_port failed");
@@ -195,13 +197,14 @@ void VerbsTransport::post(int peer, ibv_send_wr* wr, bool* signaled_out) {
   }
   if (signaled) unsignaled_[peer] = 0;
   auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms_);
-  while (in_flight_[peer] >= kSendDepth - 8) {
+  while (posted_[peer] - retired_[peer] >= static_cast<uint64_t>(kSendDepth - 8)) {
     poll();
     if (std::chrono::steady_clock::now() > deadline) fail(Result::InternalError, "verbs: send queue stayed full");
   }
   ibv_send_wr* bad = nullptr;
   if (ibv_post_send(qps_[peer], wr, &bad) != 0) fail(Result::SystemError, "ibv_post_send failed");
-  ++in_flight_[peer];
+  ++posted_[peer];
+  if (signaled) signaled_at_[peer].push_back(posted_[peer]);
   if (signaled_out) *signaled_out = signaled;
 }
 
@@ -280,7 +283,10 @@ int VerbsTransport::poll() {
     if (status != 0) stats_.completion_errors++;
     // A signalled completion retires every earlier work request of its queue pair.
     for (int p = 0; p < size_; ++p)
-      if (qps_[p] && qps_[p]->qp_num == wc[i].qp_num) in_flight_[p] = 0;
+      if (qps_[p] && qps_[p]->qp_num == wc[i].qp_num && !signaled_at_[p].empty()) {
+        retired_[p] = signaled_at_[p].front();
+        signaled_at_[p].pop_front();
+      }
     if (wc[i].wr_id & 1ull) reinterpret_cast<Request*>(wc[i].wr_id & ~1ull)->complete(status);
     else if (status != 0) MNCCL_WARN("Mini-NCCL", "verbs: work request failed with status %d", status);
   }

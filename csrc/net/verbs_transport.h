@@ -10,6 +10,7 @@
 #pragma once
 #include <infiniband/verbs.h>
 
+#include <deque>
 #include <mutex>
 #include <vector>
 
@@ -65,7 +66,12 @@ class VerbsTransport : public OneSidedTransport {
   ibv_cq* cq_ = nullptr;
   std::vector<ibv_qp*> qps_;
   std::vector<int> unsignaled_;     // per peer, since the last signalled post
-  std::vector<int> in_flight_;      // per peer, posted and not yet known complete
+  // Send-queue accounting per peer.  A polled completion retires its own request and every earlier
+  // one of the queue pair, not the ones posted after it: requests in flight = posted - retired.
+  // Completions of one reliable-connected queue pair arrive in posting order, so a FIFO of the
+  // post indices of the signalled requests tells which index a completion stands for.
+  std::vector<uint64_t> posted_, retired_;
+  std::vector<std::deque<uint64_t>> signaled_at_;
   std::mutex post_mu_;
   uint8_t port_ = 1;
   int gid_index_ = 1;

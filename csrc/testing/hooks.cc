@@ -2,7 +2,9 @@
 // (ctypes).  They are thin: each one drives a component the way its users do
 // and reports what happened.  Nothing here is on a hot path.
 #include <atomic>
+#include <chrono>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <memory>
@@ -117,6 +119,80 @@ MNCCL_EXPORT int mnccl_test_pipeline_chunks(size_t count, size_t elem_bytes, siz
     return 0;
   });
   return rc == 0 ? n : -rc;
+}
+
+// ---- soft provider: key and range checks ------------------------------------------
+// Two ranks as threads.  Rank 0 posts a write with a wrong key, a write that runs past the region,
+// then a good write and a flag; rank 1 must end up with exactly the good payload and the two bad
+// writes must be counted as remote access errors (by the receiver over sockets, by the poster on
+// the cross-memory-attach path, where a signalled request also completes with an error status).
+// Returns 0 when all of that holds, otherwise a code that names the first failed check.
+MNCCL_EXPORT int mnccl_test_soft_reject(int port, int cma) {
+  const char* old_env = getenv("MINI_NCCL_SOFT_CMA");
+  const std::string saved = old_env ? old_env : "";
+  const bool had = old_env != nullptr;
+  setenv("MINI_NCCL_SOFT_CMA", cma ? "1" : "0", 1);
+  std::atomic<int> verdict{0};
+  std::atomic<uint64_t> errors_seen{0};
+  std::atomic<int> used_cma{0};
+  auto set = [&](int code) { int zero = 0; verdict.compare_exchange_strong(zero, code); };
+  std::vector<std::thread> th;
+  for (int r = 0; r < 2; ++r) {
+    th.emplace_back([&, r] {
+      try {
+        BootstrapStore store(r, 2, "127.0.0.1", port, 10000, 50);
+        store.connect();
+        SoftTransport t(r, 2);
+        t.connect(store);
+        std::vector<uint32_t> region(1024, 0xAAAAAAAAu);   // 4 KB target on rank 1, source on rank 0
+        auto mr = t.register_memory(region.data(), region.size() * 4);
+        RemoteBuffer mine;
+        mine.addr = reinterpret_cast<uint64_t>(region.data());
+        mine.rkey = mr->rkey;
+        RemoteBuffer all[2], flags[2];
+        store.all_gather(&mine, all, sizeof(mine));
+        RemoteBuffer myflags = t.flags_remote();
+        store.all_gather(&myflags, flags, sizeof(myflags));
+        if (r == 0) {
+          for (auto& w : region) w = 0x12345678u;
+          if (t.cma_enabled(1)) used_cma.store(1);
+          RemoteBuffer bad = all[1];
+          bad.rkey ^= 0x5a5a;
+          Request* a = t.write(1, region.data(), *mr, bad, 0, 256, true);            // wrong key
+          Request* b = t.write(1, region.data(), *mr, all[1], 4096 - 128, 256, true);  // runs past the end
+          Request* c = t.write(1, region.data(), *mr, all[1], 1024, 512, true);        // fine: words 256..383
+          if (!a || !b || !c) set(1);
+          if (t.cma_enabled(1) && a && b && (a->status() == 0 || b->status() == 0)) set(2);
+          if (c && c->status() != 0) set(3);
+          for (Request* q : {a, b, c}) if (q) t.release(q);
+          t.write_flag(1, flags[1], 5, 1, false);
+        } else {
+          auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(5);
+          while (__atomic_load_n(t.flags() + 5, __ATOMIC_ACQUIRE) < 1) {
+            if (std::chrono::steady_clock::now() > deadline) { set(4); break; }
+            std::this_thread::yield();
+          }
+          for (size_t i = 0; i < region.size(); ++i) {
+            const uint32_t want = (i >= 256 && i < 384) ? 0x12345678u : 0xAAAAAAAAu;
+            if (region[i] != want) { set(5); break; }
+          }
+        }
+        store.barrier();
+        errors_seen += t.remote_access_errors();
+        store.barrier();
+        mr.reset();
+      } catch (const std::exception& e) {
+        fprintf(stderr, "soft reject rank %d: %s\n", r, e.what());
+        set(6);
+      }
+    });
+  }
+  for (auto& t : th) t.join();
+  if (had) setenv("MINI_NCCL_SOFT_CMA", saved.c_str(), 1);
+  else unsetenv("MINI_NCCL_SOFT_CMA");
+  if (verdict.load() == 0 && errors_seen.load() != 2) return 7;
+  if (verdict.load() == 0 && cma && !used_cma.load()) return -1;  // fast path not permitted here: nothing was tested
+  return verdict.load();
 }
 
 // ---- SPSC queue -----------------------------------------------------------

@@ -286,3 +286,12 @@ def test_gemm_tile_walk_covers_every_tile_once_in_owner_order(lib, pair, nranks,
                 seen.append(o)
         first = (rank + 1) % nranks if name == "reduce-scatter" else rank
         assert seen == [(first + i) % nranks for i in range(nranks)], (name, seen)
+
+
+@pytest.mark.parametrize("cma", [0, 1], ids=["sockets", "cross_memory_attach"])
+def test_soft_provider_rejects_bad_key_and_range(lib, free_port, cma):
+    lib.mnccl_test_soft_reject.restype = C.c_int
+    rc = lib.mnccl_test_soft_reject(int(free_port), cma)
+    if rc == -1:
+        pytest.skip("cross-memory attach is not permitted on this machine")
+    assert rc == 0, f"check {rc} failed"

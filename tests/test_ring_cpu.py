@@ -12,9 +12,10 @@ from tests.mp_workers import run_ranks
 ALL_DTYPES = list(range(10))
 
 
-def test_plumbing_config_two_ranks(free_port):
+@pytest.mark.parametrize("cma", [0, 1], ids=["sockets", "cross_memory_attach"])
+def test_plumbing_config_two_ranks(free_port, cma):
     env = {"MINI_NCCL_BOOTSTRAP_PORT": free_port, "MINI_NCCL_SLICE_SIZE": 131072, "MINI_NCCL_WINDOW_SIZE": 64,
-           "MINI_NCCL_SIGNAL_BATCH": 16}
+           "MINI_NCCL_SIGNAL_BATCH": 16, "MINI_NCCL_SOFT_CMA": cma, "MINI_NCCL_DEBUG": "INFO"}
     cases = [{"dtype": _lib.FLOAT32, "op": _lib.SUM, "count": 1048576, "repeat": 3}]
     res = run_ranks("cpu_ring", 2, {"cases": cases}, env)
     for r in res:
@@ -29,6 +30,13 @@ def test_plumbing_config_two_ranks(free_port):
         # the user buffer is registered once; later calls hit the cache
         assert st["transport"]["reg_hits"] >= 2
         assert "[Config] Loaded: SLICE_SIZE=131072 B, WINDOW=64, BATCH=16" in r["_stderr"]
+        if cma == 0:
+            assert st["transport"]["direct_writes"] == 0
+        elif "cross-memory attach to 1 same-host peer" in r["_stderr"]:
+            # the kernel allowed it: every payload went straight into the peer's memory
+            assert st["transport"]["direct_writes"] == st["transport"]["writes"] == 16 * 2 * 3
+        else:
+            assert st["transport"]["direct_writes"] == 0   # not permitted here: sockets, same results
 
 
 @pytest.mark.parametrize("n", [2, 3, 4])
@@ -47,9 +55,10 @@ def test_every_dtype_and_op(free_port):
     assert all(r["cases"] == 50 for r in res)
 
 
-def test_tiny_slices_exercise_credits_and_window(free_port):
+@pytest.mark.parametrize("cma", [0, 1], ids=["sockets", "cross_memory_attach"])
+def test_tiny_slices_exercise_credits_and_window(free_port, cma):
     env = {"MINI_NCCL_BOOTSTRAP_PORT": free_port, "MINI_NCCL_SLICE_SIZE": 512, "MINI_NCCL_WINDOW_SIZE": 2,
-           "MINI_NCCL_SIGNAL_BATCH": 1}
+           "MINI_NCCL_SIGNAL_BATCH": 1, "MINI_NCCL_SOFT_CMA": cma}
     cases = [{"dtype": _lib.FLOAT32, "op": _lib.SUM, "count": 200000, "repeat": 2},
              {"dtype": _lib.FLOAT64, "op": _lib.MAX, "count": 50001}]
     res = run_ranks("cpu_ring", 3, {"cases": cases}, env)
