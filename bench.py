@@ -5,15 +5,21 @@ One "step" is one fp32 sum AllReduce of 256 MiB per rank through the library's
 public Python API (Communicator.all_reduce on a tensor from Communicator.empty),
 timed on the device with CUDA events, maximum over ranks.  The message is larger
 than the 126 MB L2, so iterations do not hit in cache.  `value` is the bus
-bandwidth algBW * 2(n-1)/n in GB/s (for one GPU, where that factor is zero, the
-algorithm bandwidth of the degenerate out-of-place call).  A sweep over message
-sizes (this library and NCCL side by side, fp32 and bf16) and the 8 KB latency
-are attached under "sweep".  The "e2e" number repeats the metric with, per step,
-the host-to-device copy of the input from pinned memory and the device-to-host
-read of the result inside the timed region.
+bandwidth algBW * 2(n-1)/n in GB/s; with one GPU that factor is zero, so the
+same metric name carries the algorithm bandwidth of the degenerate out-of-place
+call (an HBM copy with the scale fused in) and `config` says so.
 
-The reference library itself cannot run here (it needs libibverbs and an RDMA
-device at build and at run time); `--impl reference` reports that.
+The K timed steps are repeated R times (each repeat bracketed by a barrier and
+a synchronize); the reported value is the MEDIAN repeat, every repeat is listed,
+and the per-step spread of the median repeat is given.  After the timed loops
+every algorithm of the library is run on seeded random data and compared with
+the host oracle ("checked"); a mismatch makes the exit code non-zero.  The "e2e"
+number repeats the metric with, per step, the host-to-device copy of the input
+from pinned memory and the device-to-host read of the result inside the timed
+region, and relates it to the measured ceiling of plain concurrent copies.  A
+sweep over message sizes (this library and NCCL side by side) is attached.
+
+`--impl reference` times the unmodified reference library (baseline/ref_arm.py).
 """
 from __future__ import annotations
 
@@ -28,32 +34,34 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 HEADLINE_BYTES = 256 << 20
+METRIC = "allreduce_busbw_GBps"
 
 
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--bytes", type=int, default=HEADLINE_BYTES)
     ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"])
+    ap.add_argument("--repeats", type=int, default=7, help="timed regions of --steps steps; the median is reported")
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-check", action="store_true")
     ap.add_argument("--sweep-max-bytes", type=int, default=1 << 30)
     ap.add_argument("--unregistered", action="store_true", help="headline on ordinary torch tensors (staged path)")
     return ap.parse_args()
 
 
 def reference_arm(args):
-    if int(os.environ.get("RANK", "0")) != 0:
-        return 0  # one line per job
-    print(json.dumps({
-        "impl": "reference",
-        "unavailable": "reference is a CMake/C++ project that needs libibverbs + libnvToolsExt at configure time and an "
-                       "RDMA device (rxe0/mlx5) at run time; neither exists on this image, and pip cannot install it "
-                       "(no setup.py / pyproject.toml)",
-    }))
-    return 0
+    from baseline import ref_arm
+
+    try:
+        return ref_arm.main(args.bytes, args.steps, args.warmup)
+    except Exception as e:  # the line must come out whatever happens
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "reference arm stopped: %s" % str(e)[:200]}))
+        return 0
 
 
 def main():
@@ -78,7 +86,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     import mini_nccl_b200 as mn
-    from mini_nccl_b200.utils.timing import ClockSampler, bus_bandwidth_gbs, max_over_ranks
+    from mini_nccl_b200.utils.timing import ClockSampler, bus_bandwidth_gbs, max_over_ranks, timed_repeats
 
     comm = mn.Communicator(world, rank, os.environ["MASTER_ADDR"])
     dtype = torch.float32 if args.dtype == "fp32" else torch.bfloat16
@@ -92,6 +100,7 @@ def main():
     buf.copy_(torch.randn(count, generator=gen, device="cuda", dtype=torch.float32).to(dtype))
     out = torch.empty(count, dtype=dtype, device="cuda") if world == 1 else buf
     stream = torch.cuda.current_stream()
+    steps, warmup, repeats = max(args.steps, 1), max(args.warmup, 3), max(args.repeats, 1)
 
     def sync_all():
         torch.cuda.synchronize()
@@ -103,7 +112,7 @@ def main():
         # scale keeps the values bounded over many in-place iterations
         comm.all_reduce(buf, "sum", out=out, scale=1.0 / world if world > 1 else 1.0)
 
-    # ---- headline: device-timed, K steps, max over ranks
+    # ---- headline: device-timed, K steps per repeat, max over ranks, median repeat
     # Untimed pre-warm for ~1 s: clocks and NVLink links leave their idle power states (a cold
     # start measured 15 to 25 % below the steady state), then the W warm-up steps proper.
     t_pre = time.perf_counter()
@@ -111,18 +120,15 @@ def main():
         for _ in range(10):
             step()
         torch.cuda.synchronize()
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(warmup):
         step()
-    sync_all()
-    sampler = ClockSampler(torch.cuda.current_device(), period_s=0.004).start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(args.steps):
-        step()
-    e1.record(stream)
-    sync_all()
+    # Clocks are sampled DURING the timed repeats by a thread that makes two NVML reads every 50 ms.
+    sampler = ClockSampler(torch.cuda.current_device(), period_s=0.05).start()
+    timed = timed_repeats(step, steps, repeats, sync_all, stream)
     clocks = sampler.stop()
-    ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    # one more repeat with no sampler thread at all, to show that sampling does not move the number
+    quiet = timed_repeats(step, steps, 1, sync_all, stream)
+    ms = timed["ms_per_step"]
     alg, bus = bus_bandwidth_gbs(args.bytes, ms, world)
     algo_used = comm.query_algo(args.bytes, dtype, "sum", registered=not (args.unregistered or world == 1))
 
@@ -131,6 +137,7 @@ def main():
     host_in.copy_(buf.cpu())
     host_out = torch.empty(count, dtype=dtype).pin_memory()
     scale = 1.0 / world if world > 1 else 1.0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
     def e2e_step():
         # The call a user of the reference makes: pinned host buffers handed to the collective
@@ -144,26 +151,60 @@ def main():
         comm.all_reduce(buf, "sum", out=out, scale=scale)
         host_out.copy_(out, non_blocking=True)
 
-    def time_e2e(step):
+    s_h2d, s_d2h = torch.cuda.Stream(), torch.cuda.Stream()
+    scratch = torch.empty(count, dtype=dtype, device="cuda")
+
+    def ceiling_step():
+        # no collective at all: the input's host-to-device copy and the result's device-to-host copy
+        # at the same time on two streams -- what the host side of this machine can carry
+        s_h2d.wait_stream(stream)
+        s_d2h.wait_stream(stream)
+        with torch.cuda.stream(s_h2d):
+            scratch.copy_(host_in, non_blocking=True)
+        with torch.cuda.stream(s_d2h):
+            host_out.copy_(out, non_blocking=True)
+        stream.wait_stream(s_h2d)
+        stream.wait_stream(s_d2h)
+
+    def time_e2e(fn):
         for _ in range(3):
-            step()
-        sync_all()
-        n_steps = max(3, min(args.steps, 20))
-        t0 = time.perf_counter()
-        e0.record(stream)
-        for _ in range(n_steps):
-            step()
-        e1.record(stream)
-        torch.cuda.synchronize()
-        wall_ms = (time.perf_counter() - t0) * 1e3 / n_steps
-        return max_over_ranks(max(e0.elapsed_time(e1) / n_steps, wall_ms))
+            fn()
+        n_steps = max(3, min(steps, 20))
+        best = []
+        for _ in range(3):
+            sync_all()
+            t0 = time.perf_counter()
+            e0.record(stream)
+            for _ in range(n_steps):
+                fn()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            wall_ms = (time.perf_counter() - t0) * 1e3 / n_steps
+            best.append(max_over_ranks(max(e0.elapsed_time(e1) / n_steps, wall_ms)))
+        return sorted(best)[1]  # median of three
 
     e2e_serial_ms = time_e2e(serial_step)
     e2e_ms = time_e2e(e2e_step)
     # the result really is in host memory: compare the two paths' outputs
     e2e_check = bool(torch.allclose(host_out, out.cpu(), rtol=1e-3, atol=1e-3))
+    ceiling_ms = time_e2e(ceiling_step)
     e2e_alg, e2e_bus = bus_bandwidth_gbs(args.bytes, e2e_ms, world)
     sync_all()
+
+    # ---- correctness against the host oracle (outside every timed region)
+    checked = None
+    if not args.no_check:
+        from mini_nccl_b200.utils import verify
+
+        ar = verify.check_allreduce(comm, world, rank)
+        gm = verify.check_fused_gemm(comm, world, rank)
+        bad = ar["failed"] + gm["failed"]
+        bad_any = int(max_over_ranks(float(bad)))
+        checked = {"cases": ar["cases"] + gm["cases"], "failed": bad_any, "nvls": ar["nvls"],
+                   "fused_gemm_cases": gm["cases"], "failures": (ar["failures"] + gm["failures"])[:8],
+                   "rule": "P2P algorithms bit-exact against the rank-ordered host oracle; NVLS within tolerance on random "
+                           "data and bit-exact on exactly representable data; fused GEMMs bit-exact on integer operands"}
+        sync_all()
 
     # ---- sweep (ours vs NCCL), attached for context
     sweep = None
@@ -171,16 +212,20 @@ def main():
         from benchmarks.sweep import run_sweep
 
         sweep = run_sweep(comm, world, rank, max_bytes=args.sweep_max_bytes, quick=True)
+        # the headline once more after the sweep: the two loops must agree
+        after = timed_repeats(step, steps, 3, sync_all, stream)
+        sweep["headline_again_ms_per_step"] = round(after["ms_per_step"], 5)
 
     stats = comm.stats()
+    rc = 0
     if rank == 0:
         line = {
-            "metric": "allreduce_busbw_GBps" if world > 1 else "allreduce_algbw_GBps_single_gpu",
+            "metric": METRIC,
             "value": round(bus, 3),
             "unit": "GB/s",
             "n_gpus": world,
-            "steps": args.steps,
-            "warmup": max(args.warmup, 3),
+            "steps": steps,
+            "warmup": warmup,
             "ms_per_step": round(ms, 5),
             "higher_is_better": True,
             "scaling": "weak",
@@ -190,14 +235,17 @@ def main():
             "impl": "ours",
             "algbw_GBps": round(alg, 3),
             "algorithm": algo_used,
+            "repeats": {"n": repeats, "reported": "median", "ms_per_step": timed["repeats_ms_per_step"],
+                        "step_us_in_median_repeat": timed["step_us"],
+                        "without_clock_sampler_ms_per_step": round(quiet["ms_per_step"], 5)},
             "config": {
                 "model": "AllReduce sum, %d MiB per rank" % (args.bytes >> 20),
                 "global_batch": args.bytes * world,
                 "seq_len": count,
                 "parallelism": "allreduce x%d" % world,
-                "buffers": "ordinary device memory (staged)" if (args.unregistered or world == 1) else "symmetric memory (zero-copy)",
+                "buffers": "ordinary device memory" if (args.unregistered or world == 1) else "symmetric memory (zero-copy)",
                 "l2": "message (%d MiB) larger than the 126 MB L2; no flush needed" % (args.bytes >> 20),
-                "timing": "CUDA events on the launching stream, max over ranks",
+                "timing": "CUDA events on the launching stream, max over ranks, median of %d repeats of %d steps" % (repeats, steps),
                 "nvls": bool(stats.get("nvls")),
             },
             "clocks": clocks,
@@ -210,18 +258,29 @@ def main():
                 "api": "Communicator.all_reduce on pinned host tensors (input and result in host memory)",
                 "serialised_copy_collective_copy_ms_per_step": round(e2e_serial_ms, 4),
                 "result_matches_device_path": e2e_check,
+                "host_copy_ceiling_ms_per_step": round(ceiling_ms, 4),
+                "fraction_of_host_copy_ceiling": round(ceiling_ms / e2e_ms, 3) if e2e_ms > 0 else None,
+                "ceiling": "the same two copies (256 MiB in, 256 MiB out, pinned memory) at once on two streams on every "
+                           "rank, no collective",
             },
-            "gpu_launches": args.steps,
+            "checked": checked,
+            "gpu_launches": steps,
+            "gpu_launches_note": "one collective kernel per step in each timed region of %d steps (%d regions)" % (steps, repeats),
             "sweep": sweep,
         }
+        if world == 1:
+            line["config"]["one_gpu"] = ("bus-bandwidth factor 2(n-1)/n is 0 for one rank: the value is the algorithm bandwidth "
+                                         "of the degenerate out-of-place call (HBM copy with the scale fused in)")
         print(json.dumps(line))
         sys.stdout.flush()
+    if checked is not None and checked["failed"]:
+        rc = 3
     if world > 1:
         dist.barrier()
     comm.destroy()
     if world > 1:
         dist.destroy_process_group()
-    return 0
+    return rc
 
 
 if __name__ == "__main__":

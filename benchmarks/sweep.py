@@ -25,8 +25,9 @@ if ROOT not in sys.path:
 
 def _time_loop(fn, iters, warmup, world, repeats=1):
     """Milliseconds per call: `iters` back-to-back calls between two CUDA events on the current
-    stream, after `warmup` calls and a barrier; the maximum over ranks; the best of `repeats`
-    such loops (short loops are exposed to one-off stalls of a shared machine)."""
+    stream, after `warmup` calls and a barrier; the maximum over ranks; the MEDIAN of `repeats`
+    such loops (a single short loop is exposed to one-off stalls of a shared machine, the best of
+    several flatters)."""
     import torch
     import torch.distributed as dist
 
@@ -34,7 +35,7 @@ def _time_loop(fn, iters, warmup, world, repeats=1):
 
     for _ in range(warmup):
         fn()
-    best = None
+    seen = []
     for _ in range(repeats):
         torch.cuda.synchronize()
         if world > 1:
@@ -47,8 +48,8 @@ def _time_loop(fn, iters, warmup, world, repeats=1):
         e1.record()
         torch.cuda.synchronize()
         ms = max_over_ranks(e0.elapsed_time(e1) / iters)
-        best = ms if best is None else min(best, ms)
-    return best
+        seen.append(ms)
+    return sorted(seen)[(len(seen) - 1) // 2]
 
 
 def run_sweep(comm, world, rank, max_bytes=1 << 30, min_bytes=8 << 10, quick=False, dtypes=("fp32", "bf16"),
@@ -80,7 +81,7 @@ def run_sweep(comm, world, rank, max_bytes=1 << 30, min_bytes=8 << 10, quick=Fal
             if quick:
                 iters = max(5, iters // 3)
             warm = 5
-            reps = 3 if nbytes <= (4 << 20) else 1
+            reps = 3
             row = {"bytes": nbytes, "dtype": dt_name}
             scale = 1.0 / world
             for algo in algos:

@@ -31,6 +31,37 @@ def time_cuda(fn, iters: int, warmup: int = 3, stream=None, pre=None) -> float:
     return start.elapsed_time(stop) / max(iters, 1)
 
 
+def timed_repeats(step, steps: int, repeats: int, sync_all, stream=None) -> dict:
+    """The benchmark's timed region, `repeats` times over: a barrier and a synchronize, one CUDA event
+    before every step and one after the last, `steps` back-to-back calls of ``step``, a synchronize.
+    Every repeat's milliseconds per step is the maximum over ranks; the reported figure is the MEDIAN
+    repeat, so that neither a one-off stall of a shared machine nor a lucky loop decides the number.
+    The per-step durations (this rank's events) of the median repeat tell a slow outlier from a
+    uniform slowdown."""
+    import torch
+
+    stream = stream or torch.cuda.current_stream()
+    per_repeat, per_step = [], []
+    for _ in range(repeats):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        sync_all()
+        ev[0].record(stream)
+        for i in range(steps):
+            step()
+            ev[i + 1].record(stream)
+        torch.cuda.synchronize()
+        per_repeat.append(max_over_ranks(ev[0].elapsed_time(ev[steps]) / steps))
+        per_step.append([ev[i].elapsed_time(ev[i + 1]) * 1e3 for i in range(steps)])
+    order = sorted(range(repeats), key=lambda i: per_repeat[i])
+    mid = order[(repeats - 1) // 2]
+    us = sorted(per_step[mid])
+    return {
+        "ms_per_step": per_repeat[mid],
+        "repeats_ms_per_step": [round(x, 5) for x in per_repeat],
+        "step_us": {"min": round(us[0], 1), "median": round(us[len(us) // 2], 1), "max": round(us[-1], 1)},
+    }
+
+
 def max_over_ranks(value: float) -> float:
     """Maximum of a host scalar over all ranks of the default torch.distributed group."""
     import torch

@@ -106,7 +106,13 @@ int ibv_post_send(ibv_qp* qp, ibv_send_wr* wr, ibv_send_wr** bad) {
     }
     // A send-queue slot is free again only when a LATER signalled completion has been polled:
     // a poster that never signals (or never polls) overruns the queue, as on real hardware.
-    if (qp->posted - qp->retired >= qp->max_send_wr) {
+    // FAKE_VERBS_SQ_DEPTH_CHECK=0 switches the depth model off (used when a program that is known to
+    // overrun its queue has to be run to completion anyway).
+    static const bool depth_check = [] {
+      const char* e = std::getenv("FAKE_VERBS_SQ_DEPTH_CHECK");
+      return !(e && e[0] == '0');
+    }();
+    if (depth_check && qp->posted - qp->retired >= qp->max_send_wr) {
       if (bad) *bad = wr;
       return ENOMEM;
     }
