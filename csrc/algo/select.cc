@@ -30,6 +30,7 @@ Algo parse_algo(const std::string& s) {
   if (!strcasecmp(c, "twoshot")) return Algo::TwoShot;
   if (!strcasecmp(c, "nvls")) return Algo::Nvls;
   if (!strcasecmp(c, "ring")) return Algo::Ring;
+  if (!strcasecmp(c, "pipe")) return Algo::Pipe;
   return Algo::Auto;
 }
 
@@ -111,7 +112,9 @@ Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
     if (algo != Algo::TwoShot && algo != Algo::Nvls) algo = nvls_usable && in.mode == Mode::ReduceScatter && wire_bytes >= th.nvls_min ? Algo::Nvls : Algo::TwoShot;
     if (algo == Algo::Nvls && !(nvls_usable && in.mode == Mode::ReduceScatter)) algo = Algo::TwoShot;
   } else if (algo == Algo::Auto) {
-    if (wire_bytes <= th.ll_max && wire_bytes * 2 <= caps.ll_slot_bytes) algo = Algo::LL;
+    const bool ordinary = !(in.in_symmetric && in.out_symmetric);
+    if (ordinary && !in.host_memory && cfg.pipe_min_bytes != 0 && wire_bytes >= cfg.pipe_min_bytes) algo = Algo::Pipe;
+    else if (wire_bytes <= th.ll_max && wire_bytes * 2 <= caps.ll_slot_bytes) algo = Algo::LL;
     else if (wire_bytes <= th.oneshot_max && wire_bytes <= caps.inbox_slot_bytes) algo = Algo::OneShot;
     else if (nvls_usable && wire_bytes >= th.nvls_min) algo = Algo::Nvls;
     else algo = Algo::TwoShot;
@@ -120,6 +123,7 @@ Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
   if (algo == Algo::LL && ceil_div(wire_bytes, 8) * 16 > caps.ll_slot_bytes) algo = Algo::OneShot;
   if (algo == Algo::OneShot && ceil_div(wire_bytes, 16) * 16 > caps.inbox_slot_bytes) algo = Algo::TwoShot;
   if (algo == Algo::Nvls && !nvls_usable) algo = Algo::TwoShot;
+  if (algo == Algo::Pipe && (in.mode != Mode::AllReduce || in.host_memory)) algo = Algo::TwoShot;
   if (algo == Algo::Ring || algo == Algo::Auto || algo == Algo::Local) algo = Algo::TwoShot;
   p.spec.algo = algo;
 
@@ -134,6 +138,25 @@ Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
     const uint64_t vecs = ceil_div(wire_bytes, 16);
     p.spec.nthreads = vecs <= 256 ? 256 : 512;
     p.spec.nblocks = static_cast<int>(std::clamp<uint64_t>(ceil_div(vecs, p.spec.nthreads), 1, max_blocks ? max_blocks : 64));
+    p.valid = true;
+    return p;
+  }
+
+  if (algo == Algo::Pipe) {
+    // Chunks of about a sixteenth of the message (1 MB at least), bounded by one ring slot of either
+    // staging area; a chunk is N shards of E elements, E a multiple of the vector width.
+    const uint64_t stride = caps.stage_bytes / kPipeSlots;
+    uint64_t target = cfg.pipe_chunk_bytes ? cfg.pipe_chunk_bytes : std::clamp<uint64_t>(wire_bytes / 16, 1u << 20, 8u << 20);
+    uint64_t ce = std::min<uint64_t>(target / wsz, stride / std::max(wsz, osz));
+    uint64_t E = ce / (uint64_t(N) * VW) * VW;
+    if (E == 0) { p.reason = "staging buffer too small for the pipelined kernel"; return p; }
+    p.shard_elems = E;
+    p.chunk_shard_vecs = E / VW;
+    p.copy_in = p.copy_out = true;
+    p.spec.pipe_nvls = caps.nvls && N > 2 && nvls_types;
+    int want = p.spec.pipe_nvls ? 80 : 112;
+    if (max_blocks) want = max_blocks;
+    p.spec.nblocks = std::clamp(want, 3, std::max(3, caps.sm_count - 8));
     p.valid = true;
     return p;
   }

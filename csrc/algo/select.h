@@ -46,6 +46,7 @@ struct PlanInput {
   bool in_symmetric = false;   // send buffer lies in symmetric memory (16-byte aligned)
   bool out_symmetric = false;  // recv buffer lies in symmetric memory (16-byte aligned)
   bool in_has_mc = false, out_has_mc = false;  // those segments have multicast mappings
+  bool host_memory = false;     // a buffer is pinned host memory (never taken by the pipelined kernel)
   Algo forced = Algo::Auto;
 };
 

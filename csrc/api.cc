@@ -97,7 +97,7 @@ MNCCL_EXPORT ncclResult_t mncclAllReduceEx(const void* sendbuff, ncclDataType_t 
                                            cudaStream_t stream) {
   if (!comm || !sendbuff || !recvbuff) return ncclInvalidArgument;
   if (!mnccl::valid_dtype(send_type) || !mnccl::valid_dtype(recv_type) || !mnccl::valid_dtype(wire_type) ||
-      !mnccl::valid_op(op) || algo < mncclAlgoAuto || algo > mncclAlgoRing)
+      !mnccl::valid_op(op) || algo < mncclAlgoAuto || algo > mncclAlgoPipe || algo == mncclAlgoLocal)
     return ncclInvalidArgument;
   if (count == 0) return ncclSuccess;
   // One range per call, named and coloured as in the reference; the payload is
@@ -212,7 +212,16 @@ MNCCL_EXPORT ncclResult_t mncclCommSetTuning(ncclComm_t comm, int max_blocks, in
   return firewall("SetTuning", ncclInternalError, [&] { unwrap(comm)->set_tuning(max_blocks, unroll); });
 }
 
-MNCCL_EXPORT unsigned mncclVersion(void) { return 100; }
+MNCCL_EXPORT ncclResult_t mncclCommSetKnob(ncclComm_t comm, const char* name, long long value) {
+  if (!comm || !name) return ncclInvalidArgument;
+  ncclResult_t bad = ncclSuccess;
+  ncclResult_t r = firewall("SetKnob", ncclInternalError, [&] {
+    if (!unwrap(comm)->set_knob(name, value)) bad = ncclInvalidArgument;
+  });
+  return r != ncclSuccess ? r : bad;
+}
+
+MNCCL_EXPORT unsigned mncclVersion(void) { return 101; }
 
 // ---- reference-compatible names -------------------------------------------
 // Linked with -Bsymbolic-functions, so these never resolve to another NCCL in

@@ -125,6 +125,14 @@ void Comm::init(int nranks, int rank, const char* ip) {
                                   cfg_.connect_retries));
   store_->connect();
 
+  // Measured crossovers for this machine, if a table was given (the built-in ones are the fallback).
+  if (!cfg_.tuning_file.empty()) {
+    std::string errors;
+    const int applied = cfg_.apply_tuning_file(cfg_.tuning_file, size_, &errors);
+    if (!errors.empty()) MNCCL_WARN("Mini-NCCL", "tuning file %s: %s", cfg_.tuning_file.c_str(), errors.c_str());
+    MNCCL_INFO("Mini-NCCL", "rank %d: %d knob(s) from %s", rank_, applied, cfg_.tuning_file.c_str());
+  }
+
   // Job namespace for host shared memory and unix sockets: a nonce from rank 0.
   uint64_t nonce = 0;
   if (rank_ == 0) {
@@ -317,6 +325,8 @@ void Comm::init_gpu_plane() {
   off += align_up(sizeof(uint32_t) * kMaxBlocks * kMaxRanks, 4096);
   dev_.off_local = off;
   off += align_up(sizeof(LocalState), 4096);
+  dev_.off_pipe = off;
+  off += align_up(sizeof(PipeCtl), 4096);
   dev_.off_ll = off;
   off += 2 * size_t(size_) * caps_.ll_slot_bytes;
   dev_.off_inbox = off;
@@ -460,8 +470,9 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
     // 8 GPUs) beats the zero-copy peer-to-peer two-shot (624 GB/s): treat them as ordinary there.
     const bool switch_sum = (op == RedOp::Sum || op == RedOp::Avg) &&
                             (wire_t == DType::Float32 || wire_t == DType::Float16 || wire_t == DType::Bfloat16);
-    if (mode == Mode::AllReduce && caps_.nvls && size_ > 2 && switch_sum && cfg_.pipeline_min_bytes != 0 &&
-        count * dtype_size(wire_t) >= cfg_.pipeline_min_bytes) {
+    const size_t demote_from = cfg_.pipe_min_bytes ? cfg_.pipe_min_bytes : cfg_.pipeline_min_bytes;
+    if (mode == Mode::AllReduce && caps_.nvls && size_ > 2 && switch_sum && demote_from != 0 &&
+        count * dtype_size(wire_t) >= demote_from) {
       if (in_seg && !in_seg->mc) pi.in_symmetric = false;
       if (out_seg && !out_seg->mc) pi.out_symmetric = false;
     }
@@ -472,6 +483,7 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
   const MemKind recv_kind = out_seg ? MemKind::Device : (recv == send ? send_kind : classify(recv, true));
   if (send_kind == MemKind::PlainHost || recv_kind == MemKind::PlainHost)
     fail(Result::InvalidArgument, "buffers must be device memory or pinned host memory on the GPU data plane");
+  pi.host_memory = send_kind == MemKind::PinnedHost || recv_kind == MemKind::PinnedHost;
   Plan plan = make_plan(pi, caps_, cfg_);
   if (!plan.valid) fail(Result::InvalidArgument, std::string("no kernel for this request: ") + plan.reason);
   if (!kernel_exists(plan.spec)) fail(Result::InvalidArgument, "no kernel for this type / operator combination");
@@ -541,8 +553,47 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
     if (zc_out) stats_.zero_copy_out++;
     if (plan.copy_in || plan.copy_out) stats_.staged_passes++;
   }
+  if (plan.spec.algo == Algo::Pipe) stats_.staged_passes++;
+  // A large zero-copy NVLS AllReduce can hand a slice of the message to peer-to-peer blocks of the
+  // same launch (the switch's reduction rate, not the links, bounds the NVLS path).
+  const uint64_t vw = 16 / dtype_size(wire_t);
+  uint64_t n2 = 0;
+  if (plan.spec.algo == Algo::Nvls && mode == Mode::AllReduce && !plan.copy_in && !plan.copy_out &&
+      cfg_.nvls_p2p_permille > 0 && count * dtype_size(wire_t) >= cfg_.nvls_p2p_min_bytes) {
+    const uint64_t unit = vw * static_cast<uint64_t>(size_);
+    const uint64_t n1 = count * static_cast<uint64_t>(1000 - cfg_.nvls_p2p_permille) / 1000 / unit * unit;
+    if (n1 >= unit && n1 < count) n2 = count - n1;
+  }
   if (size_ == 1 && mode == Mode::AllReduce && send == recv && send_t == recv_t && factor == 1.0) {
     // Nothing to do; keep stream order semantics without a launch.
+  } else if (n2 != 0) {
+    KParamsSplit ks;
+    memset(&ks, 0, sizeof(ks));
+    ks.comm = kp.comm;
+    ks.args = kp.args;
+    ks.args2 = kp.args;
+    const uint64_t n1 = count - n2;
+    CollArgs& a1 = ks.args;
+    CollArgs& a2 = ks.args2;
+    a1.count = n1;
+    a1.shard_elems = n1 / size_;
+    a1.chunk_shard_vecs = a1.shard_elems / vw;
+    a2.count = n2;
+    a2.shard_elems = ((n2 + vw - 1) / vw + size_ - 1) / size_ * vw;
+    a2.chunk_shard_vecs = a2.shard_elems / vw;
+    a2.send = static_cast<const char*>(send) + n1 * dtype_size(send_t);
+    a2.recv = static_cast<char*>(recv) + n1 * dtype_size(recv_t);
+    for (int r = 0; r < size_; ++r) {
+      a2.in_peer[r] += n1 * dtype_size(wire_t);
+      a2.out_peer[r] += n1 * dtype_size(recv_t);
+    }
+    a2.in_mc = a2.out_mc = nullptr;
+    LaunchSpec spec = plan.spec;
+    const uint64_t tiles1 = (a1.chunk_shard_vecs + 2047) / 2048;
+    ks.nb_first = static_cast<int>(std::min<uint64_t>(std::max<uint64_t>(tiles1, 1), cfg_.max_blocks > 0 ? cfg_.max_blocks : 32));
+    spec.nblocks = ks.nb_first + cfg_.nvls_p2p_blocks;
+    spec.unroll = 4;
+    RT_CHECK(launch_nvls_split(spec, ks, stream), "kernel launch");
   } else {
     RT_CHECK(launch_collective(plan.spec, kp, stream), "kernel launch");
   }
@@ -1044,7 +1095,7 @@ std::string Comm::stats_json() {
   o << "{\"rank\":" << rank_ << ",\"size\":" << size_ << ",\"plane\":\"" << (gpu_plane_ ? "nvlink" : (transport_ ? transport_->name() : "none"))
     << "\",\"device\":" << device_ << ",\"symmetric_provider\":\"" << (symm_ ? symm_->provider() : "none") << "\",\"nvls\":"
     << (caps_.nvls ? "true" : "false") << ",\"calls\":" << stats_.calls << ",\"bytes\":" << stats_.bytes << ",\"algo\":{";
-  const Algo algos[] = {Algo::LL, Algo::OneShot, Algo::TwoShot, Algo::Nvls, Algo::Ring, Algo::Local};
+  const Algo algos[] = {Algo::LL, Algo::OneShot, Algo::TwoShot, Algo::Nvls, Algo::Ring, Algo::Local, Algo::Pipe};
   bool first = true;
   for (Algo a : algos) {
     if (!first) o << ",";

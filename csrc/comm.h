@@ -66,6 +66,10 @@ class Comm {
   std::string stats_json();
   Algo query_algo(size_t bytes, DType t, RedOp op, bool registered);
   const CommDev& device_handle() const { return dev_; }
+  bool set_knob(const char* name, long long value) {
+    std::lock_guard<std::mutex> lk(call_mu_);
+    return cfg_.set_knob(name ? name : "", value);
+  }
   void set_tuning(int max_blocks, int unroll) {
     std::lock_guard<std::mutex> lk(call_mu_);
     cfg_.max_blocks = max_blocks;

@@ -2,8 +2,10 @@
 
 #include <cerrno>
 #include <cstdlib>
+#include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <string>
 #include <strings.h>
 
 #include "core/error.h"
@@ -95,6 +97,11 @@ Config Config::from_getter(Getter get, void* ctx) {
   r.num("MINI_NCCL_PIPELINE_MIN_BYTES", c.pipeline_min_bytes);
   r.num("MINI_NCCL_HOST_PIPELINE_MIN_BYTES", c.host_pipeline_min_bytes);
   r.num("MINI_NCCL_HOST_CHUNK_BYTES", c.host_chunk_bytes);
+  r.num("MINI_NCCL_PIPE_MIN_BYTES", c.pipe_min_bytes);
+  r.num("MINI_NCCL_PIPE_CHUNK_BYTES", c.pipe_chunk_bytes);
+  r.num("MINI_NCCL_NVLS_P2P_PERMILLE", c.nvls_p2p_permille);
+  r.num("MINI_NCCL_NVLS_P2P_BLOCKS", c.nvls_p2p_blocks);
+  r.num("MINI_NCCL_NVLS_P2P_MIN_BYTES", c.nvls_p2p_min_bytes);
   r.num("MINI_NCCL_MAX_BLOCKS", c.max_blocks);
   r.num("MINI_NCCL_UNROLL", c.unroll);
   r.boolean("MINI_NCCL_NUMA_BIND", c.numa_bind);
@@ -105,6 +112,7 @@ Config Config::from_getter(Getter get, void* ctx) {
   r.boolean("MINI_NCCL_PIPELINE_COPY_ENGINE", c.pipeline_copy_engine);
   r.boolean("MINI_NCCL_PIPELINE_TAPER", c.pipeline_taper);
   r.boolean("MINI_NCCL_AUTO_DEVICE", c.auto_device);
+  r.str("MINI_NCCL_TUNING_FILE", c.tuning_file);
 
   if (c.bootstrap_port <= 0 || c.bootstrap_port > 65535) fail(Result::InvalidArgument, "MINI_NCCL_BOOTSTRAP_PORT out of range");
   if (c.hera_port <= 0 || c.hera_port > 65535) fail(Result::InvalidArgument, "MINI_NCCL_HERA_PORT out of range");
@@ -112,9 +120,102 @@ Config Config::from_getter(Getter get, void* ctx) {
   if (c.socket_timeout_ms <= 0) c.socket_timeout_ms = 1;
   if (c.connect_retries <= 0) c.connect_retries = 1;
   if (c.host_chunk_bytes < (64u << 10)) c.host_chunk_bytes = 64u << 10;
+  if (c.nvls_p2p_permille < 0) c.nvls_p2p_permille = 0;
+  if (c.nvls_p2p_permille > 900) c.nvls_p2p_permille = 900;
+  if (c.nvls_p2p_blocks < 1) c.nvls_p2p_blocks = 1;
   if (c.staging_bytes < (1u << 20)) c.staging_bytes = 1u << 20;
   c.staging_bytes = (c.staging_bytes + 4095) & ~size_t(4095);
   return c;
+}
+
+bool Config::set_knob(const std::string& name, long long v) {
+  if (v < 0) return false;
+  struct SizeKnob { const char* name; size_t Config::*field; };
+  struct IntKnob { const char* name; int Config::*field; int lo, hi; };
+  static const SizeKnob sizes[] = {
+      {"LL_MAX_BYTES", &Config::ll_max_bytes}, {"ONESHOT_MAX_BYTES", &Config::oneshot_max_bytes},
+      {"NVLS_MIN_BYTES", &Config::nvls_min_bytes}, {"PIPELINE_MIN_BYTES", &Config::pipeline_min_bytes},
+      {"PIPE_MIN_BYTES", &Config::pipe_min_bytes}, {"PIPE_CHUNK_BYTES", &Config::pipe_chunk_bytes},
+      {"NVLS_P2P_MIN_BYTES", &Config::nvls_p2p_min_bytes}, {"HOST_PIPELINE_MIN_BYTES", &Config::host_pipeline_min_bytes},
+      {"HOST_CHUNK_BYTES", &Config::host_chunk_bytes},
+  };
+  static const IntKnob ints[] = {
+      {"MAX_BLOCKS", &Config::max_blocks, 0, 512}, {"UNROLL", &Config::unroll, 0, 8},
+      {"NVLS_P2P_PERMILLE", &Config::nvls_p2p_permille, 0, 900}, {"NVLS_P2P_BLOCKS", &Config::nvls_p2p_blocks, 1, 256},
+  };
+  for (const auto& k : sizes)
+    if (name == k.name) {
+      if (name == "HOST_CHUNK_BYTES" && v < (64 << 10)) return false;
+      this->*(k.field) = static_cast<size_t>(v);
+      return true;
+    }
+  for (const auto& k : ints)
+    if (name == k.name) {
+      if (v < k.lo || v > k.hi || (name == "UNROLL" && v != 0 && v != 4 && v != 8)) return false;
+      this->*(k.field) = static_cast<int>(v);
+      return true;
+    }
+  return false;
+}
+
+int Config::apply_tuning_text(const std::string& text, int nranks, std::string* errors) {
+  int applied = 0, lineno = 0;
+  size_t pos = 0;
+  while (pos <= text.size()) {
+    size_t nl = text.find('\n', pos);
+    if (nl == std::string::npos) nl = text.size();
+    std::string line = text.substr(pos, nl - pos);
+    pos = nl + 1;
+    ++lineno;
+    const size_t hash = line.find('#');
+    if (hash != std::string::npos) line.erase(hash);
+    char knob[64];
+    long long n = 0, v = 0;
+    char extra = 0;
+    const int got = sscanf(line.c_str(), " %lld %63s %lld %c", &n, knob, &v, &extra);
+    if (line.find_first_not_of(" \t\r") == std::string::npos) continue;  // blank
+    if (got != 3) {
+      if (errors) *errors += "line " + std::to_string(lineno) + ": expected '<nranks> <KNOB> <value>'; ";
+      continue;
+    }
+    if (n != 0 && n != nranks) continue;
+    std::string name = knob;
+    if (name.rfind("MINI_NCCL_", 0) == 0) name.erase(0, 10);
+    if (set_knob(name, v)) ++applied;
+    else if (errors) *errors += "line " + std::to_string(lineno) + ": unknown knob or bad value '" + name + "'; ";
+  }
+  return applied;
+}
+
+// Environment variables win over the tuning table: applied again after it.
+static void reapply_env_knobs(Config& c) {
+  static const char* const names[] = {"LL_MAX_BYTES", "ONESHOT_MAX_BYTES", "NVLS_MIN_BYTES", "PIPELINE_MIN_BYTES",
+                                      "PIPE_MIN_BYTES", "PIPE_CHUNK_BYTES", "NVLS_P2P_MIN_BYTES", "HOST_PIPELINE_MIN_BYTES",
+                                      "HOST_CHUNK_BYTES", "MAX_BLOCKS", "UNROLL", "NVLS_P2P_PERMILLE", "NVLS_P2P_BLOCKS"};
+  for (const char* n : names) {
+    const std::string var = std::string("MINI_NCCL_") + n;
+    if (const char* v = getenv(var.c_str())) {
+      char* end = nullptr;
+      const long long x = strtoll(v, &end, 10);
+      if (end != v) c.set_knob(n, x);
+    }
+  }
+}
+
+int Config::apply_tuning_file(const std::string& path, int nranks, std::string* errors) {
+  FILE* f = fopen(path.c_str(), "r");
+  if (!f) {
+    if (errors) *errors += "cannot open " + path + "; ";
+    return 0;
+  }
+  std::string text;
+  char buf[4096];
+  size_t n;
+  while ((n = fread(buf, 1, sizeof(buf), f)) > 0) text.append(buf, n);
+  fclose(f);
+  const int applied = apply_tuning_text(text, nranks, errors);
+  reapply_env_knobs(*this);
+  return applied;
 }
 
 Config Config::from_env() { return from_getter(env_getter, nullptr); }

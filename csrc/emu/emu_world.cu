@@ -89,6 +89,8 @@ MNCCL_EXPORT int mncclEmuCreate(int nranks, size_t staging_bytes, void** world) 
   off += align_up(sizeof(uint32_t) * kMaxBlocks * kMaxRanks, 4096);
   proto.off_local = off;
   off += align_up(sizeof(LocalState), 4096);
+  proto.off_pipe = off;
+  off += align_up(sizeof(PipeCtl), 4096);
   proto.off_ll = off;
   off += 2 * size_t(nranks) * w->caps.ll_slot_bytes;
   proto.off_inbox = off;
@@ -151,6 +153,15 @@ MNCCL_EXPORT int mncclEmuSetTimeoutNs(void* world, uint64_t ns) {
   if (!w) return 4;
   w->timeout_ns = ns;
   for (auto& d : w->dev) d.spin_timeout_ns = ns;
+  return 0;
+}
+
+// Chunk size of the pipelined kernel for the calls that follow (0 = built-in choice).  Small chunks
+// make a small message wrap the ring of staging slots, which is what the tests want to see.
+MNCCL_EXPORT int mncclEmuSetPipeChunk(void* world, size_t bytes) {
+  auto* w = static_cast<EmuWorld*>(world);
+  if (!w) return 4;
+  w->cfg.pipe_chunk_bytes = bytes;
   return 0;
 }
 

@@ -27,6 +27,9 @@
 // every phase.  Hence block b of one rank only ever consumes data produced by
 // block b of the other ranks, and the cross-rank barrier is per block index.
 #pragma once
+#include <cstddef>
+#include <type_traits>
+
 #include "kernels/dev_prims.cuh"
 
 namespace mnccl {
@@ -195,15 +198,17 @@ __device__ __forceinline__ void oneshot_body(const KParams& P, int blk, int nblk
 // `v0` of the shard.  Shard j covers elements [j*E, (j+1)*E) of the logical
 // message; its vector i sits at element j*E + i*VW of user buffers and at
 // vector (j*SV + i) of a staging buffer (SV = capacity per shard).
+//
+// twoshot_core is the body without the kernel prologue / epilogue: `sig_blk` is the block's index
+// for the cross-rank barrier, (`blk`, `nblk`) its place among the blocks that share this message.
+// They differ when one kernel serves two messages with two groups of blocks (the NVLS + peer-to-peer
+// split of k_nvls.cu).
 template <typename InT, typename WireT, typename OutT, int OP, bool NVLS, int MODE, int kUnroll = 4>
-__device__ __forceinline__ void twoshot_body(const KParams& P, int blk, int nblk, BlockCtl& ctl) {
-  const CommDev& c = P.comm;
-  const CollArgs& a = P.args;
+__device__ __forceinline__ void twoshot_core(const CommDev& c, const CollArgs& a, int sig_blk, int blk, int nblk, BlockCtl& ctl) {
   using Acc = typename Elem<WireT>::Acc;
   using OAcc = typename Elem<OutT>::Acc;
   constexpr int VW = 16 / sizeof(typename Elem<WireT>::Raw);
   constexpr int OUT_VB = VW * sizeof(typename Elem<OutT>::Raw);  // bytes of one output vector
-  block_begin(c, blk, ctl);
   const int N = c.nranks, me = c.rank;
   const uint64_t E = a.shard_elems;
   const uint64_t total = (MODE == kAllReduce) ? a.count : E * uint64_t(N);  // logical message length
@@ -247,7 +252,7 @@ __device__ __forceinline__ void twoshot_body(const KParams& P, int blk, int nblk
     }
     // Barrier 1: every rank's inputs are in place, and every rank has left the
     // previous pass (so its staging / receive buffers may be written again).
-    ok = block_barrier(c, blk, ctl);
+    ok = block_barrier(c, sig_blk, ctl);
     if (!ok) break;
 
     // ---- phase B: reduce my shard and hand the result out (AllGather: push my shard)
@@ -368,7 +373,7 @@ __device__ __forceinline__ void twoshot_body(const KParams& P, int blk, int nblk
         }
       }
     }
-    ok = block_barrier(c, blk, ctl);
+    ok = block_barrier(c, sig_blk, ctl);
     if (!ok) break;
 
     // ---- phase C: copy staged outputs to the user buffer
@@ -387,6 +392,287 @@ __device__ __forceinline__ void twoshot_body(const KParams& P, int blk, int nblk
             store_vec<OutT, VW>(a.recv, e0, lim, recv_al, y);
           }
         }
+      }
+    }
+  }
+}
+
+template <typename InT, typename WireT, typename OutT, int OP, bool NVLS, int MODE, int kUnroll = 4>
+__device__ __forceinline__ void twoshot_body(const KParams& P, int blk, int nblk, BlockCtl& ctl) {
+  block_begin(P.comm, blk, ctl);
+  twoshot_core<InT, WireT, OutT, OP, NVLS, MODE, kUnroll>(P.comm, P.args, blk, blk, nblk, ctl);
+  block_end(P.comm, blk, nblk, ctl);
+}
+
+
+// -------------------------------------------------------------------- pipelined (ordinary buffers)
+// AllReduce of buffers that are NOT in symmetric memory, as ONE kernel whose blocks take three
+// roles that run concurrently, chunk by chunk:
+//
+//   copy-in   user send buffer -> my stage_a slot (converted to the wire type)
+//   reduce    my shard of the chunk: sum of all ranks' stage_a slots (multimem.ld_reduce through
+//             the switch, or 128-bit peer loads in rank order) -> every rank's stage_b slot
+//             (multimem.st, or peer stores), scale and output conversion fused in
+//   copy-out  my stage_b slot -> user recv buffer
+//
+// The staging areas are rings of kPipeSlots slots, so the copies of chunk c+1.. and c-1.. overlap
+// the reduction of chunk c and the NVLink transfer never waits for a local copy (a staged two-phase
+// kernel idles the links during both copies; separate copy kernels on side streams pay a launch and
+// a cross-rank barrier per chunk).  Hand-over between roles and ranks is by monotonic chunk counters
+// (PipeCtl): the last block of a role to finish a chunk publishes "chunk g done by rank r" to every
+// rank with st.release.sys; waits are bounded like every other wait of the library.
+//
+//   copy-in  of chunk g waits for red_done[g - K] of all ranks   (the slot's last readers)
+//   reduce   of chunk g waits for in_ready[g] of all ranks       (the data)
+//                         and for out_done[g - K] of all ranks   (stage_b slots free everywhere)
+//   copy-out of chunk g waits for red_done[g] of all ranks
+//
+// Chunk geometry: a chunk is N shards of E = a.shard_elems elements (a multiple of the vector
+// width); rank r reduces shard r of every chunk.  Inside a slot the chunk is laid out like the
+// user buffer, so both copies are straight copies.
+template <int NVLS>
+__device__ __forceinline__ void pipe_roles(int nblk, int& n_in, int& n_red) {
+  // switch path: the reduction needs few blocks (measured: ~32 saturate it); peer-to-peer wants more
+  const int share = NVLS ? 3 : 2;
+  n_in = (nblk * share + 5) / 10;
+  if (n_in < 1) n_in = 1;
+  n_red = nblk - 2 * n_in;
+  if (n_red < 1) n_red = 1;
+}
+
+// Last block of a role to finish the chunk in `slot` publishes `value` into flags[slot][me] of every rank.
+__device__ __forceinline__ void pipe_publish(const CommDev& c, int role, int slot, int role_blocks, size_t flag_off,
+                                             uint32_t value) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    PipeCtl* mine = reinterpret_cast<PipeCtl*>(c.ctrl[c.rank] + c.off_pipe);
+    __threadfence_system();  // this block's writes (local, peer, multicast) before the ticket
+    const uint32_t t = atomicAdd(&mine->tick[role][slot], 1u);
+    if (t == static_cast<uint32_t>(role_blocks - 1)) {
+      mine->tick[role][slot] = 0;
+      __threadfence_system();  // the other blocks' writes, seen through the ticket, before the flags
+      for (int k = 0; k < c.nranks; ++k) {
+        const int p = (c.rank + k) % c.nranks;
+        uint32_t* f = reinterpret_cast<uint32_t*>(c.ctrl[p] + c.off_pipe + flag_off) + slot * kMaxRanks + c.rank;
+        st_release_sys(f, value);
+      }
+    }
+  }
+}
+
+// All threads call; thread t < nranks waits for flags[slot][t] >= target.  False after a failed wait.
+__device__ __forceinline__ bool pipe_wait_all(const CommDev& c, BlockCtl& ctl, size_t flag_off, int slot, uint32_t target,
+                                              int blk) {
+  const int t = threadIdx.x;
+  if (t < c.nranks) {
+    const uint32_t* f = reinterpret_cast<const uint32_t*>(c.ctrl[c.rank] + c.off_pipe + flag_off) + slot * kMaxRanks + t;
+    const uint32_t r = wait_ge(f, target, c);
+    if (r != kDevOk) {
+      ctl.fail = r;
+      record_failure(c, r, (static_cast<uint32_t>(blk) << 16) | static_cast<uint32_t>(t));
+    }
+  }
+  __syncthreads();
+  return ctl.fail == 0;
+}
+
+template <typename InT, typename WireT, typename OutT, int OP, bool NVLS>
+__device__ __forceinline__ void pipe_body(const KParams& P, int blk, int nblk, BlockCtl& ctl) {
+  const CommDev& c = P.comm;
+  const CollArgs& a = P.args;
+  using Acc = typename Elem<WireT>::Acc;
+  using OAcc = typename Elem<OutT>::Acc;
+  using WRaw = typename Elem<WireT>::Raw;
+  using ORaw = typename Elem<OutT>::Raw;
+  constexpr int VW = 16 / sizeof(WRaw);
+  constexpr int OUT_VB = VW * sizeof(ORaw);
+  static_assert(OUT_VB % 16 == 0, "output vectors are whole 16-byte units for every supported type triple");
+  constexpr int U = 4;    // vectors in flight per thread in the reduction
+  constexpr int UC = 8;   // ... and in the two copies (bound by loads in flight, not by arithmetic)
+  constexpr bool kSameIn = std::is_same<InT, WireT>::value;
+  block_begin(c, blk, ctl);
+  const int N = c.nranks, me = c.rank;
+  if (N > 0 && a.count > 0) {
+    PipeCtl* pc = reinterpret_cast<PipeCtl*>(c.ctrl[me] + c.off_pipe);
+    const uint32_t base = pc->base;  // written only by the last block of a call, after everyone read it
+    const uint64_t E = a.shard_elems;
+    const uint64_t CE = E * uint64_t(N);              // elements per chunk
+    const uint32_t nchunks = static_cast<uint32_t>((a.count + CE - 1) / CE);
+    const uint64_t stride = c.stage_bytes / kPipeSlots;  // bytes per slot in both staging areas
+    constexpr size_t kOffIn = offsetof(PipeCtl, in_ready), kOffRed = offsetof(PipeCtl, red_done),
+                     kOffOut = offsetof(PipeCtl, out_done);
+    int n_in, n_red;
+    pipe_roles<NVLS ? 1 : 0>(nblk, n_in, n_red);
+    const int n_out = nblk - n_in - n_red;
+    const uint64_t tile = uint64_t(blockDim.x) * U;
+    const uint64_t ctile = uint64_t(blockDim.x) * UC;
+    char* my_a = c.ctrl[me] + c.off_stage_a;
+    char* my_b = c.ctrl[me] + c.off_stage_b;
+
+    if (blk < n_in) {
+      // ---------------------------------------------------------------- copy-in
+      const bool in_al = vec_aligned<InT, VW>(a.send);
+      for (uint32_t ch = 0; ch < nchunks; ++ch) {
+        const uint32_t g = base + ch;
+        const int slot = static_cast<int>(g % kPipeSlots);
+        if (g >= static_cast<uint32_t>(kPipeSlots) &&
+            !pipe_wait_all(c, ctl, kOffRed, slot, g - kPipeSlots + 1, blk)) break;
+        const uint64_t e_begin = uint64_t(ch) * CE;
+        const uint64_t e_end = (e_begin + CE < a.count) ? e_begin + CE : a.count;
+        const uint64_t nvec = (e_end - e_begin + VW - 1) / VW;
+        char* dst = my_a + uint64_t(slot) * stride;
+        const uint64_t full = (e_end - e_begin) / VW;  // vectors that lie wholly inside the chunk
+        for (uint64_t v0 = uint64_t(blk) * ctile + threadIdx.x; v0 < nvec; v0 += uint64_t(n_in) * ctile) {
+          if (kSameIn && in_al && v0 + uint64_t(UC - 1) * blockDim.x < full) {
+            // same type, aligned, no ragged end: move the bits
+            const uint4* src = reinterpret_cast<const uint4*>(static_cast<const WRaw*>(a.send) + e_begin);
+            uint4 x[UC];
+#pragma unroll
+            for (int u = 0; u < UC; ++u) x[u] = src[v0 + uint64_t(u) * blockDim.x];
+#pragma unroll
+            for (int u = 0; u < UC; ++u) *reinterpret_cast<uint4*>(dst + (v0 + uint64_t(u) * blockDim.x) * 16) = x[u];
+            continue;
+          }
+#pragma unroll 2
+          for (int u = 0; u < UC; ++u) {
+            const uint64_t v = v0 + uint64_t(u) * blockDim.x;
+            if (v >= nvec) continue;
+            typename Elem<InT>::Acc x[VW];
+            load_vec<InT, VW>(a.send, e_begin + v * VW, e_end, in_al, x);
+            Acc w[VW];
+#pragma unroll
+            for (int k = 0; k < VW; ++k) w[k] = static_cast<Acc>(x[k]);
+            Packed<WireT, VW> pk;
+            pk.from_acc(w);
+            *reinterpret_cast<uint4*>(dst + v * 16) = pk.vec.q[0];
+          }
+        }
+        pipe_publish(c, 0, slot, n_in, kOffIn, g + 1);
+      }
+    } else if (blk < n_in + n_red) {
+      // ---------------------------------------------------------------- reduce my shard
+      const int rb = blk - n_in;
+      for (uint32_t ch = 0; ch < nchunks; ++ch) {
+        const uint32_t g = base + ch;
+        const int slot = static_cast<int>(g % kPipeSlots);
+        if (!pipe_wait_all(c, ctl, kOffIn, slot, g + 1, blk)) break;
+        if (g >= static_cast<uint32_t>(kPipeSlots) &&
+            !pipe_wait_all(c, ctl, kOffOut, slot, g - kPipeSlots + 1, blk)) break;
+        const uint64_t e_begin = uint64_t(ch) * CE + uint64_t(me) * E;  // my shard of this chunk
+        uint64_t e_end = e_begin + E;
+        if (e_end > a.count) e_end = a.count;
+        const uint64_t nvec = e_begin < e_end ? (e_end - e_begin + VW - 1) / VW : 0;
+        const uint64_t in_off = uint64_t(slot) * stride + uint64_t(me) * E * sizeof(WRaw);
+        const uint64_t out_off = uint64_t(slot) * stride + uint64_t(me) * E * sizeof(ORaw);
+        for (uint64_t v0 = uint64_t(rb) * tile + threadIdx.x; v0 < nvec; v0 += uint64_t(n_red) * tile) {
+          Acc acc[U][VW];
+          if constexpr (NVLS) {
+            uint4 r[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const uint64_t v = v0 + uint64_t(u) * blockDim.x;
+              r[u] = make_uint4(0, 0, 0, 0);
+              if (v < nvec) r[u] = Nvls<WireT>::ld_reduce_add(c.ctrl_mc + c.off_stage_a + in_off + v * 16);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              Packed<WireT, VW> in;
+              in.vec.q[0] = r[u];
+              in.to_acc(acc[u]);
+            }
+          } else {
+            for (int r = 0; r < N; ++r) {
+              uint4 got[U];
+              const char* src = c.ctrl[r] + c.off_stage_a + in_off;
+#pragma unroll
+              for (int u = 0; u < U; ++u) {
+                const uint64_t v = v0 + uint64_t(u) * blockDim.x;
+                got[u] = make_uint4(0, 0, 0, 0);
+                if (v < nvec) got[u] = *reinterpret_cast<const uint4*>(src + v * 16);
+              }
+#pragma unroll
+              for (int u = 0; u < U; ++u) {
+                Packed<WireT, VW> in;
+                in.vec.q[0] = got[u];
+                Acc val[VW];
+                in.to_acc(val);
+#pragma unroll
+                for (int k = 0; k < VW; ++k) acc[u][k] = (r == 0) ? val[k] : combine<OP>(acc[u][k], val[k]);
+              }
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const uint64_t v = v0 + uint64_t(u) * blockDim.x;
+            if (v >= nvec) continue;
+            OAcc y[VW];
+#pragma unroll
+            for (int k = 0; k < VW; ++k) y[k] = finalize<OutT>(static_cast<OAcc>(acc[u][k]), a);
+            Packed<OutT, VW> pk;
+            pk.from_acc(y);
+            if constexpr (NVLS) {
+              char* dst = c.ctrl_mc + c.off_stage_b + out_off + v * OUT_VB;
+#pragma unroll
+              for (int q = 0; q < OUT_VB / 16; ++q) multimem_st_v4(dst + q * 16, pk.vec.q[q]);
+            } else {
+              for (int k = 0; k < N; ++k) {
+                const int p = (me + k) % N;
+                char* dst = c.ctrl[p] + c.off_stage_b + out_off + v * OUT_VB;
+#pragma unroll
+                for (int q = 0; q < OUT_VB / 16; ++q) reinterpret_cast<uint4*>(dst)[q] = pk.vec.q[q];
+              }
+            }
+          }
+        }
+        pipe_publish(c, 1, slot, n_red, kOffRed, g + 1);
+      }
+    } else {
+      // ---------------------------------------------------------------- copy-out
+      const int ob = blk - n_in - n_red;
+      const bool out_al = vec_aligned<OutT, VW>(a.recv);
+      for (uint32_t ch = 0; ch < nchunks; ++ch) {
+        const uint32_t g = base + ch;
+        const int slot = static_cast<int>(g % kPipeSlots);
+        if (!pipe_wait_all(c, ctl, kOffRed, slot, g + 1, blk)) break;
+        const uint64_t e_begin = uint64_t(ch) * CE;
+        const uint64_t e_end = (e_begin + CE < a.count) ? e_begin + CE : a.count;
+        const uint64_t nvec = (e_end - e_begin + VW - 1) / VW;
+        const char* src = my_b + uint64_t(slot) * stride;
+        const uint64_t full = (e_end - e_begin) / VW;
+        for (uint64_t v0 = uint64_t(ob) * ctile + threadIdx.x; v0 < nvec; v0 += uint64_t(n_out) * ctile) {
+          if (out_al && v0 + uint64_t(UC - 1) * blockDim.x < full) {
+            constexpr int Q = OUT_VB / 16;
+            uint4* dstv = reinterpret_cast<uint4*>(static_cast<ORaw*>(a.recv) + e_begin);
+            uint4 y[UC][Q];
+#pragma unroll
+            for (int u = 0; u < UC; ++u)
+#pragma unroll
+              for (int q = 0; q < Q; ++q) y[u][q] = reinterpret_cast<const uint4*>(src)[(v0 + uint64_t(u) * blockDim.x) * Q + q];
+#pragma unroll
+            for (int u = 0; u < UC; ++u)
+#pragma unroll
+              for (int q = 0; q < Q; ++q) dstv[(v0 + uint64_t(u) * blockDim.x) * Q + q] = y[u][q];
+            continue;
+          }
+#pragma unroll 2
+          for (int u = 0; u < UC; ++u) {
+            const uint64_t v = v0 + uint64_t(u) * blockDim.x;
+            if (v >= nvec) continue;
+            OAcc y[VW];
+            load_vec<OutT, VW>(src + v * OUT_VB, 0, VW, true, y);
+            store_vec<OutT, VW>(a.recv, e_begin + v * VW, e_end, out_al, y);
+          }
+        }
+        pipe_publish(c, 2, slot, n_out, kOffOut, g + 1);
+      }
+    }
+    // the last block to leave moves the base past this call's chunks
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      if (atomicAdd(&pc->finished, 1u) == static_cast<uint32_t>(nblk - 1)) {
+        pc->finished = 0;
+        pc->base = base + nchunks;
       }
     }
   }

@@ -9,6 +9,7 @@
 //   local    LocalState                    this rank's private counters
 //   ll       [2][nranks][ll_slot_bytes]    one-shot "LL" inboxes (flag+data)
 //   inbox    [2][nranks][inbox_slot_bytes] one-shot inboxes (barrier flavour)
+//   pipe     PipeCtl                       chunk flags of the pipelined AllReduce
 //   stage_a  [stage_bytes]                 staged inputs  (wire type)
 //   stage_b  [stage_bytes]                 staged outputs (output type)
 //
@@ -43,6 +44,22 @@ struct LocalState {
   uint32_t pad[3];
 };
 
+// Flags of the pipelined AllReduce on ordinary buffers (coll_kernels.cuh, pipe_body).  The staging
+// areas are rings of kPipeSlots slots; chunk number g (counted over ALL pipelined calls of the
+// communicator, so nothing is ever reset) lives in slot g % kPipeSlots and its flags carry g + 1.
+// in_ready / red_done / out_done are written by every rank into every rank's copy (index: slot,
+// then source rank); the tickets and the base are private to the owner.
+constexpr int kPipeSlots = 16;
+struct PipeCtl {
+  uint32_t in_ready[kPipeSlots][kMaxRanks];   // source rank has staged its input chunk
+  uint32_t red_done[kPipeSlots][kMaxRanks];   // source rank has reduced its shard of the chunk into every stage_b
+  uint32_t out_done[kPipeSlots][kMaxRanks];   // source rank has copied the chunk out of its stage_b
+  uint32_t tick[3][kPipeSlots];               // blocks of a role that have finished the chunk in this slot
+  uint32_t base;                              // number of chunks handled by earlier calls
+  uint32_t finished;                          // blocks that have left the running call
+  uint32_t pad[2];
+};
+
 struct CommDev {
   int32_t rank;
   int32_t nranks;
@@ -52,6 +69,7 @@ struct CommDev {
   volatile uint32_t* host_progress;     // host-mapped {started, done, status, detail}; may be null
   uint64_t spin_timeout_ns;       // budget of every device-side wait
   uint64_t off_sig, off_local, off_ll, off_inbox, off_stage_a, off_stage_b;
+  uint64_t off_pipe;              // PipeCtl
   uint64_t ll_slot_bytes, inbox_slot_bytes, stage_bytes;
 };
 
@@ -76,6 +94,14 @@ struct CollArgs {
 struct KParams {
   CommDev comm;
   CollArgs args;
+};
+
+// One launch, two messages (see nvls_split_kernel): blocks [0, nb_first) work on `args`, the rest on `args2`.
+struct KParamsSplit {
+  CommDev comm;
+  CollArgs args;
+  CollArgs args2;
+  int32_t nb_first;
 };
 
 }  // namespace mnccl

@@ -7,14 +7,14 @@
 
 namespace mnccl {
 
-enum class Algo : int { Auto = 0, LL = 1, OneShot = 2, TwoShot = 3, Nvls = 4, Ring = 5, Local = 6 };
+enum class Algo : int { Auto = 0, LL = 1, OneShot = 2, TwoShot = 3, Nvls = 4, Ring = 5, Local = 6, Pipe = 7 };
 enum class Mode : int { AllReduce = 0, ReduceScatter = 1, AllGather = 2 };
 
 inline const char* algo_name(Algo a) {
   switch (a) {
     case Algo::Auto: return "auto"; case Algo::LL: return "ll"; case Algo::OneShot: return "oneshot";
     case Algo::TwoShot: return "twoshot"; case Algo::Nvls: return "nvls"; case Algo::Ring: return "ring";
-    case Algo::Local: return "local";
+    case Algo::Local: return "local"; case Algo::Pipe: return "pipe";
   }
   return "?";
 }
@@ -27,6 +27,7 @@ struct LaunchSpec {
   int nblocks = 1;
   int nthreads = 512;
   int unroll = 4;  // vectors in flight per thread in the NVLS kernels (4 or 8)
+  bool pipe_nvls = false;  // Algo::Pipe: reduce through the switch (multimem) instead of peer loads / stores
 };
 
 // True when a kernel exists for this combination of algorithm, mode, types
@@ -35,6 +36,10 @@ bool kernel_exists(const LaunchSpec& spec);
 
 // Launch on one rank (the normal case).  `p` is passed by value to the kernel.
 cudaError_t launch_collective(const LaunchSpec& spec, const KParams& p, cudaStream_t stream);
+
+// NVLS AllReduce of a large message with a slice of it travelling peer-to-peer in the same launch:
+// blocks [0, p.nb_first) of spec.nblocks take p.args through the switch, the others p.args2.
+cudaError_t launch_nvls_split(const LaunchSpec& spec, const KParamsSplit& p, cudaStream_t stream);
 
 // Single-GPU emulation of `vranks` ranks: ONE cooperative launch whose grid is
 // vranks * spec.nblocks blocks; block g acts as block g % nblocks of rank

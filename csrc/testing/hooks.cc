@@ -107,6 +107,24 @@ MNCCL_EXPORT int mnccl_test_config(const char* env, char* out, size_t len) {
   });
 }
 
+// Applies a tuning table given as text for `nranks`; out: JSON of the tunable knobs and the loader's complaints.
+MNCCL_EXPORT int mnccl_test_tuning_text(const char* text, int nranks, char* out, size_t len) {
+  return guarded([&] {
+    Config c;
+    std::string errors;
+    const int applied = c.apply_tuning_text(text ? text : "", nranks, &errors);
+    for (char& ch : errors)
+      if (ch == '"' || ch == '\\') ch = '\'';
+    std::ostringstream o;
+    o << "{\"applied\":" << applied << ",\"ll_max_bytes\":" << c.ll_max_bytes << ",\"oneshot_max_bytes\":" << c.oneshot_max_bytes
+      << ",\"nvls_min_bytes\":" << c.nvls_min_bytes << ",\"pipe_min_bytes\":" << c.pipe_min_bytes << ",\"pipe_chunk_bytes\":"
+      << c.pipe_chunk_bytes << ",\"nvls_p2p_permille\":" << c.nvls_p2p_permille << ",\"max_blocks\":" << c.max_blocks
+      << ",\"errors\":\"" << errors << "\"}";
+    copy_out(o.str(), out, len);
+    return 0;
+  });
+}
+
 // ---- chunk schedule of the pipeline -------------------------------------------
 // Writes up to `max` chunk sizes (elements) to `out`; returns the number of chunks or a negative code.
 MNCCL_EXPORT int mnccl_test_pipeline_chunks(size_t count, size_t elem_bytes, size_t uniform_elems, size_t cap_elems, int taper,

@@ -96,7 +96,9 @@ typedef enum {
   mncclAlgoOneShot = 2,   /* one-shot push + per-block barrier             */
   mncclAlgoTwoShot = 3,   /* P2P reduce-scatter (pull) + all-gather (push) */
   mncclAlgoNvls = 4,      /* multimem.ld_reduce + multimem.st              */
-  mncclAlgoRing = 5       /* host-driven ring over the one-sided transport */
+  mncclAlgoRing = 5,      /* host-driven ring over the one-sided transport */
+  mncclAlgoLocal = 6,     /* one rank: copy with scale / conversion (reported only) */
+  mncclAlgoPipe = 7       /* ordinary buffers: copy-in, reduce, copy-out blocks of one kernel, chunk by chunk */
 } mncclAlgo_t;
 
 /* AllReduce fused with a dtype conversion and a scale:
@@ -161,6 +163,14 @@ ncclResult_t mncclCommDeviceHandle(ncclComm_t comm, void* out, size_t len, size_
 /* Launch tuning for the calls that follow (0 keeps the built-in value).  Every
  * rank must use the same values.  Meant for benchmarking sweeps. */
 ncclResult_t mncclCommSetTuning(ncclComm_t comm, int max_blocks, int unroll);
+
+/* One launch-tuning knob by the name of its environment variable without the MINI_NCCL_ prefix
+ * ("LL_MAX_BYTES", "ONESHOT_MAX_BYTES", "NVLS_MIN_BYTES", "PIPE_MIN_BYTES", "PIPE_CHUNK_BYTES",
+ * "NVLS_P2P_PERMILLE", "NVLS_P2P_BLOCKS", "MAX_BLOCKS", ...), for the calls that follow.  Every rank
+ * must use the same value.  The same knobs can be given per rank count in a table that
+ * MINI_NCCL_TUNING_FILE names (lines "<nranks> <KNOB> <value>", written by benchmarks/tune.py);
+ * environment variables win over the table. */
+ncclResult_t mncclCommSetKnob(ncclComm_t comm, const char* name, long long value);
 
 unsigned mncclVersion(void);
 

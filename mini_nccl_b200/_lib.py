@@ -22,7 +22,7 @@ INT8, UINT8, INT32, UINT32, INT64, UINT64, FLOAT16, FLOAT32, FLOAT64, BFLOAT16 =
 SUM, PROD, MAX, MIN, AVG = range(5)
 # mncclAlgo_t
 ALGO_AUTO, ALGO_LL, ALGO_ONESHOT, ALGO_TWOSHOT, ALGO_NVLS, ALGO_RING = range(6)
-ALGO_NAMES = {0: "auto", 1: "ll", 2: "oneshot", 3: "twoshot", 4: "nvls", 5: "ring", 6: "local"}
+ALGO_NAMES = {0: "auto", 1: "ll", 2: "oneshot", 3: "twoshot", 4: "nvls", 5: "ring", 6: "local", 7: "pipe"}
 DTYPE_SIZES = {INT8: 1, UINT8: 1, INT32: 4, UINT32: 4, INT64: 8, UINT64: 8, FLOAT16: 2, FLOAT32: 4, FLOAT64: 8, BFLOAT16: 2}
 
 
@@ -81,6 +81,7 @@ def lib() -> C.CDLL:
     sig("mncclCommQueryAlgo", i32, vp, sz, i32, i32, i32, P(i32))
     sig("mncclCommDeviceHandle", i32, vp, vp, sz, P(sz))
     sig("mncclCommSetTuning", i32, vp, i32, i32)
+    sig("mncclCommSetKnob", i32, vp, C.c_char_p, C.c_longlong)
     sig("mncclVersion", C.c_uint)
     # reference-compatible names (exported for C users; typed here for the ABI tests)
     sig("ncclGetErrorString", C.c_char_p, i32)
@@ -112,6 +113,7 @@ def lib() -> C.CDLL:
     sig("mncclEmuAlloc", i32, vp, sz, P(vp))
     sig("mncclEmuSetTimeoutNs", i32, vp, u64)
     sig("mncclEmuSetDeaf", i32, vp, i32, i32)
+    sig("mncclEmuSetPipeChunk", i32, vp, sz)
     sig("mncclEmuCollective", i32, vp, i32, P(vp), P(vp), sz, i32, i32, i32, i32, dbl, i32, i32, vp)
     sig("mncclEmuStatus", i32, vp, P(u32), P(u32))
     sig("mncclEmuLastPlan", i32, vp, P(i32), P(i32))
@@ -127,6 +129,7 @@ def lib() -> C.CDLL:
     sig("mnccl_bf16_to_float", C.c_float, C.c_uint16)
     sig("mnccl_half_to_float", C.c_float, C.c_uint16)
     sig("mnccl_test_config", i32, C.c_char_p, C.c_char_p, sz)
+    sig("mnccl_test_tuning_text", i32, C.c_char_p, i32, C.c_char_p, sz)
     sig("mnccl_test_spsc", i32, i32, i32)
     sig("mnccl_test_request_pool", i32, i32)
     sig("mnccl_test_reg_cache", i32)

@@ -42,10 +42,10 @@ HOST_SOURCES = [
     "comm.cc", "api.cc", "testing/hooks.cc",
 ]
 CUDA_SOURCES = [
-    "kernels/k_small.cu", "kernels/k_twoshot.cu", "kernels/k_rsag.cu", "kernels/k_nvls.cu",
+    "kernels/k_small.cu", "kernels/k_twoshot.cu", "kernels/k_rsag.cu", "kernels/k_nvls.cu", "kernels/k_pipe.cu",
     "kernels/launch.cu", "emu/emu_world.cu",
 ]
-# Optional translation units: compiled when present (later build stages add them).
+# Translation units compiled when present (a source tree may be trimmed to the collectives alone).
 OPTIONAL_CUDA = ["kernels/gemm_sm100.cu", "kernels/gemm_fused.cu", "kernels/noalloc.cu", "kernels/elementwise.cu"]
 OPTIONAL_HOST = ["net/verbs_transport.cc"]
 

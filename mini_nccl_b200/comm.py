@@ -45,7 +45,7 @@ def _torch_dtype_code(dt) -> int:
 
 
 _OPS = {"sum": _lib.SUM, "prod": _lib.PROD, "max": _lib.MAX, "min": _lib.MIN, "avg": _lib.AVG}
-_ALGOS = {"auto": 0, "ll": 1, "oneshot": 2, "twoshot": 3, "nvls": 4, "ring": 5}
+_ALGOS = {"auto": 0, "ll": 1, "oneshot": 2, "twoshot": 3, "nvls": 4, "ring": 5, "pipe": 7}
 
 
 class Communicator:
@@ -196,6 +196,11 @@ class Communicator:
     def set_tuning(self, max_blocks: int = 0, unroll: int = 0) -> None:
         """Grid cap and NVLS unroll for the calls that follow (0 = built-in).  Same values on every rank."""
         check(lib().mncclCommSetTuning(self._h, max_blocks, unroll), "mncclCommSetTuning")
+
+    def set_knob(self, name: str, value: int) -> None:
+        """One launch-tuning knob by the name of its environment variable without the ``MINI_NCCL_``
+        prefix (``"PIPE_CHUNK_BYTES"``, ``"NVLS_P2P_PERMILLE"``, ...).  Same value on every rank."""
+        check(lib().mncclCommSetKnob(self._h, name.encode(), int(value)), "mncclCommSetKnob(%s)" % name)
 
     def query_algo(self, nbytes: int, dtype=None, op: str = "sum", registered: bool = False) -> str:
         a = C.c_int()

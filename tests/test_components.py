@@ -131,6 +131,33 @@ def plan(lib, n, count, dtype=_lib.FLOAT32, op=_lib.SUM, mode=0, in_sym=0, out_s
     return dict(algo=_lib.ALGO_NAMES[algo.value], nblocks=nb.value, shard=se.value, chunk=cv.value, copy_in=cin.value, copy_out=cout.value)
 
 
+def test_tuning_table_loader(lib):
+    """MINI_NCCL_TUNING_FILE: lines '<nranks> <KNOB> <value>'; rows for other rank counts are skipped,
+    nranks 0 matches all, comments and blank lines are ignored, bad rows are reported and skipped."""
+    import json
+
+    text = """# measured on some machine
+8 LL_MAX_BYTES 32768
+8 ONESHOT_MAX_BYTES 262144   # crossover to the two-phase kernels
+4 ONESHOT_MAX_BYTES 1048576
+0 PIPE_MIN_BYTES 16777216
+8 MINI_NCCL_NVLS_P2P_PERMILLE 150
+
+8 NO_SUCH_KNOB 1
+8 MAX_BLOCKS 100000
+garbage here
+"""
+    buf = C.create_string_buffer(2048)
+    assert lib.mnccl_test_tuning_text(text.encode(), 8, buf, len(buf)) == 0
+    got = json.loads(buf.value.decode())
+    assert got["applied"] == 4 and got["ll_max_bytes"] == 32768 and got["oneshot_max_bytes"] == 262144
+    assert got["pipe_min_bytes"] == 16777216 and got["nvls_p2p_permille"] == 150 and got["max_blocks"] == 0
+    assert "NO_SUCH_KNOB" in got["errors"] and "MAX_BLOCKS" in got["errors"] and "line 10" in got["errors"]
+    assert lib.mnccl_test_tuning_text(text.encode(), 4, buf, len(buf)) == 0
+    got = json.loads(buf.value.decode())
+    assert got["applied"] == 2 and got["oneshot_max_bytes"] == 1048576 and got["ll_max_bytes"] == 0
+
+
 def test_planner_picks_by_size(lib):
     assert plan(lib, 8, 2048)["algo"] == "ll"                      # 8 KB
     assert plan(lib, 8, 16384)["algo"] == "ll"                     # 64 KB
@@ -151,7 +178,7 @@ def test_planner_geometry(lib):
     assert p["copy_in"] == 1 and p["copy_out"] == 1
     z = plan(lib, 8, 1 << 24, in_sym=1, out_sym=1, nvls=1)
     assert z["algo"] == "nvls" and z["copy_in"] == 0 and z["copy_out"] == 0 and z["chunk"] * 4 == z["shard"]
-    s = plan(lib, 4, 1 << 26, stage=1 << 20)           # 256 MB through 1 MB of staging: many passes
+    s = plan(lib, 4, 1 << 26, stage=1 << 20, forced=_lib.ALGO_TWOSHOT)   # 256 MB through 1 MB of staging: many passes
     assert s["chunk"] == (1 << 20) // (4 * 16)
     assert 1 <= s["nblocks"] <= 512
     assert plan(lib, 4, 1000, dtype=_lib.FLOAT32, wire=_lib.INT32) is None   # no such cast
@@ -159,6 +186,23 @@ def test_planner_geometry(lib):
     assert rs["algo"] == "twoshot" and rs["shard"] == 1001 and rs["copy_out"] == 0
     ag = plan(lib, 4, 1001, mode=2)
     assert ag["algo"] == "twoshot" and ag["copy_in"] == 0 and ag["copy_out"] == 1
+
+
+def test_planner_pipelined_kernel_for_large_ordinary_buffers(lib):
+    """Ordinary device buffers of 24 MB and more take the pipelined kernel; its chunk is N shards of
+    whole vectors and fits one of the 16 ring slots of either staging area."""
+    p = plan(lib, 8, 1 << 26, nvls=1)                    # 256 MB fp32, ordinary buffers
+    assert p["algo"] == "pipe" and p["copy_in"] == 1 and p["copy_out"] == 1
+    assert p["shard"] % 4 == 0 and p["shard"] * 8 * 4 <= (256 << 20) // 16 and 3 <= p["nblocks"] <= 140
+    assert plan(lib, 8, 1 << 26, nvls=1, in_sym=1, out_sym=1)["algo"] == "nvls"     # symmetric buffers stay zero-copy
+    assert plan(lib, 8, (8 << 20) // 4, nvls=1)["algo"] != "pipe"                    # below the threshold
+    q = plan(lib, 2, 1 << 26)                            # two ranks: peer-to-peer reduction inside the same kernel
+    assert q["algo"] == "pipe" and q["shard"] % 4 == 0
+    m = plan(lib, 8, 1 << 25, nvls=1, wire=_lib.BFLOAT16, out=_lib.FLOAT32)          # fp32 out of a bf16 wire: slot bound by the output
+    assert m["algo"] == "pipe" and m["shard"] % 8 == 0 and m["shard"] * 8 * 4 <= (256 << 20) // 16
+    t = plan(lib, 4, 1 << 26, stage=1 << 20)             # tiny staging: 64 KB slots
+    assert t["algo"] == "pipe" and t["shard"] * 4 * 4 <= (1 << 20) // 16
+    assert plan(lib, 8, 1 << 26, mode=1)["algo"] == "twoshot"                        # only AllReduce is pipelined
 
 
 def test_gemm_host_plan_picks_tiles_and_cta_pairs():

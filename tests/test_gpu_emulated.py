@@ -20,7 +20,7 @@ pytestmark = pytest.mark.gpu
 ALL_DTYPES = [_lib.INT8, _lib.UINT8, _lib.INT32, _lib.UINT32, _lib.INT64, _lib.UINT64, _lib.FLOAT16, _lib.FLOAT32,
               _lib.FLOAT64, _lib.BFLOAT16]
 ALL_OPS = [_lib.SUM, _lib.PROD, _lib.MAX, _lib.MIN, _lib.AVG]
-ALGOS = {"ll": _lib.ALGO_LL, "oneshot": _lib.ALGO_ONESHOT, "twoshot": _lib.ALGO_TWOSHOT}
+ALGOS = {"ll": _lib.ALGO_LL, "oneshot": _lib.ALGO_ONESHOT, "twoshot": _lib.ALGO_TWOSHOT, "pipe": 7}
 
 
 class World:
@@ -263,3 +263,45 @@ def test_missing_rank_fails_bounded(lib):
         w.close()
     x = torch.ones(16, device="cuda")
     assert float((x + 1).sum()) == 32.0
+
+
+# ------------------------------------------------------------------ pipelined kernel (ordinary buffers)
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_pipe_kernel_wraps_slot_ring(worlds, lib, n):
+    """Copy-in, reduce and copy-out blocks of ONE kernel, chunk by chunk: with 64 KB chunks a
+    message of a few MB runs many times around the ring of 16 staging slots, and the second and
+    third call continue the chunk numbering where the one before stopped."""
+    w = worlds(n, 64 << 20)
+    assert lib.mncclEmuSetPipeChunk(w.h, 64 << 10) == 0
+    try:
+        for count in (3 * 1024 * 1024 + 77, 1 << 20, 16 * 1024 + 3, 5):
+            check_allreduce(w, count, _lib.FLOAT32, _lib.SUM, ALGOS["pipe"], seed=count)
+            assert w.last_plan()[0] == "pipe"
+        check_allreduce(w, 2 * 1024 * 1024 + 1, _lib.BFLOAT16, _lib.SUM, ALGOS["pipe"], scale=1.0 / n)
+        check_allreduce(w, 700001, _lib.FLOAT32, _lib.SUM, ALGOS["pipe"], misalign=1)          # unaligned user buffers
+        check_allreduce(w, 1 << 20, _lib.FLOAT32, _lib.SUM, ALGOS["pipe"], wire=_lib.BFLOAT16)  # fp32 -> bf16 wire -> fp32
+        check_allreduce(w, 1 << 20, _lib.FLOAT32, _lib.SUM, ALGOS["pipe"], wire=_lib.BFLOAT16, out_t=_lib.BFLOAT16)
+        check_allreduce(w, 300001, _lib.INT32, _lib.MAX, ALGOS["pipe"])
+        check_allreduce(w, 300001, _lib.FLOAT64, _lib.PROD, ALGOS["pipe"])
+        check_allreduce(w, 1 << 20, _lib.FLOAT32, _lib.SUM, ALGOS["pipe"], in_place=True)
+    finally:
+        lib.mncclEmuSetPipeChunk(w.h, 0)
+
+
+def test_pipe_kernel_is_the_automatic_choice_for_large_ordinary_buffers(worlds):
+    w = worlds(4, 0)
+    check_allreduce(w, (32 << 20) // 4 + 3, _lib.FLOAT32, _lib.SUM, 0)
+    assert w.last_plan()[0] == "pipe"
+    check_allreduce(w, (8 << 20) // 4, _lib.FLOAT32, _lib.SUM, 0)   # below the threshold: staged two-phase kernel
+    assert w.last_plan()[0] != "pipe"
+
+
+def test_pipe_kernel_few_blocks(worlds, lib):
+    """Three blocks (one per role) are the smallest grid; the roles must still hand over correctly."""
+    w = worlds(2, 64 << 20)
+    assert lib.mncclEmuSetPipeChunk(w.h, 256 << 10) == 0
+    try:
+        for nb in (3, 4, 5, 7):
+            check_allreduce(w, 2 * 1024 * 1024 + 9, _lib.FLOAT32, _lib.SUM, ALGOS["pipe"], nblocks=nb, seed=nb)
+    finally:
+        lib.mncclEmuSetPipeChunk(w.h, 0)
