@@ -554,46 +554,8 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
     if (plan.copy_in || plan.copy_out) stats_.staged_passes++;
   }
   if (plan.spec.algo == Algo::Pipe) stats_.staged_passes++;
-  // A large zero-copy NVLS AllReduce can hand a slice of the message to peer-to-peer blocks of the
-  // same launch (the switch's reduction rate, not the links, bounds the NVLS path).
-  const uint64_t vw = 16 / dtype_size(wire_t);
-  uint64_t n2 = 0;
-  if (plan.spec.algo == Algo::Nvls && mode == Mode::AllReduce && !plan.copy_in && !plan.copy_out &&
-      cfg_.nvls_p2p_permille > 0 && count * dtype_size(wire_t) >= cfg_.nvls_p2p_min_bytes) {
-    const uint64_t unit = vw * static_cast<uint64_t>(size_);
-    const uint64_t n1 = count * static_cast<uint64_t>(1000 - cfg_.nvls_p2p_permille) / 1000 / unit * unit;
-    if (n1 >= unit && n1 < count) n2 = count - n1;
-  }
   if (size_ == 1 && mode == Mode::AllReduce && send == recv && send_t == recv_t && factor == 1.0) {
     // Nothing to do; keep stream order semantics without a launch.
-  } else if (n2 != 0) {
-    KParamsSplit ks;
-    memset(&ks, 0, sizeof(ks));
-    ks.comm = kp.comm;
-    ks.args = kp.args;
-    ks.args2 = kp.args;
-    const uint64_t n1 = count - n2;
-    CollArgs& a1 = ks.args;
-    CollArgs& a2 = ks.args2;
-    a1.count = n1;
-    a1.shard_elems = n1 / size_;
-    a1.chunk_shard_vecs = a1.shard_elems / vw;
-    a2.count = n2;
-    a2.shard_elems = ((n2 + vw - 1) / vw + size_ - 1) / size_ * vw;
-    a2.chunk_shard_vecs = a2.shard_elems / vw;
-    a2.send = static_cast<const char*>(send) + n1 * dtype_size(send_t);
-    a2.recv = static_cast<char*>(recv) + n1 * dtype_size(recv_t);
-    for (int r = 0; r < size_; ++r) {
-      a2.in_peer[r] += n1 * dtype_size(wire_t);
-      a2.out_peer[r] += n1 * dtype_size(recv_t);
-    }
-    a2.in_mc = a2.out_mc = nullptr;
-    LaunchSpec spec = plan.spec;
-    const uint64_t tiles1 = (a1.chunk_shard_vecs + 2047) / 2048;
-    ks.nb_first = static_cast<int>(std::min<uint64_t>(std::max<uint64_t>(tiles1, 1), cfg_.max_blocks > 0 ? cfg_.max_blocks : 32));
-    spec.nblocks = ks.nb_first + cfg_.nvls_p2p_blocks;
-    spec.unroll = 4;
-    RT_CHECK(launch_nvls_split(spec, ks, stream), "kernel launch");
   } else {
     RT_CHECK(launch_collective(plan.spec, kp, stream), "kernel launch");
   }

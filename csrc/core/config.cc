@@ -99,9 +99,6 @@ Config Config::from_getter(Getter get, void* ctx) {
   r.num("MINI_NCCL_HOST_CHUNK_BYTES", c.host_chunk_bytes);
   r.num("MINI_NCCL_PIPE_MIN_BYTES", c.pipe_min_bytes);
   r.num("MINI_NCCL_PIPE_CHUNK_BYTES", c.pipe_chunk_bytes);
-  r.num("MINI_NCCL_NVLS_P2P_PERMILLE", c.nvls_p2p_permille);
-  r.num("MINI_NCCL_NVLS_P2P_BLOCKS", c.nvls_p2p_blocks);
-  r.num("MINI_NCCL_NVLS_P2P_MIN_BYTES", c.nvls_p2p_min_bytes);
   r.num("MINI_NCCL_MAX_BLOCKS", c.max_blocks);
   r.num("MINI_NCCL_UNROLL", c.unroll);
   r.boolean("MINI_NCCL_NUMA_BIND", c.numa_bind);
@@ -120,9 +117,6 @@ Config Config::from_getter(Getter get, void* ctx) {
   if (c.socket_timeout_ms <= 0) c.socket_timeout_ms = 1;
   if (c.connect_retries <= 0) c.connect_retries = 1;
   if (c.host_chunk_bytes < (64u << 10)) c.host_chunk_bytes = 64u << 10;
-  if (c.nvls_p2p_permille < 0) c.nvls_p2p_permille = 0;
-  if (c.nvls_p2p_permille > 900) c.nvls_p2p_permille = 900;
-  if (c.nvls_p2p_blocks < 1) c.nvls_p2p_blocks = 1;
   if (c.staging_bytes < (1u << 20)) c.staging_bytes = 1u << 20;
   c.staging_bytes = (c.staging_bytes + 4095) & ~size_t(4095);
   return c;
@@ -136,12 +130,10 @@ bool Config::set_knob(const std::string& name, long long v) {
       {"LL_MAX_BYTES", &Config::ll_max_bytes}, {"ONESHOT_MAX_BYTES", &Config::oneshot_max_bytes},
       {"NVLS_MIN_BYTES", &Config::nvls_min_bytes}, {"PIPELINE_MIN_BYTES", &Config::pipeline_min_bytes},
       {"PIPE_MIN_BYTES", &Config::pipe_min_bytes}, {"PIPE_CHUNK_BYTES", &Config::pipe_chunk_bytes},
-      {"NVLS_P2P_MIN_BYTES", &Config::nvls_p2p_min_bytes}, {"HOST_PIPELINE_MIN_BYTES", &Config::host_pipeline_min_bytes},
-      {"HOST_CHUNK_BYTES", &Config::host_chunk_bytes},
+      {"HOST_PIPELINE_MIN_BYTES", &Config::host_pipeline_min_bytes}, {"HOST_CHUNK_BYTES", &Config::host_chunk_bytes},
   };
   static const IntKnob ints[] = {
       {"MAX_BLOCKS", &Config::max_blocks, 0, 512}, {"UNROLL", &Config::unroll, 0, 8},
-      {"NVLS_P2P_PERMILLE", &Config::nvls_p2p_permille, 0, 900}, {"NVLS_P2P_BLOCKS", &Config::nvls_p2p_blocks, 1, 256},
   };
   for (const auto& k : sizes)
     if (name == k.name) {
@@ -190,8 +182,8 @@ int Config::apply_tuning_text(const std::string& text, int nranks, std::string* 
 // Environment variables win over the tuning table: applied again after it.
 static void reapply_env_knobs(Config& c) {
   static const char* const names[] = {"LL_MAX_BYTES", "ONESHOT_MAX_BYTES", "NVLS_MIN_BYTES", "PIPELINE_MIN_BYTES",
-                                      "PIPE_MIN_BYTES", "PIPE_CHUNK_BYTES", "NVLS_P2P_MIN_BYTES", "HOST_PIPELINE_MIN_BYTES",
-                                      "HOST_CHUNK_BYTES", "MAX_BLOCKS", "UNROLL", "NVLS_P2P_PERMILLE", "NVLS_P2P_BLOCKS"};
+                                      "PIPE_MIN_BYTES", "PIPE_CHUNK_BYTES", "HOST_PIPELINE_MIN_BYTES", "HOST_CHUNK_BYTES",
+                                      "MAX_BLOCKS", "UNROLL"};
   for (const char* n : names) {
     const std::string var = std::string("MINI_NCCL_") + n;
     if (const char* v = getenv(var.c_str())) {

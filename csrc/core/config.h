@@ -46,9 +46,6 @@ struct Config {
   size_t pipeline_min_bytes = 48u << 20;  // MINI_NCCL_PIPELINE_MIN_BYTES: ordinary buffers of at least this size go through the chunk pipeline (0 = never)
   size_t pipe_min_bytes = 24u << 20;  // MINI_NCCL_PIPE_MIN_BYTES: ordinary DEVICE buffers of at least this size take the pipelined kernel (copy-in, reduce, copy-out blocks in one launch); 0 = never (then MINI_NCCL_PIPELINE_MIN_BYTES decides on the stream pipeline)
   size_t pipe_chunk_bytes = 0;        // MINI_NCCL_PIPE_CHUNK_BYTES: chunk of that kernel (0 = a sixteenth of the message, 1 to 8 MB)
-  int nvls_p2p_permille = 0;          // MINI_NCCL_NVLS_P2P_PERMILLE: share (in 1/1000) of a large zero-copy NVLS AllReduce that travels peer-to-peer in the same launch (0 = none)
-  int nvls_p2p_blocks = 48;           // MINI_NCCL_NVLS_P2P_BLOCKS: blocks of that peer-to-peer share
-  size_t nvls_p2p_min_bytes = 64u << 20;  // MINI_NCCL_NVLS_P2P_MIN_BYTES: smallest message that is split
   int max_blocks = 0;                 // MINI_NCCL_MAX_BLOCKS (0 = built-in)
   int unroll = 0;                     // MINI_NCCL_UNROLL (NVLS vectors in flight per thread: 4 or 8; 0 = built-in)
   bool numa_bind = true;              // MINI_NCCL_NUMA_BIND (verbs path only, calling thread)
@@ -71,7 +68,6 @@ struct Config {
   static const Config& reload();
 
   // Sets one numeric tuning knob by the name of its environment variable without the MINI_NCCL_
-  // prefix ("LL_MAX_BYTES", "PIPE_CHUNK_BYTES", "NVLS_P2P_PERMILLE", ...).  False for an unknown name
   // or a value out of range.  Only launch-tuning knobs can be set this way (not ports or timeouts).
   bool set_knob(const std::string& name, long long value);
   // Applies a tuning table (MINI_NCCL_TUNING_FILE; written by benchmarks/tune.py) for `nranks`:

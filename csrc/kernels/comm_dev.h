@@ -96,12 +96,4 @@ struct KParams {
   CollArgs args;
 };
 
-// One launch, two messages (see nvls_split_kernel): blocks [0, nb_first) work on `args`, the rest on `args2`.
-struct KParamsSplit {
-  CommDev comm;
-  CollArgs args;
-  CollArgs args2;
-  int32_t nb_first;
-};
-
 }  // namespace mnccl

@@ -15,7 +15,6 @@ struct LaunchCtx {
   int vranks;            // 0: query only (does the kernel exist?), 1: normal, >1: emulated
   cudaStream_t stream;
   int* occupancy_out;    // non-null: report max co-resident blocks per SM instead of launching
-  const KParamsSplit* split = nullptr;  // the two-message NVLS + peer-to-peer launch
 };
 
 template <typename KernelT, typename EmuT>

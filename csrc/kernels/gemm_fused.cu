@@ -245,9 +245,58 @@ struct AgEpilogue {
   uint32_t* bar[kMaxTpRanks];        // every rank's barrier words [n_comm][nranks]
   StoreEpilogue<false> plain;
 
+  int swiglu;                        // 1: the store applies SwiGLU (see store_swiglu); C is [M, N / 2]
+  int chunks_per_tile;               // 32-column pieces per tile (tile width / 32)
+
   __device__ __forceinline__ void store(const GemmArgs& g, uint32_t epoch, int row, int col, const uint32_t (&r)[32],
                                         int chunk, uint8_t* warp_smem, int lane) const {
-    plain.store(g, epoch, row, col, r, chunk, warp_smem, lane);
+    if (swiglu) store_swiglu(g, row, col, r, chunk, warp_smem, lane);
+    else plain.store(g, epoch, row, col, r, chunk, warp_smem, lane);
+  }
+
+  // SwiGLU in the epilogue.  The weight's rows (the GEMM's columns) come interleaved in groups of 16:
+  // columns [32k, 32k+16) are gate features 16k.., columns [32k+16, 32k+32) the up features of the
+  // same indices, so one 32-column piece of an accumulator row holds both operands of 16 outputs:
+  //   act[row, 16k + j] = silu(acc[32k + j]) * acc[32k + 16 + j]        (fp32 math, one rounding)
+  // Up to four pieces (64 outputs = 128 bytes per row) are collected in shared memory and leave as
+  // whole rows, 8 lanes per row.  The H = (gate | up) matrix never reaches memory: the kernel
+  // writes half the bytes and the separate elementwise pass disappears.
+  __device__ __forceinline__ void store_swiglu(const GemmArgs& g, int row, int col, const uint32_t (&r)[32], int chunk,
+                                               uint8_t* warp_smem, int lane) const {
+    if (col >= g.N) return;  // the same for the whole warp (N is a multiple of 32 here)
+    const int part = chunk & 3;
+    uint8_t* mine = warp_smem + lane * kEpiRowBytes + part * 32;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      uint4 v;
+      uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int i = 8 * j + 2 * k;
+        const float g0 = __uint_as_float(r[i]), g1 = __uint_as_float(r[i + 1]);
+        const float u0 = __uint_as_float(r[16 + i]), u1 = __uint_as_float(r[16 + i + 1]);
+        __nv_bfloat162 p = __floats2bfloat162_rn(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+        w[k] = *reinterpret_cast<uint32_t*>(&p);
+      }
+      *reinterpret_cast<uint4*>(mine + j * 16) = v;
+    }
+    const bool flush = part == 3 || chunk == chunks_per_tile - 1 || col + 32 >= g.N;
+    if (!flush) return;
+    __syncwarp();
+    const int row_base = row - lane;
+    const int out_col = (col - part * 32) / 2;       // first output column of the collected pieces
+    const int out_cols = (part + 1) * 16;
+    __nv_bfloat16* c = static_cast<__nv_bfloat16*>(g.c);
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int rr = it * 4 + (lane >> 3), seg = lane & 7;
+      const int grow = row_base + rr;
+      if (grow < g.M && seg * 8 < out_cols) {
+        const uint4 v = *reinterpret_cast<const uint4*>(warp_smem + rr * kEpiRowBytes + seg * 16);
+        *reinterpret_cast<uint4*>(c + static_cast<size_t>(grow) * g.ldc + out_col + seg * 8) = v;
+      }
+    }
+    __syncwarp();
   }
   static constexpr int kWarpSmemBytes = kEpiWarpBytes;
   static constexpr int kSingleStages = kStages;
@@ -427,11 +476,15 @@ MNCCL_EXPORT int mncclGemmReduceScatterBf16(const void* A, const void* B, void* 
 // already be at rows [rank * M/nranks, ...) of its own buffer.  ready_peers / bar_peers: counter
 // and barrier words of every rank; state: two zero-initialised device words of this rank.
 // n_comm_ctas CTAs of the grid move data instead of computing (0 = default).
-MNCCL_EXPORT int mncclAllGatherGemmBf16(void* const* xg_peers, const void* B, void* C, int M, int N, int K, int lda, int ldb,
-                                        int ldc, int rank, int nranks, void* const* ready_peers, void* const* bar_peers,
-                                        uint32_t* state, int n_comm_ctas, cudaStream_t stream) {
+static int ag_gemm_launch(void* const* xg_peers, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                          int rank, int nranks, void* const* ready_peers, void* const* bar_peers, uint32_t* state,
+                          int n_comm_ctas, bool swiglu, cudaStream_t stream) {
   if (!xg_peers || !B || !C || !state) return -1;
   if (!check_common(M, N, K, rank, nranks, "all-gather->GEMM")) return -2;
+  if (swiglu && (N % 32 != 0 || (ldc != 0 && ldc % 8 != 0) || (reinterpret_cast<uintptr_t>(C) & 15u) != 0)) {
+    fprintf(stderr, "[Mini-NCCL] all-gather->GEMM with SwiGLU: needs N a multiple of 32, ldc a multiple of 8 and C 16-byte aligned\n");
+    return -2;
+  }
   if (nranks > 1 && (!ready_peers || !bar_peers)) return -1;
   if (K * 2 > kStages * kStageBytes / 4) {
     fprintf(stderr, "[Mini-NCCL] all-gather->GEMM: K too large for the row ring (max %d)\n", kStages * kStageBytes / 8);
@@ -439,13 +492,14 @@ MNCCL_EXPORT int mncclAllGatherGemmBf16(void* const* xg_peers, const void* B, vo
   }
   if (lda == 0) lda = K;
   if (ldb == 0) ldb = K;
-  if (ldc == 0) ldc = N;
+  if (ldc == 0) ldc = swiglu ? N / 2 : N;
   CUtensorMap ta, tb;
   std::string why;
   // The A operand is this rank's own gather buffer: TMA only ever reads local memory.
   const bool pair = ((M / nranks) % (2 * kBM)) == 0 && want_pair(M, N, sm_count() - (nranks > 1 ? 16 : 0)) &&
                     2 * max_pairs<AgEpilogue>() >= (sm_count() & ~1);
-  const int bn = pair ? kBN : pick_tile_n(M, N, sm_count() - (nranks > 1 ? 16 : 0), true);
+  // (the SwiGLU store collects pairs of 32-column pieces: no 224-wide tiles then)
+  const int bn = pair ? kBN : pick_tile_n(M, N, sm_count() - (nranks > 1 ? 16 : 0), !swiglu);
   if (!make_tensor_map_bf16(&ta, xg_peers[rank], M, K, lda, kBM, kBK, &why) ||
       !make_tensor_map_bf16(&tb, B, N, K, ldb, pair ? kBN / 2 : bn, kBK, &why)) {
     fprintf(stderr, "[Mini-NCCL] all-gather->GEMM: %s\n", why.c_str());
@@ -474,6 +528,8 @@ MNCCL_EXPORT int mncclAllGatherGemmBf16(void* const* xg_peers, const void* B, vo
   epi.nranks = nranks;
   epi.rows_per_rank = M / nranks;
   epi.lda = lda;
+  epi.swiglu = swiglu ? 1 : 0;
+  epi.chunks_per_tile = bn / 32;
   for (int r = 0; r < nranks; ++r) {
     epi.xg[r] = static_cast<char*>(xg_peers[r]);
     epi.ready[r] = nranks > 1 ? static_cast<uint32_t*>(ready_peers[r]) : nullptr;
@@ -508,6 +564,23 @@ MNCCL_EXPORT int mncclAllGatherGemmBf16(void* const* xg_peers, const void* B, vo
   cudaError_t e = pair ? launch_pair(ta, tb, g, epi, n_gemm + n_comm, stream)
                        : launch(ta, tb, g, epi, n_gemm + n_comm, stream, bn);
   return e == cudaSuccess ? 0 : static_cast<int>(e) + 1000;
+}
+
+MNCCL_EXPORT int mncclAllGatherGemmBf16(void* const* xg_peers, const void* B, void* C, int M, int N, int K, int lda, int ldb,
+                                        int ldc, int rank, int nranks, void* const* ready_peers, void* const* bar_peers,
+                                        uint32_t* state, int n_comm_ctas, cudaStream_t stream) {
+  return ag_gemm_launch(xg_peers, B, C, M, N, K, lda, ldb, ldc, rank, nranks, ready_peers, bar_peers, state, n_comm_ctas, false,
+                        stream);
+}
+
+// The same with SwiGLU applied in the epilogue: act[M, N / 2] = silu(gate) * up, where B's rows are
+// interleaved in groups of 16 (rows [32k, 32k+16) gate features 16k.., rows [32k+16, 32k+32) the up
+// features of the same indices).  N must be a multiple of 32; ldc (0 = N / 2) a multiple of 8.
+MNCCL_EXPORT int mncclAllGatherGemmSwiGluBf16(void* const* xg_peers, const void* B, void* act, int M, int N, int K, int lda,
+                                              int ldb, int ldc, int rank, int nranks, void* const* ready_peers,
+                                              void* const* bar_peers, uint32_t* state, int n_comm_ctas, cudaStream_t stream) {
+  return ag_gemm_launch(xg_peers, B, act, M, N, K, lda, ldb, ldc, rank, nranks, ready_peers, bar_peers, state, n_comm_ctas, true,
+                        stream);
 }
 
 }  // extern "C"

@@ -12,7 +12,6 @@ cudaError_t dispatch_nvls_ar(const LaunchCtx&);
 cudaError_t dispatch_rs(const LaunchCtx&);
 cudaError_t dispatch_rs_nvls(const LaunchCtx&);
 cudaError_t dispatch_ag(const LaunchCtx&);
-cudaError_t dispatch_nvls_split(const LaunchCtx&);
 cudaError_t dispatch_pipe(const LaunchCtx&);
 cudaError_t dispatch_pipe_nvls(const LaunchCtx&);
 }  // namespace dev
@@ -27,7 +26,7 @@ cudaError_t route(const dev::LaunchCtx& x) {
         case Algo::LL: return dev::dispatch_ll(x);
         case Algo::OneShot: return dev::dispatch_oneshot(x);
         case Algo::TwoShot: return dev::dispatch_twoshot_ar(x);
-        case Algo::Nvls: return x.split ? dev::dispatch_nvls_split(x) : dev::dispatch_nvls_ar(x);
+        case Algo::Nvls: return dev::dispatch_nvls_ar(x);
         case Algo::Pipe: return s.pipe_nvls ? dev::dispatch_pipe_nvls(x) : dev::dispatch_pipe(x);
         default: return dev::kNoKernel;
       }
@@ -54,14 +53,6 @@ cudaError_t launch_collective(const LaunchSpec& spec, const KParams& p, cudaStre
   if (spec.nblocks < 1 || spec.nblocks > max_blocks || spec.nthreads < 32 || spec.nthreads > 512)
     return cudaErrorInvalidConfiguration;
   dev::LaunchCtx x{&spec, &p, nullptr, 1, stream, nullptr};
-  return route(x);
-}
-
-cudaError_t launch_nvls_split(const LaunchSpec& spec, const KParamsSplit& p, cudaStream_t stream) {
-  if (spec.algo != Algo::Nvls || spec.mode != Mode::AllReduce || p.nb_first < 1 || p.nb_first >= spec.nblocks ||
-      spec.nblocks > kMaxBlocks || spec.nthreads < 32 || spec.nthreads > 512)
-    return cudaErrorInvalidConfiguration;
-  dev::LaunchCtx x{&spec, nullptr, nullptr, 1, stream, nullptr, &p};
   return route(x);
 }
 

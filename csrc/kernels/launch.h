@@ -37,10 +37,6 @@ bool kernel_exists(const LaunchSpec& spec);
 // Launch on one rank (the normal case).  `p` is passed by value to the kernel.
 cudaError_t launch_collective(const LaunchSpec& spec, const KParams& p, cudaStream_t stream);
 
-// NVLS AllReduce of a large message with a slice of it travelling peer-to-peer in the same launch:
-// blocks [0, p.nb_first) of spec.nblocks take p.args through the switch, the others p.args2.
-cudaError_t launch_nvls_split(const LaunchSpec& spec, const KParamsSplit& p, cudaStream_t stream);
-
 // Single-GPU emulation of `vranks` ranks: ONE cooperative launch whose grid is
 // vranks * spec.nblocks blocks; block g acts as block g % nblocks of rank
 // g / nblocks and reads its parameters from table[g / nblocks] (device

@@ -118,7 +118,7 @@ MNCCL_EXPORT int mnccl_test_tuning_text(const char* text, int nranks, char* out,
     std::ostringstream o;
     o << "{\"applied\":" << applied << ",\"ll_max_bytes\":" << c.ll_max_bytes << ",\"oneshot_max_bytes\":" << c.oneshot_max_bytes
       << ",\"nvls_min_bytes\":" << c.nvls_min_bytes << ",\"pipe_min_bytes\":" << c.pipe_min_bytes << ",\"pipe_chunk_bytes\":"
-      << c.pipe_chunk_bytes << ",\"nvls_p2p_permille\":" << c.nvls_p2p_permille << ",\"max_blocks\":" << c.max_blocks
+      << c.pipe_chunk_bytes << ",\"max_blocks\":" << c.max_blocks
       << ",\"errors\":\"" << errors << "\"}";
     copy_out(o.str(), out, len);
     return 0;

@@ -166,8 +166,7 @@ ncclResult_t mncclCommSetTuning(ncclComm_t comm, int max_blocks, int unroll);
 
 /* One launch-tuning knob by the name of its environment variable without the MINI_NCCL_ prefix
  * ("LL_MAX_BYTES", "ONESHOT_MAX_BYTES", "NVLS_MIN_BYTES", "PIPE_MIN_BYTES", "PIPE_CHUNK_BYTES",
- * "NVLS_P2P_PERMILLE", "NVLS_P2P_BLOCKS", "MAX_BLOCKS", ...), for the calls that follow.  Every rank
- * must use the same value.  The same knobs can be given per rank count in a table that
+ * "MAX_BLOCKS", ...), for the calls that follow.  Every rank must use the same value.  The same knobs can be given per rank count in a table that
  * MINI_NCCL_TUNING_FILE names (lines "<nranks> <KNOB> <value>", written by benchmarks/tune.py);
  * environment variables win over the table. */
 ncclResult_t mncclCommSetKnob(ncclComm_t comm, const char* name, long long value);

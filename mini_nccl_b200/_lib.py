@@ -107,6 +107,7 @@ def lib() -> C.CDLL:
         sig("mncclAgGemmBarWords", sz, i32, i32)
         sig("mncclGemmReduceScatterBf16", i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, P(vp), P(vp), vp, vp)
         sig("mncclAllGatherGemmBf16", i32, P(vp), vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, P(vp), P(vp), vp, i32, vp)
+        sig("mncclAllGatherGemmSwiGluBf16", i32, P(vp), vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, P(vp), P(vp), vp, i32, vp)
     # emulation + probes
     sig("mncclEmuCreate", i32, i32, sz, P(vp))
     sig("mncclEmuDestroy", i32, vp)

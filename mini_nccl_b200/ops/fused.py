@@ -106,19 +106,46 @@ class AllGatherGemm:
         r, per = self.comm.rank, self.M // self.comm.size
         return self.gather[r * per:(r + 1) * per]
 
-    def __call__(self, b, out=None, stream=None):
-        """``b [N_r, K]`` bf16 -> ``out [M, N_r]`` bf16 = (all ranks' shards stacked) @ b.T."""
+    def __call__(self, b, out=None, stream=None, swiglu: bool = False):
+        """``b [N_r, K]`` bf16 -> ``out [M, N_r]`` bf16 = (all ranks' shards stacked) @ b.T.
+
+        ``swiglu=True``: the epilogue applies SwiGLU and ``out`` is ``[M, N_r / 2]``; the rows of ``b`` must then
+        be interleaved in groups of 16 (:func:`interleave_gate_up`), N_r a multiple of 32."""
         import torch
 
         if b.dtype != torch.bfloat16 or b.shape[1] != self.K or b.stride(1) != 1:
             raise TypeError("b must be bf16 [N, K] with a unit inner stride")
         N = b.shape[0]
+        if swiglu and N % 32:
+            raise ValueError("SwiGLU in the epilogue needs N a multiple of 32")
+        n_out = N // 2 if swiglu else N
         if out is None:
-            out = torch.empty((self.M, N), dtype=torch.bfloat16, device=b.device)
+            out = torch.empty((self.M, n_out), dtype=torch.bfloat16, device=b.device)
+        if tuple(out.shape) != (self.M, n_out) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+            raise ValueError(f"out must be bf16 [{self.M}, {n_out}] with a unit inner stride")
         s = stream.cuda_stream if stream is not None else torch.cuda.current_stream().cuda_stream
-        rc = _native().mncclAllGatherGemmBf16(self._xg, b.data_ptr(), out.data_ptr(), self.M, N, self.K, self.K, b.stride(0),
-                                              out.stride(0), self.comm.rank, self.comm.size, self._ready, self._bar,
-                                              self.state.data_ptr(), self.n_comm, s)
+        fn = _native().mncclAllGatherGemmSwiGluBf16 if swiglu else _native().mncclAllGatherGemmBf16
+        rc = fn(self._xg, b.data_ptr(), out.data_ptr(), self.M, N, self.K, self.K, b.stride(0), out.stride(0), self.comm.rank,
+                self.comm.size, self._ready, self._bar, self.state.data_ptr(), self.n_comm, s)
         if rc != 0:
-            raise RuntimeError(f"mncclAllGatherGemmBf16 failed with code {rc}")
+            raise RuntimeError(f"all-gather->GEMM kernel failed with code {rc}")
         return out
+
+
+def interleave_gate_up(w_gate, w_up):
+    """Weight layout for SwiGLU in the all-gather->GEMM epilogue: ``[2F, K]`` whose rows alternate between 16 gate
+    features and the 16 up features of the same indices, so that one 32-column piece of an accumulator row holds
+    both operands of 16 outputs.  ``F`` must be a multiple of 16."""
+    import torch
+
+    F, K = w_gate.shape
+    if tuple(w_up.shape) != (F, K) or F % 16:
+        raise ValueError("gate and up must both be [F, K] with F a multiple of 16")
+    return torch.stack((w_gate.reshape(F // 16, 16, K), w_up.reshape(F // 16, 16, K)), dim=1).reshape(2 * F, K).contiguous()
+
+
+def split_gate_up(h):
+    """Inverse view for a product with interleaved weights: ``h [M, 2F]`` -> ``(gate [M, F], up [M, F])``."""
+    M, N = h.shape
+    v = h.reshape(M, N // 32, 2, 16)
+    return v[:, :, 0, :].reshape(M, N // 2), v[:, :, 1, :].reshape(M, N // 2)

@@ -2,7 +2,7 @@
 fused kernels.  Activations between blocks are sharded by tokens (M / ranks rows per rank); weights
 are sharded along the hidden FFN dimension.
 
-  MLP:   X_r [M/R, H]  --all-gather->GEMM-->  [M, 2F/R] (gate | up)  --SwiGLU-->  [M, F/R]
+  MLP:   X_r [M/R, H]  --all-gather->GEMM with SwiGLU in its epilogue-->  act [M, F/R]
                        --GEMM->reduce-scatter-->  Y_r [M/R, H]
   attention output projection:  A [M, H/R]  --GEMM->reduce-scatter-->  Y_r [M/R, H]
 
@@ -16,7 +16,7 @@ import torch
 import torch.nn.functional as F
 
 from ..ops.elementwise import swiglu_bf16
-from ..ops.fused import AllGatherGemm, GemmReduceScatter
+from ..ops.fused import AllGatherGemm, GemmReduceScatter, interleave_gate_up, split_gate_up
 
 
 class TensorParallelMLP:
@@ -27,16 +27,22 @@ class TensorParallelMLP:
         self.comm, self.tokens, self.hidden, self.ffn_local = comm, tokens, hidden, ffn // R
         g = torch.Generator(device="cuda").manual_seed(seed * 1000 + comm.rank)
         std = 0.02
-        # nn.Linear layout [out_features, in_features]; gate and up stacked along out_features
-        self.w_gate_up = (torch.randn(2 * self.ffn_local, hidden, generator=g, device="cuda") * std).to(torch.bfloat16)
+        # nn.Linear layout [out_features, in_features].  Gate and up are stored as ONE matrix whose rows are
+        # interleaved in groups of 16, the layout the SwiGLU epilogue of the all-gather->GEMM kernel consumes.
+        w_gate = (torch.randn(self.ffn_local, hidden, generator=g, device="cuda") * std).to(torch.bfloat16)
+        w_up = (torch.randn(self.ffn_local, hidden, generator=g, device="cuda") * std).to(torch.bfloat16)
+        if self.ffn_local % 16:
+            raise ValueError("ffn / ranks must be a multiple of 16")
+        self.w_gate_up = interleave_gate_up(w_gate, w_up)
+        self.w_gate_up_plain = torch.cat((w_gate, w_up))  # (gate | up) stacked: what the library-only baseline multiplies by
         self.w_down = (torch.randn(hidden, self.ffn_local, generator=g, device="cuda") * std).to(torch.bfloat16)
         self.ag_gemm = AllGatherGemm(comm, tokens, hidden, n_comm_ctas=n_comm_ctas)
         self.gemm_rs = GemmReduceScatter(comm, tokens, hidden)
-        self._h = torch.empty(tokens, 2 * self.ffn_local, dtype=torch.bfloat16, device="cuda")
         self._act = torch.empty(tokens, self.ffn_local, dtype=torch.bfloat16, device="cuda")
-        # SwiGLU between the two fused kernels: the library's one-pass kernel (MINI_NCCL_TP_FUSED_SWIGLU=1)
-        # or the framework's silu and mul (default)
-        self.fused_swiglu = os.environ.get("MINI_NCCL_TP_FUSED_SWIGLU", "0") == "1" and self.ffn_local % 8 == 0
+        # MINI_NCCL_TP_SWIGLU=separate keeps the H = (gate | up) matrix and runs the library's one-pass SwiGLU
+        # kernel between the two fused kernels (for measuring what the epilogue fusion saves).
+        self.swiglu_in_epilogue = os.environ.get("MINI_NCCL_TP_SWIGLU", "epilogue") != "separate"
+        self._h = None if self.swiglu_in_epilogue else torch.empty(tokens, 2 * self.ffn_local, dtype=torch.bfloat16, device="cuda")
 
     @property
     def input_shard(self):
@@ -44,12 +50,12 @@ class TensorParallelMLP:
         return self.ag_gemm.local_shard
 
     def forward(self, out=None):
-        h = self.ag_gemm(self.w_gate_up, out=self._h)
-        if self.fused_swiglu:
-            swiglu_bf16(h, out=self._act)  # one pass, one rounding
+        if self.swiglu_in_epilogue:
+            self.ag_gemm(self.w_gate_up, out=self._act, swiglu=True)
         else:
-            gate, up = h[:, :self.ffn_local], h[:, self.ffn_local:]
-            torch.mul(F.silu(gate), up, out=self._act)
+            h = self.ag_gemm(self.w_gate_up, out=self._h)
+            gate, up = split_gate_up(h)  # views; the one-pass kernel wants (gate | up) halves
+            swiglu_bf16(torch.cat((gate, up), dim=1), out=self._act)
         return self.gemm_rs(self._act, self.w_down, out=out)
 
     def forward_unfused(self, x_shard, group=None):
@@ -62,7 +68,7 @@ class TensorParallelMLP:
             dist.all_gather_into_tensor(full, x_shard, group=group)
         else:
             full = x_shard
-        h = full @ self.w_gate_up.t()
+        h = full @ self.w_gate_up_plain.t()
         act = F.silu(h[:, :self.ffn_local]) * h[:, self.ffn_local:]
         y = act @ self.w_down.t()
         if R == 1:

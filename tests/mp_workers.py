@@ -427,7 +427,7 @@ def gpu_tp(rank, n, kw):
         torch.cuda.synchronize()
         assert gemm_status() == 0, "a bounded wait ran out in GEMM->reduce-scatter"
         err = (out.float() - ref).abs().max().item() / ref.abs().max().item()
-        assert err < 3e-2, f"gemm_rs it {it}: rel err {err}"
+        assert err < 1e-2, f"gemm_rs it {it}: rel err {err}"
         worst = max(worst, err)
         # all-gather -> GEMM: stack of every rank's x times my b
         xs = torch.cat([operands(r)[2] for r in range(n)])
@@ -438,11 +438,16 @@ def gpu_tp(rank, n, kw):
         assert gemm_status() == 0, "a bounded wait ran out in all-gather->GEMM"
         assert torch.equal(ag.gather, xs), f"ag_gemm it {it}: gathered rows differ"
         err2 = (c.float() - ref2).abs().max().item() / ref2.abs().max().item()
-        assert err2 < 2e-2, f"ag_gemm it {it}: rel err {err2}"
+        assert err2 < 1e-2, f"ag_gemm it {it}: rel err {err2}"
         worst = max(worst, err2)
+    # bit for bit against the host restatement on integer-valued operands (rank order, roundings)
+    from mini_nccl_b200.utils import verify
+
+    res = verify.check_fused_gemm(comm, n, rank, M=M, N=N, K=K)
+    assert res["failed"] == 0, res["failures"]
     comm.barrier()
     comm.destroy()
-    return {"rank": rank, "worst": worst}
+    return {"rank": rank, "worst": worst, "oracle_cases": res["cases"]}
 
 
 FUNCS = {f.__name__: f for f in (cpu_ring, cpu_ring_fault, gpu_battery, gpu_stall, gpu_tp)}

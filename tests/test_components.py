@@ -141,7 +141,6 @@ def test_tuning_table_loader(lib):
 8 ONESHOT_MAX_BYTES 262144   # crossover to the two-phase kernels
 4 ONESHOT_MAX_BYTES 1048576
 0 PIPE_MIN_BYTES 16777216
-8 MINI_NCCL_NVLS_P2P_PERMILLE 150
 
 8 NO_SUCH_KNOB 1
 8 MAX_BLOCKS 100000
@@ -150,9 +149,9 @@ garbage here
     buf = C.create_string_buffer(2048)
     assert lib.mnccl_test_tuning_text(text.encode(), 8, buf, len(buf)) == 0
     got = json.loads(buf.value.decode())
-    assert got["applied"] == 4 and got["ll_max_bytes"] == 32768 and got["oneshot_max_bytes"] == 262144
-    assert got["pipe_min_bytes"] == 16777216 and got["nvls_p2p_permille"] == 150 and got["max_blocks"] == 0
-    assert "NO_SUCH_KNOB" in got["errors"] and "MAX_BLOCKS" in got["errors"] and "line 10" in got["errors"]
+    assert got["applied"] == 3 and got["ll_max_bytes"] == 32768 and got["oneshot_max_bytes"] == 262144
+    assert got["pipe_min_bytes"] == 16777216 and got["max_blocks"] == 0
+    assert "NO_SUCH_KNOB" in got["errors"] and "MAX_BLOCKS" in got["errors"] and "line 9" in got["errors"]
     assert lib.mnccl_test_tuning_text(text.encode(), 4, buf, len(buf)) == 0
     got = json.loads(buf.value.decode())
     assert got["applied"] == 2 and got["oneshot_max_bytes"] == 1048576 and got["ll_max_bytes"] == 0
