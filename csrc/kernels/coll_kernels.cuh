@@ -463,28 +463,33 @@ __device__ __forceinline__ void pipe_publish(const CommDev& c, int role, int slo
   }
 }
 
-// Worker threads only (wt = index among them, nwork of them, a multiple of 32): worker wt < nranks
-// waits for flags[slot][wt] >= target, then all workers meet on named barrier 1.
+// Worker warps wait on their own: lane t < nranks of EVERY worker warp polls flags[slot][t] >= target,
+// then the warp goes on.  No barrier between the warps of a block: at a chunk boundary only the warp
+// that crosses it has nothing in flight, the others keep the links and the memory system busy.
+// False after a failed wait (of this warp or, seen through ctl.fail, of another one).
 __device__ __forceinline__ bool pipe_wait_all(const CommDev& c, BlockCtl& ctl, size_t flag_off, int slot, uint32_t target,
-                                              int blk, int wt, int nwork) {
-  if (wt < c.nranks) {
-    const uint32_t* f = reinterpret_cast<const uint32_t*>(c.ctrl[c.rank] + c.off_pipe + flag_off) + slot * kMaxRanks + wt;
+                                              int blk) {
+  const int lane = threadIdx.x & 31;
+  if (lane < c.nranks) {
+    const uint32_t* f = reinterpret_cast<const uint32_t*>(c.ctrl[c.rank] + c.off_pipe + flag_off) + slot * kMaxRanks + lane;
     const uint32_t r = wait_ge(f, target, c);
     if (r != kDevOk) {
       ctl.fail = r;
-      record_failure(c, r, (static_cast<uint32_t>(blk) << 16) | static_cast<uint32_t>(wt));
+      record_failure(c, r, (static_cast<uint32_t>(blk) << 16) | static_cast<uint32_t>(lane));
     }
   }
-  asm volatile("bar.sync 1, %0;" ::"r"(nwork) : "memory");
+  __syncwarp();
   return ctl.fail == 0;
 }
 
 // A worker warp has issued all its loads and stores of the current chunk.
-__device__ __forceinline__ void pipe_warp_done(BlockCtl& ctl) {
+// Counted per ring slot: the warps of a block run up to kPipeSlots - 1 chunks apart (never more: a
+// warp enters chunk g + kPipeSlots only after chunk g was published, which needs every warp's count).
+__device__ __forceinline__ void pipe_warp_done(BlockCtl& ctl, int slot) {
   __syncwarp();
   if ((threadIdx.x & 31) == 0) {
     __threadfence_block();
-    atomicAdd(const_cast<uint32_t*>(&ctl.pipe_done), 1u);
+    atomicAdd(const_cast<uint32_t*>(&ctl.pipe_done[slot]), 1u);
   }
 }
 
@@ -531,11 +536,12 @@ __device__ __forceinline__ void pipe_body(const KParams& P, int blk, int nblk, B
         const int role_blocks = role == 0 ? n_in : (role == 1 ? n_red : n_out);
         const size_t flag_off = role == 0 ? kOffIn : (role == 1 ? kOffRed : kOffOut);
         for (uint32_t ch = 0; ch < nchunks; ++ch) {
-          const uint32_t want = (ch + 1) * warps;
+          const uint32_t g = base + ch;
+          const int slot = static_cast<int>(g % kPipeSlots);
           bool ok = true;
-          if (ctl.pipe_done < want) {
+          if (ctl.pipe_done[slot] < warps) {
             const uint64_t t0 = globaltimer_ns();
-            for (uint32_t it = 1; ctl.pipe_done < want; ++it) {
+            for (uint32_t it = 1; ctl.pipe_done[slot] < warps; ++it) {
               if (ctl.fail != 0) { ok = false; break; }
               if ((it & 1023u) == 0u && globaltimer_ns() - t0 > c.spin_timeout_ns) {
                 ctl.fail = kDevTimeout;
@@ -546,8 +552,8 @@ __device__ __forceinline__ void pipe_body(const KParams& P, int blk, int nblk, B
             }
           }
           if (!ok) break;
-          const uint32_t g = base + ch;
-          pipe_publish(c, role, static_cast<int>(g % kPipeSlots), role_blocks, flag_off, g + 1);
+          ctl.pipe_done[slot] = 0;  // nobody counts into this slot again before the chunk is published
+          pipe_publish(c, role, slot, role_blocks, flag_off, g + 1);
         }
       }
     } else if (role == 0) {
@@ -557,7 +563,7 @@ __device__ __forceinline__ void pipe_body(const KParams& P, int blk, int nblk, B
         const uint32_t g = base + ch;
         const int slot = static_cast<int>(g % kPipeSlots);
         if (g >= static_cast<uint32_t>(kPipeSlots) &&
-            !pipe_wait_all(c, ctl, kOffRed, slot, g - kPipeSlots + 1, blk, wt, nwork)) break;
+            !pipe_wait_all(c, ctl, kOffRed, slot, g - kPipeSlots + 1, blk)) break;
         const uint64_t e_begin = uint64_t(ch) * CE;
         const uint64_t e_end = (e_begin + CE < a.count) ? e_begin + CE : a.count;
         const uint64_t nvec = (e_end - e_begin + VW - 1) / VW;
@@ -588,7 +594,7 @@ __device__ __forceinline__ void pipe_body(const KParams& P, int blk, int nblk, B
             *reinterpret_cast<uint4*>(dst + v * 16) = pk.vec.q[0];
           }
         }
-        pipe_warp_done(ctl);
+        pipe_warp_done(ctl, slot);
       }
     } else if (role == 1) {
       // ---------------------------------------------------------------- reduce my shard
@@ -596,9 +602,9 @@ __device__ __forceinline__ void pipe_body(const KParams& P, int blk, int nblk, B
       for (uint32_t ch = 0; ch < nchunks; ++ch) {
         const uint32_t g = base + ch;
         const int slot = static_cast<int>(g % kPipeSlots);
-        if (!pipe_wait_all(c, ctl, kOffIn, slot, g + 1, blk, wt, nwork)) break;
+        if (!pipe_wait_all(c, ctl, kOffIn, slot, g + 1, blk)) break;
         if (g >= static_cast<uint32_t>(kPipeSlots) &&
-            !pipe_wait_all(c, ctl, kOffOut, slot, g - kPipeSlots + 1, blk, wt, nwork)) break;
+            !pipe_wait_all(c, ctl, kOffOut, slot, g - kPipeSlots + 1, blk)) break;
         const uint64_t e_begin = uint64_t(ch) * CE + uint64_t(me) * E;  // my shard of this chunk
         uint64_t e_end = e_begin + E;
         if (e_end > a.count) e_end = a.count;
@@ -665,7 +671,7 @@ __device__ __forceinline__ void pipe_body(const KParams& P, int blk, int nblk, B
             }
           }
         }
-        pipe_warp_done(ctl);
+        pipe_warp_done(ctl, slot);
       }
     } else {
       // ---------------------------------------------------------------- copy-out
@@ -674,7 +680,7 @@ __device__ __forceinline__ void pipe_body(const KParams& P, int blk, int nblk, B
       for (uint32_t ch = 0; ch < nchunks; ++ch) {
         const uint32_t g = base + ch;
         const int slot = static_cast<int>(g % kPipeSlots);
-        if (!pipe_wait_all(c, ctl, kOffRed, slot, g + 1, blk, wt, nwork)) break;
+        if (!pipe_wait_all(c, ctl, kOffRed, slot, g + 1, blk)) break;
         const uint64_t e_begin = uint64_t(ch) * CE;
         const uint64_t e_end = (e_begin + CE < a.count) ? e_begin + CE : a.count;
         const uint64_t nvec = (e_end - e_begin + VW - 1) / VW;
@@ -704,7 +710,7 @@ __device__ __forceinline__ void pipe_body(const KParams& P, int blk, int nblk, B
             store_vec<OutT, VW>(a.recv, e_begin + v * VW, e_end, out_al, y);
           }
         }
-        pipe_warp_done(ctl);
+        pipe_warp_done(ctl, slot);
       }
     }
     // the last block to leave moves the base past this call's chunks

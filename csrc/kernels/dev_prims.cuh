@@ -61,7 +61,7 @@ struct BlockCtl {        // one per thread block, in shared memory
   uint32_t epoch;        // this block's barrier epoch (cached from LocalState)
   uint32_t ll_seq;
   volatile uint32_t fail;  // DevStatus of the first failed wait in this block
-  volatile uint32_t pipe_done;  // pipelined kernel: worker warps that have finished a chunk, over all chunks
+  volatile uint32_t pipe_done[kPipeSlots];  // pipelined kernel: worker warps that have finished the chunk in a ring slot
 };
 
 __device__ __forceinline__ LocalState* local_state(const CommDev& c) {
@@ -104,7 +104,7 @@ __device__ __forceinline__ void block_begin(const CommDev& c, int blk, BlockCtl&
     ctl.epoch = ls->epoch[blk];
     ctl.ll_seq = ls->ll_seq[blk];
     ctl.fail = 0;
-    ctl.pipe_done = 0;
+    for (int i = 0; i < kPipeSlots; ++i) ctl.pipe_done[i] = 0;
     if (blk == 0) {
       uint32_t s = ls->started + 1;
       ls->started = s;

@@ -1,6 +1,7 @@
 // C entry points that expose internal components to the Python test-suite
 // (ctypes).  They are thin: each one drives a component the way its users do
-// and reports what happened.  Nothing here is on a hot path.
+// and reports what happened.  Built into libmini_nccl_testhooks.so only: the
+// product library exports the API and the host oracle, nothing of this file.
 #include <atomic>
 #include <chrono>
 #include <cstdio>
@@ -54,28 +55,6 @@ void copy_out(const std::string& s, char* out, size_t len) {
 
 extern "C" {
 #define MNCCL_EXPORT __attribute__((visibility("default")))
-
-// ---- oracle ---------------------------------------------------------------
-MNCCL_EXPORT int mnccl_oracle_allreduce(int in_t, int wire_t, int out_t, int op, int nranks, const void* const* inputs,
-                                        void* out, size_t count, double scale) {
-  return guarded([&] {
-    oracle_allreduce(static_cast<DType>(in_t), static_cast<DType>(wire_t), static_cast<DType>(out_t),
-                     static_cast<RedOp>(op), nranks, inputs, out, count, scale);
-    return 0;
-  });
-}
-MNCCL_EXPORT int mnccl_verify_f32(const float* got, const float* want, size_t n, float atol, size_t* first_bad) {
-  return verify_f32_avx2(got, want, n, atol, first_bad) ? 0 : 1;
-}
-MNCCL_EXPORT int mnccl_verify_const_f32(const float* got, float want, size_t n, float atol, size_t* first_bad) {
-  return verify_const_f32_avx2(got, want, n, atol, first_bad) ? 0 : 1;
-}
-MNCCL_EXPORT void mnccl_sum_f32(const float* a, const float* b, float* out, size_t n) { sum_f32_avx2(a, b, out, n); }
-MNCCL_EXPORT int mnccl_cpu_has_avx2() { return cpu_has_avx2() ? 1 : 0; }
-MNCCL_EXPORT uint16_t mnccl_float_to_bf16(float f) { return float_to_bf16(f); }
-MNCCL_EXPORT uint16_t mnccl_float_to_half(float f) { return float_to_half(f); }
-MNCCL_EXPORT float mnccl_bf16_to_float(uint16_t h) { return bf16_to_float(h); }
-MNCCL_EXPORT float mnccl_half_to_float(uint16_t h) { return half_to_float(h); }
 
 // ---- config ---------------------------------------------------------------
 // env: "NAME=value;NAME=value".  out: JSON of the parsed knobs.

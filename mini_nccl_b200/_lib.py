@@ -119,7 +119,7 @@ def lib() -> C.CDLL:
     sig("mncclEmuStatus", i32, vp, P(u32), P(u32))
     sig("mncclEmuLastPlan", i32, vp, P(i32), P(i32))
     sig("mncclProbeBoundedWait", i32, u64, i32, P(u32), P(u32))
-    # test hooks
+    # host oracle (csrc/ref/oracle_api.cc)
     sig("mnccl_oracle_allreduce", i32, i32, i32, i32, i32, i32, P(vp), vp, sz, dbl)
     sig("mnccl_verify_f32", i32, vp, vp, sz, C.c_float, P(sz))
     sig("mnccl_verify_const_f32", i32, vp, C.c_float, sz, C.c_float, P(sz))
@@ -129,30 +129,45 @@ def lib() -> C.CDLL:
     sig("mnccl_float_to_half", C.c_uint16, C.c_float)
     sig("mnccl_bf16_to_float", C.c_float, C.c_uint16)
     sig("mnccl_half_to_float", C.c_float, C.c_uint16)
-    sig("mnccl_test_config", i32, C.c_char_p, C.c_char_p, sz)
-    sig("mnccl_test_tuning_text", i32, C.c_char_p, i32, C.c_char_p, sz)
-    sig("mnccl_test_spsc", i32, i32, i32)
-    sig("mnccl_test_request_pool", i32, i32)
-    sig("mnccl_test_reg_cache", i32)
-    sig("mnccl_test_select_nic", i32, C.c_char_p, C.c_char_p, P(i32))
-    sig("mnccl_test_parse_cpu_list", i32, C.c_char_p, P(i32), i32)
-    sig("mnccl_test_numa", i32, C.c_char_p, C.c_char_p, P(i32), P(i32))
-    sig("mnccl_test_plan", i32, i32, i32, u64, i32, i32, i32, i32, i32, i32, i32, i32, u64, P(i32), P(i32), P(u64), P(u64), P(i32), P(i32))
-    sig("mnccl_test_watchdog", i32, i32, i32)
-    sig("mnccl_test_fdpass", i32, C.c_char_p)
-    sig("mnccl_hera_master_start", vp, i32, i32, i32)
-    sig("mnccl_hera_master_port", i32, vp)
-    sig("mnccl_hera_master_registered", i32, vp)
-    sig("mnccl_hera_master_abort_sent", i32, vp)
-    sig("mnccl_hera_master_worker", i32, vp, i32, P(i32), P(i32), C.c_char_p, C.c_char_p, P(i32))
-    sig("mnccl_hera_master_stop", None, vp)
-    sig("mnccl_hera_worker_register", vp, C.c_char_p, i32, P(i32), P(i32), C.c_char_p)
-    sig("mnccl_hera_worker_topology", i32, vp, P(i32), P(i32), C.c_char_p)
-    sig("mnccl_hera_worker_start_agent", i32, vp, i32, i32)
-    sig("mnccl_hera_worker_abort_seen", i32, i32)
-    sig("mnccl_hera_worker_send_abort", i32, vp, C.c_uint)
-    sig("mnccl_hera_worker_set_state", None, vp, C.c_uint)
-    sig("mnccl_hera_worker_free", None, vp)
+    # Entry points for the test-suite live in a library of their own (libmini_nccl_testhooks.so, the same
+    # objects plus csrc/testing/hooks.cc); when it is present they are attached to this handle under
+    # their names, so tests call them like any other function.  The product library exports none of them.
+    hooks_path = path.parent / "libmini_nccl_testhooks.so"
+    if hooks_path.exists():
+        H = C.CDLL(str(hooks_path), mode=C.RTLD_LOCAL)
+
+        def hsig(name, res, *args):
+            f = getattr(H, name)
+            f.restype = res
+            f.argtypes = list(args)
+            setattr(L, name, f)
+
+        hsig("mnccl_test_config", i32, C.c_char_p, C.c_char_p, sz)
+        hsig("mnccl_test_tuning_text", i32, C.c_char_p, i32, C.c_char_p, sz)
+        hsig("mnccl_test_pipeline_chunks", i32, sz, sz, sz, sz, i32, P(sz), i32)
+        hsig("mnccl_test_soft_reject", i32, i32, i32)
+        hsig("mnccl_test_spsc", i32, i32, i32)
+        hsig("mnccl_test_request_pool", i32, i32)
+        hsig("mnccl_test_reg_cache", i32)
+        hsig("mnccl_test_select_nic", i32, C.c_char_p, C.c_char_p, P(i32))
+        hsig("mnccl_test_parse_cpu_list", i32, C.c_char_p, P(i32), i32)
+        hsig("mnccl_test_numa", i32, C.c_char_p, C.c_char_p, P(i32), P(i32))
+        hsig("mnccl_test_plan", i32, i32, i32, u64, i32, i32, i32, i32, i32, i32, i32, i32, u64, P(i32), P(i32), P(u64), P(u64), P(i32), P(i32))
+        hsig("mnccl_test_watchdog", i32, i32, i32)
+        hsig("mnccl_test_fdpass", i32, C.c_char_p)
+        hsig("mnccl_hera_master_start", vp, i32, i32, i32)
+        hsig("mnccl_hera_master_port", i32, vp)
+        hsig("mnccl_hera_master_registered", i32, vp)
+        hsig("mnccl_hera_master_abort_sent", i32, vp)
+        hsig("mnccl_hera_master_worker", i32, vp, i32, P(i32), P(i32), C.c_char_p, C.c_char_p, P(i32))
+        hsig("mnccl_hera_master_stop", None, vp)
+        hsig("mnccl_hera_worker_register", vp, C.c_char_p, i32, P(i32), P(i32), C.c_char_p)
+        hsig("mnccl_hera_worker_topology", i32, vp, P(i32), P(i32), C.c_char_p)
+        hsig("mnccl_hera_worker_start_agent", i32, vp, i32, i32)
+        hsig("mnccl_hera_worker_abort_seen", i32, i32)
+        hsig("mnccl_hera_worker_send_abort", i32, vp, C.c_uint)
+        hsig("mnccl_hera_worker_set_state", None, vp, C.c_uint)
+        hsig("mnccl_hera_worker_free", None, vp)
     _LIB = L
     return L
 

@@ -38,9 +38,12 @@ HOST_SOURCES = [
     "bootstrap/socket.cc", "bootstrap/store.cc", "bootstrap/fdpass.cc", "bootstrap/hera.cc",
     "net/soft_transport.cc", "net/nic_select.cc", "net/ring.cc", "net/factory.cc",
     "mem/cuda_driver.cc", "mem/symmetric.cc",
-    "algo/select.cc", "watchdog/watchdog.cc", "ref/oracle.cc",
-    "comm.cc", "api.cc", "testing/hooks.cc",
+    "algo/select.cc", "watchdog/watchdog.cc", "ref/oracle.cc", "ref/oracle_api.cc",
+    "comm.cc", "api.cc",
 ]
+# Entry points for the test-suite only: linked, with all of the above, into a library of their own
+# (libmini_nccl_testhooks.so), so that the product library exports the API and nothing else.
+TESTHOOK_SOURCES = ["testing/hooks.cc"]
 CUDA_SOURCES = [
     "kernels/k_small.cu", "kernels/k_twoshot.cu", "kernels/k_rsag.cu", "kernels/k_nvls.cu", "kernels/k_pipe.cu",
     "kernels/launch.cu", "emu/emu_world.cu",
@@ -143,6 +146,16 @@ def build(verbose: bool = False, programs: bool = True, jobs: int | None = None)
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed\n{r.stdout}\n{r.stderr}")
+    hooks = LIBDIR / "libmini_nccl_testhooks.so"
+    hook_objs = [_compile(CSRC / h, hdr, verbose, extra) for h in TESTHOOK_SOURCES if (CSRC / h).exists()]
+    if hook_objs and (not hooks.exists() or hooks.stat().st_mtime < max(newest_obj, max(o.stat().st_mtime for o in hook_objs))):
+        cmd = [NVCC, "-shared", *ARCH, "-cudart", "static", "-Xlinker", "-Bsymbolic-functions",
+               "-o", str(hooks), *map(str, objs), *map(str, hook_objs), "-lpthread", "-lrt", "-ldl"]
+        if "-DMNCCL_HAVE_VERBS=1" in extra:
+            cmd.append("-libverbs")
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link of the test hooks failed\n{r.stdout}\n{r.stderr}")
     if programs:
         for name, (sources, needs_cuda) in PROGRAMS.items():
             paths = [ROOT / s for s in sources]
@@ -199,7 +212,8 @@ def build_fake_verbs_variant(verbose: bool = False) -> Path:
 
 SELFTEST_SOURCES = ["core/log.cc", "core/config.cc", "bootstrap/socket.cc", "bootstrap/store.cc", "bootstrap/fdpass.cc",
                     "bootstrap/hera.cc", "net/soft_transport.cc", "net/nic_select.cc", "net/ring.cc", "net/factory.cc",
-                    "algo/select.cc", "watchdog/watchdog.cc", "ref/oracle.cc", "testing/hooks.cc", "testing/selftest_main.cc"]
+                    "algo/select.cc", "watchdog/watchdog.cc", "ref/oracle.cc", "ref/oracle_api.cc", "testing/hooks.cc",
+                    "testing/selftest_main.cc"]
 
 
 def build_sanitized_selftest(kind: str = "address") -> Path:

@@ -9,11 +9,19 @@ is fused with the 1/world scale and, optionally, with a cast to an fp32
 main-gradient buffer (bf16 on the wire, fp32 accumulation, fp32 result), all in
 the one communication kernel.
 
+A stock training loop may rebind ``param.grad`` (``optimizer.zero_grad()`` sets it to ``None`` by
+default, after which autograd allocates a fresh tensor): the gradient hook notices, copies such a
+gradient into its bucket slot and points ``param.grad`` back at the slot, so the bucket that is
+reduced always holds the step's gradients.  ``no_sync()`` skips the reduction for gradient
+accumulation; accumulating WITHOUT it is also correct (the already averaged part is the same on
+every rank, so averaging it again changes nothing), just one collective per micro-step.
+
 ``allreduce_comm_hook`` is the same reduction packaged for
 ``torch.nn.parallel.DistributedDataParallel.register_comm_hook``.
 """
 from __future__ import annotations
 
+import contextlib
 from typing import Optional
 
 import torch
@@ -56,7 +64,10 @@ class DistributedDataParallel(nn.Module):
         self._buckets: list[_Bucket] = []
         self._param_bucket = {}
         self._callback_queued = False
+        self._sync = True
+        self._slot = {}          # id(param) -> its view into the bucket
         self.launches = 0
+        self.repaired = 0        # gradients found outside their bucket and moved back in
         self._build_buckets(int(bucket_mb * 1024 * 1024))
         self._broadcast_parameters()
         for p in self._params():
@@ -100,6 +111,7 @@ class DistributedDataParallel(nn.Module):
                 b.main.zero_()
             for p, off in zip(params, offsets):
                 p.grad = b.flat[off:off + p.numel()].view_as(p)
+                self._slot[id(p)] = p.grad
                 if b.main is not None:
                     p.main_grad = b.main[off:off + p.numel()].view_as(p)
                 self._param_bucket[id(p)] = b
@@ -120,6 +132,19 @@ class DistributedDataParallel(nn.Module):
     # -------------------------------------------------------------- backward hooks
     def _on_grad(self, p):
         b = self._param_bucket[id(p)]
+        slot = self._slot[id(p)]
+        if p.grad is not slot and (p.grad is None or p.grad.data_ptr() != slot.data_ptr()):
+            # Someone rebound .grad (zero_grad(set_to_none=True), a manual assignment): the bucket slot holds
+            # stale data.  Move the fresh gradient in and make .grad the view again.
+            with torch.no_grad():
+                if p.grad is None:
+                    slot.zero_()
+                else:
+                    slot.copy_(p.grad)
+            p.grad = slot
+            self.repaired += 1
+        if not self._sync:
+            return
         if b.pending == 0:
             b.pending = len(b.params)
         b.pending -= 1
@@ -158,10 +183,25 @@ class DistributedDataParallel(nn.Module):
     def forward(self, *args, **kwargs):
         return self.module(*args, **kwargs)
 
+    @contextlib.contextmanager
+    def no_sync(self):
+        """Backward passes inside this context only accumulate into the buckets; the first backward after it
+        reduces the accumulated gradients (gradient accumulation with one collective per optimizer step)."""
+        old, self._sync = self._sync, False
+        try:
+            yield
+        finally:
+            self._sync = old
+
     def zero_grad(self, set_to_none: bool = False):
-        # Gradients are views into the buckets and must stay so.
+        """Zeroes the buckets and keeps every ``.grad`` a view into them, whatever ``set_to_none`` says
+        (prefer this to ``optimizer.zero_grad()``, which costs a copy per parameter in the next backward)."""
         for b in self._buckets:
             b.flat.zero_()
+        for p in self._params():
+            slot = self._slot[id(p)]
+            if p.grad is not slot:
+                p.grad = slot
 
     @property
     def buckets(self):

@@ -63,3 +63,47 @@ def test_reduction_after_backward_when_overlap_is_off():
             assert torch.equal(b.main, b.flat.float())
     finally:
         comm.destroy()
+
+
+def test_stock_optimizer_zero_grad_and_no_sync():
+    """optimizer.zero_grad() with its default set_to_none=True makes autograd allocate fresh .grad tensors:
+    the wrapper must move them back into the buckets (what gets reduced is the bucket).  Under no_sync() the
+    backward only accumulates; the next synchronised backward reduces the sum."""
+    import mini_nccl_b200 as mn
+    from mini_nccl_b200.parallel import DistributedDataParallel
+
+    cfg, model = _tiny_model()
+    comm = mn.Communicator(1, 0)
+    try:
+        ddp = DistributedDataParallel(model, comm, bucket_mb=0.25, main_grad_dtype=torch.float32)
+        opt = torch.optim.SGD(model.parameters(), lr=1e-3)
+        ids = torch.randint(0, cfg.vocab_size, (2, cfg.seq_len), device="cuda")
+        used = lambda: [p for p in model.parameters() if p.grad is not None]
+        for step in range(2):
+            opt.zero_grad()                      # default arguments: .grad becomes None
+            assert all(p.grad is None for p in model.parameters())
+            ddp(ids, ids).backward()
+            torch.cuda.synchronize()
+            assert ddp.repaired > 0
+            for b in ddp.buckets:
+                lo, hi = b.flat.data_ptr(), b.flat.data_ptr() + b.flat.numel() * b.flat.element_size()
+                assert all(p.grad is not None and lo <= p.grad.data_ptr() < hi for p in b.params), "a .grad left its bucket"
+                assert torch.equal(b.main, b.flat.float()), "the reduced bucket does not hold this step's gradients"
+            assert any(p.grad.abs().sum().item() > 0 for p in used())
+            opt.step()
+        # gradient accumulation: two micro-steps, one reduction
+        ddp.zero_grad()
+        before = ddp.launches
+        with ddp.no_sync():
+            ddp(ids, ids).backward()
+        torch.cuda.synchronize()
+        assert ddp.launches == before, "no collective under no_sync()"
+        once = [b.flat.clone() for b in ddp.buckets]
+        ddp(ids, ids).backward()
+        torch.cuda.synchronize()
+        assert ddp.launches - before == len(ddp.buckets)
+        for b, o in zip(ddp.buckets, once):
+            assert torch.allclose(b.flat.float(), 2 * o.float(), rtol=2e-2, atol=1e-3), "second micro-step did not accumulate"
+            assert torch.equal(b.main, b.flat.float())
+    finally:
+        comm.destroy()
