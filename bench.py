@@ -115,11 +115,20 @@ def main():
     # ---- headline: device-timed, K steps per repeat, max over ranks, median repeat
     # Untimed pre-warm for ~1 s: clocks and NVLink links leave their idle power states (a cold
     # start measured 15 to 25 % below the steady state), then the W warm-up steps proper.
+    # Every rank must issue the SAME number of collectives: whether to go on is decided together
+    # (each rank's own clock would let one rank run a batch more than another and leave its kernels
+    # without partners).
     t_pre = time.perf_counter()
-    while time.perf_counter() - t_pre < 1.0:
+    go_on = torch.ones(1, device="cuda")
+    while True:
         for _ in range(10):
             step()
         torch.cuda.synchronize()
+        go_on.fill_(1.0 if time.perf_counter() - t_pre < 1.0 else 0.0)
+        if world > 1:
+            dist.all_reduce(go_on, op=dist.ReduceOp.MIN)
+        if go_on.item() == 0.0:
+            break
     for _ in range(warmup):
         step()
     # Clocks are sampled DURING the timed repeats by a thread that makes two NVML reads every 50 ms.

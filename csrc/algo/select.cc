@@ -113,7 +113,13 @@ Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
     if (algo == Algo::Nvls && !(nvls_usable && in.mode == Mode::ReduceScatter)) algo = Algo::TwoShot;
   } else if (algo == Algo::Auto) {
     const bool ordinary = !(in.in_symmetric && in.out_symmetric);
-    if (ordinary && !in.host_memory && cfg.pipe_min_bytes != 0 && wire_bytes >= cfg.pipe_min_bytes) algo = Algo::Pipe;
+    // The pipelined kernel is the automatic choice where the switch reduces (more than two ranks, a type
+    // and operator it can add): measured 632 us for 256 MiB on 8 GPUs against 772 us for copy kernels on
+    // side streams and 717 us for NCCL.  Its peer-to-peer form (forced with algo = pipe) measured slower
+    // than the stream pipeline on two GPUs (800 against 605 us), so two ranks and the other operators
+    // keep that one.
+    const bool pipe_auto = caps.nvls && N > 2 && nvls_types;
+    if (ordinary && pipe_auto && !in.host_memory && cfg.pipe_min_bytes != 0 && wire_bytes >= cfg.pipe_min_bytes) algo = Algo::Pipe;
     else if (wire_bytes <= th.ll_max && wire_bytes * 2 <= caps.ll_slot_bytes) algo = Algo::LL;
     else if (wire_bytes <= th.oneshot_max && wire_bytes <= caps.inbox_slot_bytes) algo = Algo::OneShot;
     else if (nvls_usable && wire_bytes >= th.nvls_min) algo = Algo::Nvls;
@@ -143,10 +149,11 @@ Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
   }
 
   if (algo == Algo::Pipe) {
-    // Chunks of about a sixteenth of the message (1 MB at least), bounded by one ring slot of either
-    // staging area; a chunk is N shards of E elements, E a multiple of the vector width.
+    // One block per chunk and role: chunks are small (512 KB by default: measured best on 8 GPUs,
+    // 632 us for 256 MiB against 660 with 1 MB and 790 with 256 KB), bounded by one ring slot of
+    // either staging area; a chunk is N shards of E elements, E a multiple of the vector width.
     const uint64_t stride = caps.stage_bytes / kPipeSlots;
-    uint64_t target = cfg.pipe_chunk_bytes ? cfg.pipe_chunk_bytes : std::clamp<uint64_t>(wire_bytes / 16, 1u << 20, 8u << 20);
+    uint64_t target = cfg.pipe_chunk_bytes ? cfg.pipe_chunk_bytes : (512u << 10);
     uint64_t ce = std::min<uint64_t>(target / wsz, stride / std::max(wsz, osz));
     uint64_t E = ce / (uint64_t(N) * VW) * VW;
     if (E == 0) { p.reason = "staging buffer too small for the pipelined kernel"; return p; }
@@ -154,7 +161,7 @@ Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
     p.chunk_shard_vecs = E / VW;
     p.copy_in = p.copy_out = true;
     p.spec.pipe_nvls = caps.nvls && N > 2 && nvls_types;
-    int want = p.spec.pipe_nvls ? 80 : 112;
+    int want = p.spec.pipe_nvls ? 48 : 112;  // switch path: 14 + 20 + 14 blocks measured best (more only add contention)
     if (max_blocks) want = max_blocks;
     p.spec.nblocks = std::clamp(want, 3, std::max(3, caps.sm_count - 8));
     p.valid = true;

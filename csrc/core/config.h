@@ -45,7 +45,7 @@ struct Config {
   bool pipeline_copy_engine = false;  // MINI_NCCL_PIPELINE_COPY_ENGINE: the chunk pipeline moves ordinary DEVICE buffers with the copy engines too (off: copy kernels)
   size_t pipeline_min_bytes = 48u << 20;  // MINI_NCCL_PIPELINE_MIN_BYTES: ordinary buffers of at least this size go through the chunk pipeline (0 = never)
   size_t pipe_min_bytes = 24u << 20;  // MINI_NCCL_PIPE_MIN_BYTES: ordinary DEVICE buffers of at least this size take the pipelined kernel (copy-in, reduce, copy-out blocks in one launch); 0 = never (then MINI_NCCL_PIPELINE_MIN_BYTES decides on the stream pipeline)
-  size_t pipe_chunk_bytes = 0;        // MINI_NCCL_PIPE_CHUNK_BYTES: chunk of that kernel (0 = a sixteenth of the message, 1 to 8 MB)
+  size_t pipe_chunk_bytes = 0;        // MINI_NCCL_PIPE_CHUNK_BYTES: chunk of that kernel (0 = 512 KB)
   int max_blocks = 0;                 // MINI_NCCL_MAX_BLOCKS (0 = built-in)
   int unroll = 0;                     // MINI_NCCL_UNROLL (NVLS vectors in flight per thread: 4 or 8; 0 = built-in)
   bool numa_bind = true;              // MINI_NCCL_NUMA_BIND (verbs path only, calling thread)

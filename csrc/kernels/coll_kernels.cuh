@@ -407,7 +407,7 @@ __device__ __forceinline__ void twoshot_body(const KParams& P, int blk, int nblk
 
 // -------------------------------------------------------------------- pipelined (ordinary buffers)
 // AllReduce of buffers that are NOT in symmetric memory, as ONE kernel whose blocks take three
-// roles that run concurrently, chunk by chunk:
+// roles that run concurrently on different chunks of the message:
 //
 //   copy-in   user send buffer -> my stage_a slot (converted to the wire type)
 //   reduce    my shard of the chunk: sum of all ranks' stage_a slots (multimem.ld_reduce through
@@ -415,24 +415,42 @@ __device__ __forceinline__ void twoshot_body(const KParams& P, int blk, int nblk
 //             (multimem.st, or peer stores), scale and output conversion fused in
 //   copy-out  my stage_b slot -> user recv buffer
 //
-// The staging areas are rings of kPipeSlots slots, so the copies of chunk c+1.. and c-1.. overlap
-// the reduction of chunk c and the NVLink transfer never waits for a local copy (a staged two-phase
-// kernel idles the links during both copies; separate copy kernels on side streams pay a launch and
-// a cross-rank barrier per chunk).  Hand-over between roles and ranks is by monotonic chunk counters
-// (PipeCtl): the last block of a role to finish a chunk publishes "chunk g done by rank r" to every
-// rank; waits are bounded like every other wait of the library.
+// The staging areas are rings of kPipeSlots slots.  Chunks are dealt round-robin to the blocks of a
+// role: block b of a role with n blocks handles chunks b, b + n, b + 2n, ... ONE block per chunk, so
+// every block streams through its own chunks with its loads in flight all the time and the blocks
+// never meet.  (A first version let all blocks of a role share every chunk: each warp then touched
+// every chunk, a chunk cost at least one load round trip of ~9 us whatever its size, and most lanes
+// of a pass idled.)  The copies of later and earlier chunks overlap the reduction, so the NVLink
+// transfer never waits for a local copy: a staged two-phase kernel idles the links during both
+// copies, separate copy kernels on side streams pay a launch and a cross-rank barrier per chunk.
+//
+// Hand-over between roles and ranks is by monotonic chunk numbers (PipeCtl): chunk g, counted over
+// ALL pipelined calls of the communicator, lives in slot g % kPipeSlots and its flags carry g + 1,
+// so nothing is ever reset.  The block that finishes a chunk publishes "chunk g done by rank r" to
+// every rank; waits are bounded like every other wait of the library.
 //
 //   copy-in  of chunk g waits for red_done[g - K] of all ranks   (the slot's last readers)
 //   reduce   of chunk g waits for in_ready[g] of all ranks       (the data)
 //                         and for out_done[g - K] of all ranks   (stage_b slots free everywhere)
 //   copy-out of chunk g waits for red_done[g] of all ranks
 //
+// Inside a block, warp 0 publishes and warp 1 polls; the other warps work and never stall on either:
+// a worker warp that has finished its part of a chunk bumps a counter in shared memory and goes on
+// to the block's next chunk as soon as the poller has seen its inputs (at most kPipeAhead chunks
+// ahead of the publisher).
+//
 // Chunk geometry: a chunk is N shards of E = a.shard_elems elements (a multiple of the vector
 // width); rank r reduces shard r of every chunk.  Inside a slot the chunk is laid out like the
-// user buffer, so both copies are straight copies.
+// user buffer, so both copies are straight copies.  On the peer-to-peer path a rank's OWN shard
+// never touches the staging areas: the reduction reads it from the user's send buffer and writes the
+// result straight into the user's recv buffer, and both copies skip it (with two ranks that halves
+// the copy traffic).  The switch path cannot do that: multimem.ld_reduce reads the same offset of
+// every rank's staging, the reader's own included.
+constexpr int kPipeAhead = 4;  // chunks of one block whose completion may be outstanding; size of BlockCtl::pipe_done
+
 template <int NVLS>
 __device__ __forceinline__ void pipe_roles(int nblk, int& n_in, int& n_red) {
-  // switch path: the reduction needs few blocks (measured: ~32 saturate it); peer-to-peer wants more
+  // switch path: the reduction needs fewer blocks than peer-to-peer loads and stores
   const int share = NVLS ? 3 : 2;
   n_in = (nblk * share + 5) / 10;
   if (n_in < 1) n_in = 1;
@@ -440,34 +458,23 @@ __device__ __forceinline__ void pipe_roles(int nblk, int& n_in, int& n_red) {
   if (n_red < 1) n_red = 1;
 }
 
-// Hand-over without stalling the workers.  Warp 0 of every block is a control warp, the other warps
-// work.  A worker warp that has finished its part of a chunk bumps a counter in shared memory and
-// goes straight on to the next chunk; the control warp's lane 0 waits for all worker warps, makes the
-// block's writes visible (one system-scope fence: local, peer and multicast stores), takes a ticket,
-// and the last block of the role to do so publishes "chunk g done by this rank" to every rank: ONE
-// more fence, then plain system-scope stores (a release store per peer would wait for the previous
-// peer's flag to be acknowledged across NVLink every time: measured ~30 us per chunk on 8 GPUs).
-__device__ __forceinline__ void pipe_publish(const CommDev& c, int role, int slot, int role_blocks, size_t flag_off,
-                                             uint32_t value) {
-  PipeCtl* mine = reinterpret_cast<PipeCtl*>(c.ctrl[c.rank] + c.off_pipe);
+// Publisher: makes the block's writes visible (ONE system-scope fence: local, peer and multicast
+// stores), then plain system-scope stores of the chunk number into flags[slot][me] of every rank.  (A
+// release store per peer would wait for the previous peer's flag to be acknowledged across NVLink
+// every time: measured ~30 us per chunk on 8 GPUs.)
+__device__ __forceinline__ void pipe_publish(const CommDev& c, int slot, size_t flag_off, uint32_t value) {
   __threadfence_system();
-  const uint32_t t = atomicAdd(&mine->tick[role][slot], 1u);
-  if (t == static_cast<uint32_t>(role_blocks - 1)) {
-    mine->tick[role][slot] = 0;
-    __threadfence_system();  // the other blocks' writes, seen through the ticket, before the flags
-    for (int k = 0; k < c.nranks; ++k) {
-      const int p = (c.rank + k) % c.nranks;
-      uint32_t* f = reinterpret_cast<uint32_t*>(c.ctrl[p] + c.off_pipe + flag_off) + slot * kMaxRanks + c.rank;
-      st_volatile_u32(f, value);
-    }
+  for (int k = 0; k < c.nranks; ++k) {
+    const int p = (c.rank + k) % c.nranks;
+    uint32_t* f = reinterpret_cast<uint32_t*>(c.ctrl[p] + c.off_pipe + flag_off) + slot * kMaxRanks + c.rank;
+    st_volatile_u32(f, value);
   }
 }
 
-// Worker warps wait on their own: lane t < nranks of EVERY worker warp polls flags[slot][t] >= target,
-// then the warp goes on.  No barrier between the warps of a block: at a chunk boundary only the warp
-// that crosses it has nothing in flight, the others keep the links and the memory system busy.
-// False after a failed wait (of this warp or, seen through ctl.fail, of another one).
-__device__ __forceinline__ bool pipe_wait_all(const CommDev& c, BlockCtl& ctl, size_t flag_off, int slot, uint32_t target,
+// Poller: lane t < nranks waits for flags[slot][t] >= target with the bounded system-scope wait.
+// Worker warps never touch the flags (a thousand warps polling them, and the abort word in host
+// memory behind them, was measured to slow the kernel a hundredfold).
+__device__ __forceinline__ bool pipe_poll_all(const CommDev& c, BlockCtl& ctl, size_t flag_off, int slot, uint32_t target,
                                               int blk) {
   const int lane = threadIdx.x & 31;
   if (lane < c.nranks) {
@@ -482,14 +489,27 @@ __device__ __forceinline__ bool pipe_wait_all(const CommDev& c, BlockCtl& ctl, s
   return ctl.fail == 0;
 }
 
-// A worker warp has issued all its loads and stores of the current chunk.
-// Counted per ring slot: the warps of a block run up to kPipeSlots - 1 chunks apart (never more: a
-// warp enters chunk g + kPipeSlots only after chunk g was published, which needs every warp's count).
-__device__ __forceinline__ void pipe_warp_done(BlockCtl& ctl, int slot) {
+// Spin on a counter in shared memory until it exceeds `want_above` (bounded; ctl.fail ends it).
+__device__ __forceinline__ bool pipe_spin(const CommDev& c, BlockCtl& ctl, const volatile uint32_t* counter, uint32_t want_above) {
+  if (*counter <= want_above) {
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t it = 1; *counter <= want_above; ++it) {
+      if (ctl.fail != 0) return false;
+      if ((it & 4095u) == 0u && globaltimer_ns() - t0 > 2 * c.spin_timeout_ns) {  // the poller gives up first
+        ctl.fail = kDevTimeout;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// A worker warp has issued all its loads and stores of the block's i-th chunk.
+__device__ __forceinline__ void pipe_warp_done(BlockCtl& ctl, uint32_t i) {
   __syncwarp();
   if ((threadIdx.x & 31) == 0) {
     __threadfence_block();
-    atomicAdd(const_cast<uint32_t*>(&ctl.pipe_done[slot]), 1u);
+    atomicAdd(const_cast<uint32_t*>(&ctl.pipe_done[i % kPipeAhead]), 1u);
   }
 }
 
@@ -504,13 +524,13 @@ __device__ __forceinline__ void pipe_body(const KParams& P, int blk, int nblk, B
   constexpr int VW = 16 / sizeof(WRaw);
   constexpr int OUT_VB = VW * sizeof(ORaw);
   static_assert(OUT_VB % 16 == 0, "output vectors are whole 16-byte units for every supported type triple");
-  constexpr int U = 4;    // vectors in flight per thread in the reduction
-  constexpr int UC = 8;   // ... and in the two copies (bound by loads in flight, not by arithmetic)
+  constexpr int U = NVLS ? 4 : 8;  // vectors in flight per thread in the reduction (peer loads: two round trips per step)
+  constexpr int UC = (OUT_VB > 16) ? 8 : 16;  // ... and in the two copies (bound by loads in flight, not by arithmetic)
   constexpr bool kSameIn = std::is_same<InT, WireT>::value;
   block_begin(c, blk, ctl);
   const int N = c.nranks, me = c.rank;
-  const int nwork = static_cast<int>(blockDim.x) - 32;     // worker threads (warps 1..)
-  const int wt = static_cast<int>(threadIdx.x) - 32;       // index among the workers; negative in the control warp
+  const int nwork = static_cast<int>(blockDim.x) - 64;     // worker threads (warps 2..); warp 0 publishes, warp 1 polls
+  const int wt = static_cast<int>(threadIdx.x) - 64;       // index among the workers; negative in the two control warps
   if (N > 0 && a.count > 0 && nwork >= 32) {
     PipeCtl* pc = reinterpret_cast<PipeCtl*>(c.ctrl[me] + c.off_pipe);
     const uint32_t base = pc->base;  // written only by the last block of a call, after everyone read it
@@ -524,193 +544,252 @@ __device__ __forceinline__ void pipe_body(const KParams& P, int blk, int nblk, B
     pipe_roles<NVLS ? 1 : 0>(nblk, n_in, n_red);
     const int n_out = nblk - n_in - n_red;
     const int role = blk < n_in ? 0 : (blk < n_in + n_red ? 1 : 2);
+    const uint32_t rb = static_cast<uint32_t>(role == 0 ? blk : (role == 1 ? blk - n_in : blk - n_in - n_red));
+    const uint32_t nrb = static_cast<uint32_t>(role == 0 ? n_in : (role == 1 ? n_red : n_out));
+    // this block's chunks: rb, rb + nrb, ...; `i` counts them
+    const uint32_t mine_n = rb < nchunks ? (nchunks - rb + nrb - 1) / nrb : 0;
     const uint64_t tile = uint64_t(nwork) * U;
     const uint64_t ctile = uint64_t(nwork) * UC;
     char* my_a = c.ctrl[me] + c.off_stage_a;
     char* my_b = c.ctrl[me] + c.off_stage_b;
 
-    if (wt < 0) {
-      // ---------------------------------------------------------------- control warp
+    if (wt < -32) {
+      // ---------------------------------------------------------------- publisher (warp 0, lane 0)
       if (threadIdx.x == 0) {
         const uint32_t warps = static_cast<uint32_t>(nwork / 32);
-        const int role_blocks = role == 0 ? n_in : (role == 1 ? n_red : n_out);
         const size_t flag_off = role == 0 ? kOffIn : (role == 1 ? kOffRed : kOffOut);
-        for (uint32_t ch = 0; ch < nchunks; ++ch) {
-          const uint32_t g = base + ch;
-          const int slot = static_cast<int>(g % kPipeSlots);
-          bool ok = true;
-          if (ctl.pipe_done[slot] < warps) {
-            const uint64_t t0 = globaltimer_ns();
-            for (uint32_t it = 1; ctl.pipe_done[slot] < warps; ++it) {
-              if (ctl.fail != 0) { ok = false; break; }
-              if ((it & 1023u) == 0u && globaltimer_ns() - t0 > c.spin_timeout_ns) {
-                ctl.fail = kDevTimeout;
-                record_failure(c, kDevTimeout, (static_cast<uint32_t>(blk) << 16) | 0xffffu);
-                ok = false;
-                break;
-              }
-            }
+        for (uint32_t i = 0; i < mine_n; ++i) {
+          if (!pipe_spin(c, ctl, &ctl.pipe_done[i % kPipeAhead], warps - 1)) {
+            if (ctl.fail == kDevTimeout) record_failure(c, kDevTimeout, (static_cast<uint32_t>(blk) << 16) | 0xffffu);
+            break;
           }
-          if (!ok) break;
-          ctl.pipe_done[slot] = 0;  // nobody counts into this slot again before the chunk is published
-          pipe_publish(c, role, slot, role_blocks, flag_off, g + 1);
+          ctl.pipe_done[i % kPipeAhead] = 0;  // counted into again only by chunk i + kPipeAhead, which waits for pipe_pub
+          const uint32_t g = base + rb + i * nrb;
+          pipe_publish(c, static_cast<int>(g % kPipeSlots), flag_off, g + 1);
+          ctl.pipe_pub = i + 1;
         }
       }
-    } else if (role == 0) {
-      // ---------------------------------------------------------------- copy-in
+    } else if (wt < 0) {
+      // ---------------------------------------------------------------- poller (warp 1)
+      for (uint32_t i = 0; i < mine_n; ++i) {
+        const uint32_t g = base + rb + i * nrb;
+        const int slot = static_cast<int>(g % kPipeSlots);
+        const bool reuse = g >= static_cast<uint32_t>(kPipeSlots);
+        bool ok = true;
+        if (role == 0) {
+          if (reuse) ok = pipe_poll_all(c, ctl, kOffRed, slot, g - kPipeSlots + 1, blk);
+        } else if (role == 1) {
+          ok = pipe_poll_all(c, ctl, kOffIn, slot, g + 1, blk);
+          if (ok && reuse) ok = pipe_poll_all(c, ctl, kOffOut, slot, g - kPipeSlots + 1, blk);
+        } else {
+          ok = pipe_poll_all(c, ctl, kOffRed, slot, g + 1, blk);
+        }
+        if (!ok) break;
+        if ((threadIdx.x & 31) == 0) {
+          __threadfence_block();
+          ctl.pipe_ready = i + 1;
+        }
+      }
+    } else {
+      // ---------------------------------------------------------------- workers
       const bool in_al = vec_aligned<InT, VW>(a.send);
-      for (uint32_t ch = 0; ch < nchunks; ++ch) {
+      const bool out_al = vec_aligned<OutT, VW>(a.recv);
+      for (uint32_t i = 0; i < mine_n; ++i) {
+        // inputs seen by the poller, and not more than kPipeAhead - 1 chunks ahead of the publisher
+        if (!pipe_spin(c, ctl, &ctl.pipe_ready, i)) break;
+        if (i >= static_cast<uint32_t>(kPipeAhead - 1) && !pipe_spin(c, ctl, &ctl.pipe_pub, i - (kPipeAhead - 1))) break;
+        __threadfence_block();  // acquire side of the poller's hand-over
+        const uint32_t ch = rb + i * nrb;
         const uint32_t g = base + ch;
         const int slot = static_cast<int>(g % kPipeSlots);
-        if (g >= static_cast<uint32_t>(kPipeSlots) &&
-            !pipe_wait_all(c, ctl, kOffRed, slot, g - kPipeSlots + 1, blk)) break;
-        const uint64_t e_begin = uint64_t(ch) * CE;
-        const uint64_t e_end = (e_begin + CE < a.count) ? e_begin + CE : a.count;
-        const uint64_t nvec = (e_end - e_begin + VW - 1) / VW;
-        char* dst = my_a + uint64_t(slot) * stride;
-        const uint64_t full = (e_end - e_begin) / VW;  // vectors that lie wholly inside the chunk
-        for (uint64_t v0 = uint64_t(blk) * ctile + wt; v0 < nvec; v0 += uint64_t(n_in) * ctile) {
-          if (kSameIn && in_al && v0 + uint64_t(UC - 1) * nwork < full) {
-            // same type, aligned, no ragged end: move the bits
-            const uint4* src = reinterpret_cast<const uint4*>(static_cast<const WRaw*>(a.send) + e_begin);
-            uint4 x[UC];
+        if (role == 0) {
+          // -------------------------------------------------------------- copy-in
+          const uint64_t e_begin = uint64_t(ch) * CE;
+          const uint64_t e_end = (e_begin + CE < a.count) ? e_begin + CE : a.count;
+          const uint64_t nvec = (e_end - e_begin + VW - 1) / VW;
+          char* dst = my_a + uint64_t(slot) * stride;
+          const uint64_t full = (e_end - e_begin) / VW;  // vectors that lie wholly inside the chunk
+          // peer-to-peer path: vectors [own_lo, own_hi) are my own shard, which is not staged
+          const uint64_t own_lo = NVLS ? nvec : uint64_t(me) * (E / VW);
+          const uint64_t own_hi = NVLS ? nvec : own_lo + E / VW;
+          for (uint64_t v0 = wt; v0 < nvec; v0 += ctile) {
+            if (v0 >= own_lo && v0 + uint64_t(UC - 1) * nwork < own_hi) continue;  // the whole step lies in my shard
+            if (NVLS && kSameIn && in_al && v0 + uint64_t(UC - 1) * nwork < full) {
+              // same type, aligned, no ragged end: move the bits
+              const uint4* src = reinterpret_cast<const uint4*>(static_cast<const WRaw*>(a.send) + e_begin);
+              uint4 x[UC];
 #pragma unroll
-            for (int u = 0; u < UC; ++u) x[u] = src[v0 + uint64_t(u) * nwork];
+              for (int u = 0; u < UC; ++u) x[u] = src[v0 + uint64_t(u) * nwork];
 #pragma unroll
-            for (int u = 0; u < UC; ++u) *reinterpret_cast<uint4*>(dst + (v0 + uint64_t(u) * nwork) * 16) = x[u];
-            continue;
-          }
+              for (int u = 0; u < UC; ++u) *reinterpret_cast<uint4*>(dst + (v0 + uint64_t(u) * nwork) * 16) = x[u];
+              continue;
+            }
+            if (!NVLS && kSameIn && in_al && v0 + uint64_t(UC - 1) * nwork < full) {
+              const uint4* src = reinterpret_cast<const uint4*>(static_cast<const WRaw*>(a.send) + e_begin);
+              uint4 x[UC];
+#pragma unroll
+              for (int u = 0; u < UC; ++u) {
+                const uint64_t v = v0 + uint64_t(u) * nwork;
+                if (v < own_lo || v >= own_hi) x[u] = src[v];
+              }
+#pragma unroll
+              for (int u = 0; u < UC; ++u) {
+                const uint64_t v = v0 + uint64_t(u) * nwork;
+                if (v < own_lo || v >= own_hi) *reinterpret_cast<uint4*>(dst + v * 16) = x[u];
+              }
+              continue;
+            }
 #pragma unroll 2
-          for (int u = 0; u < UC; ++u) {
-            const uint64_t v = v0 + uint64_t(u) * nwork;
-            if (v >= nvec) continue;
-            typename Elem<InT>::Acc x[VW];
-            load_vec<InT, VW>(a.send, e_begin + v * VW, e_end, in_al, x);
-            Acc w[VW];
-#pragma unroll
-            for (int k = 0; k < VW; ++k) w[k] = static_cast<Acc>(x[k]);
-            Packed<WireT, VW> pk;
-            pk.from_acc(w);
-            *reinterpret_cast<uint4*>(dst + v * 16) = pk.vec.q[0];
-          }
-        }
-        pipe_warp_done(ctl, slot);
-      }
-    } else if (role == 1) {
-      // ---------------------------------------------------------------- reduce my shard
-      const int rb = blk - n_in;
-      for (uint32_t ch = 0; ch < nchunks; ++ch) {
-        const uint32_t g = base + ch;
-        const int slot = static_cast<int>(g % kPipeSlots);
-        if (!pipe_wait_all(c, ctl, kOffIn, slot, g + 1, blk)) break;
-        if (g >= static_cast<uint32_t>(kPipeSlots) &&
-            !pipe_wait_all(c, ctl, kOffOut, slot, g - kPipeSlots + 1, blk)) break;
-        const uint64_t e_begin = uint64_t(ch) * CE + uint64_t(me) * E;  // my shard of this chunk
-        uint64_t e_end = e_begin + E;
-        if (e_end > a.count) e_end = a.count;
-        const uint64_t nvec = e_begin < e_end ? (e_end - e_begin + VW - 1) / VW : 0;
-        const uint64_t in_off = uint64_t(slot) * stride + uint64_t(me) * E * sizeof(WRaw);
-        const uint64_t out_off = uint64_t(slot) * stride + uint64_t(me) * E * sizeof(ORaw);
-        for (uint64_t v0 = uint64_t(rb) * tile + wt; v0 < nvec; v0 += uint64_t(n_red) * tile) {
-          Acc acc[U][VW];
-          if constexpr (NVLS) {
-            uint4 r[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
+            for (int u = 0; u < UC; ++u) {
               const uint64_t v = v0 + uint64_t(u) * nwork;
-              r[u] = make_uint4(0, 0, 0, 0);
-              if (v < nvec) r[u] = Nvls<WireT>::ld_reduce_add(c.ctrl_mc + c.off_stage_a + in_off + v * 16);
-            }
+              if (v >= nvec || (v >= own_lo && v < own_hi)) continue;
+              typename Elem<InT>::Acc x[VW];
+              load_vec<InT, VW>(a.send, e_begin + v * VW, e_end, in_al, x);
+              Acc w[VW];
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-              Packed<WireT, VW> in;
-              in.vec.q[0] = r[u];
-              in.to_acc(acc[u]);
+              for (int k = 0; k < VW; ++k) w[k] = static_cast<Acc>(x[k]);
+              Packed<WireT, VW> pk;
+              pk.from_acc(w);
+              *reinterpret_cast<uint4*>(dst + v * 16) = pk.vec.q[0];
             }
-          } else {
-            for (int r = 0; r < N; ++r) {
-              uint4 got[U];
-              const char* src = c.ctrl[r] + c.off_stage_a + in_off;
+          }
+        } else if (role == 1) {
+          // -------------------------------------------------------------- reduce my shard
+          const uint64_t e_begin = uint64_t(ch) * CE + uint64_t(me) * E;  // my shard of this chunk
+          uint64_t e_end = e_begin + E;
+          if (e_end > a.count) e_end = a.count;
+          const uint64_t nvec = e_begin < e_end ? (e_end - e_begin + VW - 1) / VW : 0;
+          const uint64_t in_off = uint64_t(slot) * stride + uint64_t(me) * E * sizeof(WRaw);
+          const uint64_t out_off = uint64_t(slot) * stride + uint64_t(me) * E * sizeof(ORaw);
+          for (uint64_t v0 = wt; v0 < nvec; v0 += tile) {
+            Acc acc[U][VW];
+            if constexpr (NVLS) {
+              uint4 r[U];
 #pragma unroll
               for (int u = 0; u < U; ++u) {
                 const uint64_t v = v0 + uint64_t(u) * nwork;
-                got[u] = make_uint4(0, 0, 0, 0);
-                if (v < nvec) got[u] = *reinterpret_cast<const uint4*>(src + v * 16);
+                r[u] = make_uint4(0, 0, 0, 0);
+                if (v < nvec) r[u] = Nvls<WireT>::ld_reduce_add(c.ctrl_mc + c.off_stage_a + in_off + v * 16);
               }
 #pragma unroll
               for (int u = 0; u < U; ++u) {
                 Packed<WireT, VW> in;
-                in.vec.q[0] = got[u];
-                Acc val[VW];
-                in.to_acc(val);
-#pragma unroll
-                for (int k = 0; k < VW; ++k) acc[u][k] = (r == 0) ? val[k] : combine<OP>(acc[u][k], val[k]);
+                in.vec.q[0] = r[u];
+                in.to_acc(acc[u]);
               }
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const uint64_t v = v0 + uint64_t(u) * nwork;
-            if (v >= nvec) continue;
-            OAcc y[VW];
-#pragma unroll
-            for (int k = 0; k < VW; ++k) y[k] = finalize<OutT>(static_cast<OAcc>(acc[u][k]), a);
-            Packed<OutT, VW> pk;
-            pk.from_acc(y);
-            if constexpr (NVLS) {
-              char* dst = c.ctrl_mc + c.off_stage_b + out_off + v * OUT_VB;
-#pragma unroll
-              for (int q = 0; q < OUT_VB / 16; ++q) multimem_st_v4(dst + q * 16, pk.vec.q[q]);
             } else {
-              for (int k = 0; k < N; ++k) {
-                const int p = (me + k) % N;
-                char* dst = c.ctrl[p] + c.off_stage_b + out_off + v * OUT_VB;
+              for (int r = 0; r < N; ++r) {
+                uint4 got[U];
+                if (r == me) {
+                  // my own contribution comes from the user's buffer, rounded to the wire type like everyone's
 #pragma unroll
-                for (int q = 0; q < OUT_VB / 16; ++q) reinterpret_cast<uint4*>(dst)[q] = pk.vec.q[q];
+                  for (int u = 0; u < U; ++u) {
+                    const uint64_t v = v0 + uint64_t(u) * nwork;
+                    got[u] = make_uint4(0, 0, 0, 0);
+                    if (v < nvec) {
+                      typename Elem<InT>::Acc x[VW];
+                      load_vec<InT, VW>(a.send, e_begin + v * VW, e_end, in_al, x);
+                      Acc w[VW];
+#pragma unroll
+                      for (int k = 0; k < VW; ++k) w[k] = static_cast<Acc>(x[k]);
+                      Packed<WireT, VW> pk;
+                      pk.from_acc(w);
+                      got[u] = pk.vec.q[0];
+                    }
+                  }
+                } else {
+                  const char* src = c.ctrl[r] + c.off_stage_a + in_off;
+#pragma unroll
+                  for (int u = 0; u < U; ++u) {
+                    const uint64_t v = v0 + uint64_t(u) * nwork;
+                    got[u] = make_uint4(0, 0, 0, 0);
+                    // L2-only loads: the slot held another chunk earlier in this kernel, a line of it
+                    // must not be served from this SM's L1
+                    if (v < nvec) got[u] = ld_cg_v4(src + v * 16);
+                  }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                  Packed<WireT, VW> in;
+                  in.vec.q[0] = got[u];
+                  Acc val[VW];
+                  in.to_acc(val);
+#pragma unroll
+                  for (int k = 0; k < VW; ++k) acc[u][k] = (r == 0) ? val[k] : combine<OP>(acc[u][k], val[k]);
+                }
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const uint64_t v = v0 + uint64_t(u) * nwork;
+              if (v >= nvec) continue;
+              OAcc y[VW];
+#pragma unroll
+              for (int k = 0; k < VW; ++k) y[k] = finalize<OutT>(static_cast<OAcc>(acc[u][k]), a);
+              Packed<OutT, VW> pk;
+              pk.from_acc(y);
+              if constexpr (NVLS) {
+                char* dst = c.ctrl_mc + c.off_stage_b + out_off + v * OUT_VB;
+#pragma unroll
+                for (int q = 0; q < OUT_VB / 16; ++q) multimem_st_v4(dst + q * 16, pk.vec.q[q]);
+              } else {
+                store_vec<OutT, VW>(a.recv, e_begin + v * VW, e_end, out_al, y);  // mine: straight to the user's buffer
+                for (int k = 1; k < N; ++k) {
+                  const int p = (me + k) % N;
+                  char* dst = c.ctrl[p] + c.off_stage_b + out_off + v * OUT_VB;
+#pragma unroll
+                  for (int q = 0; q < OUT_VB / 16; ++q) reinterpret_cast<uint4*>(dst)[q] = pk.vec.q[q];
+                }
               }
             }
           }
-        }
-        pipe_warp_done(ctl, slot);
-      }
-    } else {
-      // ---------------------------------------------------------------- copy-out
-      const int ob = blk - n_in - n_red;
-      const bool out_al = vec_aligned<OutT, VW>(a.recv);
-      for (uint32_t ch = 0; ch < nchunks; ++ch) {
-        const uint32_t g = base + ch;
-        const int slot = static_cast<int>(g % kPipeSlots);
-        if (!pipe_wait_all(c, ctl, kOffRed, slot, g + 1, blk)) break;
-        const uint64_t e_begin = uint64_t(ch) * CE;
-        const uint64_t e_end = (e_begin + CE < a.count) ? e_begin + CE : a.count;
-        const uint64_t nvec = (e_end - e_begin + VW - 1) / VW;
-        const char* src = my_b + uint64_t(slot) * stride;
-        const uint64_t full = (e_end - e_begin) / VW;
-        for (uint64_t v0 = uint64_t(ob) * ctile + wt; v0 < nvec; v0 += uint64_t(n_out) * ctile) {
-          if (out_al && v0 + uint64_t(UC - 1) * nwork < full) {
-            constexpr int Q = OUT_VB / 16;
-            uint4* dstv = reinterpret_cast<uint4*>(static_cast<ORaw*>(a.recv) + e_begin);
-            uint4 y[UC][Q];
+        } else {
+          // -------------------------------------------------------------- copy-out
+          const uint64_t e_begin = uint64_t(ch) * CE;
+          const uint64_t e_end = (e_begin + CE < a.count) ? e_begin + CE : a.count;
+          const uint64_t nvec = (e_end - e_begin + VW - 1) / VW;
+          const char* src = my_b + uint64_t(slot) * stride;
+          const uint64_t full = (e_end - e_begin) / VW;
+          const uint64_t own_lo = NVLS ? nvec : uint64_t(me) * (E / VW);  // my shard is already in recv (peer-to-peer path)
+          const uint64_t own_hi = NVLS ? nvec : own_lo + E / VW;
+          for (uint64_t v0 = wt; v0 < nvec; v0 += ctile) {
+            if (v0 >= own_lo && v0 + uint64_t(UC - 1) * nwork < own_hi) continue;
+            if (out_al && v0 + uint64_t(UC - 1) * nwork < full) {
+              constexpr int Q = OUT_VB / 16;
+              uint4* dstv = reinterpret_cast<uint4*>(static_cast<ORaw*>(a.recv) + e_begin);
+              uint4 y[UC][Q];
 #pragma unroll
-            for (int u = 0; u < UC; ++u)
+              for (int u = 0; u < UC; ++u) {
+                const uint64_t v = v0 + uint64_t(u) * nwork;
+                if (v < own_lo || v >= own_hi) {
 #pragma unroll
-              for (int q = 0; q < Q; ++q) y[u][q] = reinterpret_cast<const uint4*>(src)[(v0 + uint64_t(u) * nwork) * Q + q];
+                  for (int q = 0; q < Q; ++q) y[u][q] = ld_cg_v4(src + (v * Q + q) * 16);
+                }
+              }
 #pragma unroll
-            for (int u = 0; u < UC; ++u)
+              for (int u = 0; u < UC; ++u) {
+                const uint64_t v = v0 + uint64_t(u) * nwork;
+                if (v < own_lo || v >= own_hi) {
 #pragma unroll
-              for (int q = 0; q < Q; ++q) dstv[(v0 + uint64_t(u) * nwork) * Q + q] = y[u][q];
-            continue;
-          }
+                  for (int q = 0; q < Q; ++q) dstv[v * Q + q] = y[u][q];
+                }
+              }
+              continue;
+            }
 #pragma unroll 2
-          for (int u = 0; u < UC; ++u) {
-            const uint64_t v = v0 + uint64_t(u) * nwork;
-            if (v >= nvec) continue;
-            OAcc y[VW];
-            load_vec<OutT, VW>(src + v * OUT_VB, 0, VW, true, y);
-            store_vec<OutT, VW>(a.recv, e_begin + v * VW, e_end, out_al, y);
+            for (int u = 0; u < UC; ++u) {
+              const uint64_t v = v0 + uint64_t(u) * nwork;
+              if (v >= nvec || (v >= own_lo && v < own_hi)) continue;
+              Packed<OutT, VW> pk;
+#pragma unroll
+              for (int q = 0; q < OUT_VB / 16; ++q) pk.vec.q[q] = ld_cg_v4(src + v * OUT_VB + q * 16);
+              OAcc y[VW];
+              pk.to_acc(y);
+              store_vec<OutT, VW>(a.recv, e_begin + v * VW, e_end, out_al, y);
+            }
           }
         }
-        pipe_warp_done(ctl, slot);
+        pipe_warp_done(ctl, i);
       }
     }
     // the last block to leave moves the base past this call's chunks

@@ -48,13 +48,12 @@ struct LocalState {
 // areas are rings of kPipeSlots slots; chunk number g (counted over ALL pipelined calls of the
 // communicator, so nothing is ever reset) lives in slot g % kPipeSlots and its flags carry g + 1.
 // in_ready / red_done / out_done are written by every rank into every rank's copy (index: slot,
-// then source rank); the tickets and the base are private to the owner.
-constexpr int kPipeSlots = 16;
+// then source rank); the base is private to the owner.
+constexpr int kPipeSlots = 64;
 struct PipeCtl {
   uint32_t in_ready[kPipeSlots][kMaxRanks];   // source rank has staged its input chunk
   uint32_t red_done[kPipeSlots][kMaxRanks];   // source rank has reduced its shard of the chunk into every stage_b
   uint32_t out_done[kPipeSlots][kMaxRanks];   // source rank has copied the chunk out of its stage_b
-  uint32_t tick[3][kPipeSlots];               // blocks of a role that have finished the chunk in this slot
   uint32_t base;                              // number of chunks handled by earlier calls
   uint32_t finished;                          // blocks that have left the running call
   uint32_t pad[2];

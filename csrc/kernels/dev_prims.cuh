@@ -44,6 +44,15 @@ __device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
                : "memory");
   return v;
 }
+// 16-byte load that is cached in L2 only: for buffers whose lines this SM may hold from an earlier use.
+__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
 __device__ __forceinline__ void st_volatile_v4(void* p, uint4 v) {
   asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
                "r"(v.w)
@@ -61,7 +70,11 @@ struct BlockCtl {        // one per thread block, in shared memory
   uint32_t epoch;        // this block's barrier epoch (cached from LocalState)
   uint32_t ll_seq;
   volatile uint32_t fail;  // DevStatus of the first failed wait in this block
-  volatile uint32_t pipe_done[kPipeSlots];  // pipelined kernel: worker warps that have finished the chunk in a ring slot
+  // pipelined kernel (pipe_body): worker warps that have finished the block's i-th chunk (ring of 4),
+  // chunks of this block whose inputs the poller has seen, chunks the publisher has published
+  volatile uint32_t pipe_done[4];
+  volatile uint32_t pipe_ready;
+  volatile uint32_t pipe_pub;
 };
 
 __device__ __forceinline__ LocalState* local_state(const CommDev& c) {
@@ -104,7 +117,9 @@ __device__ __forceinline__ void block_begin(const CommDev& c, int blk, BlockCtl&
     ctl.epoch = ls->epoch[blk];
     ctl.ll_seq = ls->ll_seq[blk];
     ctl.fail = 0;
-    for (int i = 0; i < kPipeSlots; ++i) ctl.pipe_done[i] = 0;
+    for (int i = 0; i < 4; ++i) ctl.pipe_done[i] = 0;
+    ctl.pipe_ready = 0;
+    ctl.pipe_pub = 0;
     if (blk == 0) {
       uint32_t s = ls->started + 1;
       ls->started = s;

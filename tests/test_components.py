@@ -195,12 +195,14 @@ def test_planner_pipelined_kernel_for_large_ordinary_buffers(lib):
     assert p["shard"] % 4 == 0 and p["shard"] * 8 * 4 <= (256 << 20) // 16 and 3 <= p["nblocks"] <= 140
     assert plan(lib, 8, 1 << 26, nvls=1, in_sym=1, out_sym=1)["algo"] == "nvls"     # symmetric buffers stay zero-copy
     assert plan(lib, 8, (8 << 20) // 4, nvls=1)["algo"] != "pipe"                    # below the threshold
-    q = plan(lib, 2, 1 << 26)                            # two ranks: peer-to-peer reduction inside the same kernel
+    assert plan(lib, 2, 1 << 26)["algo"] == "twoshot"     # two ranks keep the stream pipeline around the two-phase kernel
+    q = plan(lib, 2, 1 << 26, forced=7)                  # ... unless the pipelined kernel is asked for (peer-to-peer reduction)
     assert q["algo"] == "pipe" and q["shard"] % 4 == 0
+    assert plan(lib, 8, 1 << 26, nvls=1, op=_lib.MAX)["algo"] == "twoshot"          # the switch only adds
     m = plan(lib, 8, 1 << 25, nvls=1, wire=_lib.BFLOAT16, out=_lib.FLOAT32)          # fp32 out of a bf16 wire: slot bound by the output
     assert m["algo"] == "pipe" and m["shard"] % 8 == 0 and m["shard"] * 8 * 4 <= (256 << 20) // 16
-    t = plan(lib, 4, 1 << 26, stage=1 << 20)             # tiny staging: 64 KB slots
-    assert t["algo"] == "pipe" and t["shard"] * 4 * 4 <= (1 << 20) // 16
+    t = plan(lib, 4, 1 << 26, nvls=1, stage=1 << 20)     # tiny staging: 16 KB slots
+    assert t["algo"] == "pipe" and t["shard"] * 4 * 4 <= (1 << 20) // 64
     assert plan(lib, 8, 1 << 26, mode=1)["algo"] == "twoshot"                        # only AllReduce is pipelined
 
 
