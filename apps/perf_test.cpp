@@ -68,7 +68,11 @@ int main(int argc, char** argv) {
   int ndev = 0;
   bool gpu = cudaGetDeviceCount(&ndev) == cudaSuccess && ndev > 0;
   if (!gpu) (void)cudaGetLastError();
-  if (gpu && rank_arg >= 0) cudaSetDevice(rank_arg % ndev);  // Hera mode: the library picks the GPU from the local rank
+  // PERF_TEST_SHARE_GPU=1: every rank on GPU 0, the reference benchmark's layout (reference:
+  // tests/perf_test.cpp:46); the library then runs its host-synchronised plane for ranks that share a GPU.
+  const bool share_gpu = getenv("PERF_TEST_SHARE_GPU") && atoi(getenv("PERF_TEST_SHARE_GPU")) != 0;
+  if (gpu && share_gpu) cudaSetDevice(0);
+  else if (gpu && rank_arg >= 0) cudaSetDevice(rank_arg % ndev);  // Hera mode: the library picks the GPU from the local rank
 
   ncclComm_t comm;
   NCCL_OK(ncclCommInitRank(&comm, n, rank_arg, ip));

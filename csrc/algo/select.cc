@@ -143,7 +143,9 @@ Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
   if (algo == Algo::OneShot) {
     const uint64_t vecs = ceil_div(wire_bytes, 16);
     p.spec.nthreads = vecs <= 256 ? 256 : 512;
-    p.spec.nblocks = static_cast<int>(std::clamp<uint64_t>(ceil_div(vecs, p.spec.nthreads), 1, max_blocks ? max_blocks : 64));
+    // measured on 8 GPUs, 1 MiB on ordinary buffers: 29.4 us with 64 blocks, 27.7 us with 128 (NCCL: 30)
+    const uint64_t cap = max_blocks ? max_blocks : (wire_bytes >= (768u << 10) ? 128 : 64);
+    p.spec.nblocks = static_cast<int>(std::clamp<uint64_t>(ceil_div(vecs, p.spec.nthreads), 1, cap));
     p.valid = true;
     return p;
   }
@@ -157,6 +159,13 @@ Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
     uint64_t ce = std::min<uint64_t>(target / wsz, stride / std::max(wsz, osz));
     uint64_t E = ce / (uint64_t(N) * VW) * VW;
     if (E == 0) { p.reason = "staging buffer too small for the pipelined kernel"; return p; }
+    // Ramp: four chunks of 1/16, 1/8, 1/4 and 1/2 of the regular size first, where the shard still divides
+    // into whole vectors and the message is long enough for it to matter.
+    const uint64_t unit = VW << 4;
+    if (E >= 4 * unit && total_elems >= 8 * E * uint64_t(N)) {
+      E = E / unit * unit;
+      p.pipe_ramp = 4;
+    }
     p.shard_elems = E;
     p.chunk_shard_vecs = E / VW;
     p.copy_in = p.copy_out = true;

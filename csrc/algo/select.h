@@ -55,6 +55,7 @@ struct Plan {
   uint64_t shard_elems = 0;
   uint64_t chunk_shard_vecs = 0;
   bool copy_in = false, copy_out = false;
+  int pipe_ramp = 0;           // pipelined kernel: small first chunks (shard_elems is divisible by vector width << pipe_ramp)
   bool valid = false;
   const char* reason = "";  // why the plan is invalid
 };

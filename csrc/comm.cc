@@ -209,18 +209,27 @@ void Comm::init(int nranks, int rank, const char* ip) {
     }
   }
   bool want_gpu_plane = size_ == 1 ? has_gpu_ : (one_host && all_gpu && distinct && p2p_ok && size_ <= kMaxRanks);
-  if (cfg_.transport == "soft" || cfg_.transport == "verbs") want_gpu_plane = false;
+  // Ranks that share a GPU (the reference's benchmark pins every rank to GPU 0, reference:
+  // tests/perf_test.cpp:46): kernels of different processes on one GPU cannot wait for one another, so
+  // the NVLink plane is out; a host-synchronised plane over CUDA IPC staging takes its place.
+  bool want_shared = size_ > 1 && has_gpu_ && one_host && all_gpu && !distinct && size_ <= kMaxRanks;
+  if (cfg_.transport == "soft" || cfg_.transport == "verbs") want_gpu_plane = want_shared = false;
   // Every rank must take the same plane.
-  uint8_t mine = want_gpu_plane ? 1 : 0;
+  uint8_t mine = want_gpu_plane ? 1 : (want_shared ? 2 : 0);
   std::vector<uint8_t> votes(size_);
   store_->all_gather(&mine, votes.data(), 1);
   gpu_plane_ = true;
-  for (uint8_t v : votes) gpu_plane_ = gpu_plane_ && v;
+  shared_plane_ = true;
+  for (uint8_t v : votes) {
+    gpu_plane_ = gpu_plane_ && v == 1;
+    shared_plane_ = shared_plane_ && v == 2;
+  }
   if (cfg_.transport == "nvlink" && !gpu_plane_)
     fail(Result::SystemError, "MINI_NCCL_TRANSPORT=nvlink but the ranks do not share one NVLink-connected host");
 
   setup_shared_host_segment();
   if (gpu_plane_) init_gpu_plane();
+  else if (shared_plane_) init_shared_gpu_plane();
   else init_net_plane();
 
   if (hera_ && cfg_.hera_keepalive) {
@@ -231,7 +240,7 @@ void Comm::init(int nranks, int rank, const char* ip) {
   }
   store_->barrier();
   MNCCL_INFO("Mini-NCCL", "rank %d/%d ready: plane=%s device=%d local_rank=%d", rank_, size_,
-             gpu_plane_ ? "nvlink" : (transport_ ? transport_->name() : "none"), device_, local_rank_);
+             gpu_plane_ ? "nvlink" : (shared_plane_ ? "shared-gpu" : (transport_ ? transport_->name() : "none")), device_, local_rank_);
 }
 
 void Comm::setup_shared_host_segment() {
@@ -356,6 +365,124 @@ void Comm::init_gpu_plane() {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Plane for ranks that share a GPU.  Every rank owns a staging buffer in device memory that all
+// ranks map over CUDA IPC.  An AllReduce is, per piece of at most one staging buffer:
+//   copy the input into my staging  ->  host barrier  ->  ONE kernel per rank that adds all ranks'
+//   staging in rank order into my result  ->  host barrier (staging may be overwritten again).
+// No kernel ever waits for another process's kernel; the ranks meet on the HOST, on per-rank epoch
+// words in the shared page (bounded by the watchdog timeout, ended by the abort word).  The call is
+// host-synchronous, like the reference's (reference: src/mini_nccl.cu:200-214).  This is what the
+// reference's CUDA-IPC branch (reference: src/mini_nccl.cu:128-133,171-176) is meant to be.
+void Comm::init_shared_gpu_plane() {
+  if (!shm_map_ || private_host_)
+    fail(Result::SystemError, "ranks that share a GPU need the host's shared page for their barrier (shm_open failed)");
+  shared_stage_bytes_ = std::min<size_t>(cfg_.staging_bytes, size_t(64) << 20);
+  RT_CHECK(cudaMalloc(reinterpret_cast<void**>(&shared_stage_), shared_stage_bytes_), "cudaMalloc(shared staging)");
+  RT_CHECK(cudaMalloc(reinterpret_cast<void**>(&shared_out_), shared_stage_bytes_), "cudaMalloc(shared result staging)");
+  struct Wire {
+    cudaIpcMemHandle_t handle;
+    int32_t ok;
+  } mine{};
+  mine.ok = cudaIpcGetMemHandle(&mine.handle, shared_stage_) == cudaSuccess ? 1 : 0;
+  if (!mine.ok) (void)cudaGetLastError();
+  std::vector<Wire> all(size_);
+  store_->all_gather(&mine, all.data(), sizeof(mine));
+  shared_peer_stage_.assign(size_, nullptr);
+  bool ok = true;
+  for (int r = 0; r < size_ && ok; ++r) {
+    if (!all[r].ok) { ok = false; break; }
+    if (r == rank_) { shared_peer_stage_[r] = shared_stage_; continue; }
+    void* p = nullptr;
+    if (cudaIpcOpenMemHandle(&p, all[r].handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+      (void)cudaGetLastError();
+      ok = false;
+      break;
+    }
+    shared_peer_stage_[r] = static_cast<char*>(p);
+  }
+  uint8_t mine_ok = ok ? 1 : 0;
+  std::vector<uint8_t> oks(size_);
+  store_->all_gather(&mine_ok, oks.data(), 1);
+  for (uint8_t v : oks) ok = ok && v;
+  if (!ok) fail(Result::SystemError, "cannot map the peers' staging over CUDA IPC");
+  memset(&dev_, 0, sizeof(dev_));
+  dev_.rank = rank_;
+  dev_.nranks = size_;
+}
+
+// All ranks of the host meet: each publishes its epoch in its own words of the shared page and waits
+// until every rank's epoch has caught up.  Bounded; the abort word ends it.
+void Comm::host_barrier() {
+  volatile uint32_t* words = static_cast<volatile uint32_t*>(shm_map_);
+  const uint32_t e = ++shared_epoch_;
+  __atomic_store_n(const_cast<uint32_t*>(progress_host_ + 8), e, __ATOMIC_RELEASE);
+  const auto t0 = std::chrono::steady_clock::now();
+  for (int r = 0; r < size_; ++r) {
+    volatile uint32_t* w = words + kProgressWords * (1 + r) + 8;
+    uint32_t spins = 0;
+    while (static_cast<int32_t>(__atomic_load_n(const_cast<uint32_t*>(w), __ATOMIC_ACQUIRE) - e) < 0) {
+      if ((++spins & 1023u) != 0) continue;
+      if (*abort_host_ != 0) {
+        aborted_.store(true);
+        fail(Result::InternalError, "NCCL Watchdog Timeout: Communication hang detected.");
+      }
+      const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+      if (ms > cfg_.watchdog_timeout_ms) {
+        log_always("Watchdog", "TIMEOUT DETECTED! rank %d waited %lld ms for rank %d at a host barrier", rank_, static_cast<long long>(ms), r);
+        __atomic_store_n(const_cast<uint32_t*>(abort_host_), 1u, __ATOMIC_RELEASE);
+        aborted_.store(true);
+        fail(Result::InternalError, "NCCL Watchdog Timeout: Communication hang detected.");
+      }
+      if (spins > (1u << 16)) std::this_thread::yield();
+    }
+  }
+}
+
+void Comm::shared_gpu_all_reduce(const void* send, void* recv, size_t count, DType t, RedOp op, double scale,
+                                 cudaStream_t stream) {
+  const size_t esz = dtype_size(t);
+  const bool is_float = t == DType::Float16 || t == DType::Bfloat16 || t == DType::Float32 || t == DType::Float64;
+  if (!is_float && scale != 1.0) fail(Result::InvalidArgument, "a scale factor needs a floating-point type");
+  const MemKind sk = classify(send, true), rk = classify(recv, true);
+  if (sk == MemKind::PlainHost || rk == MemKind::PlainHost)
+    fail(Result::InvalidArgument, "buffers must be device memory or pinned host memory");
+  LaunchSpec spec;
+  spec.algo = Algo::HostSync;
+  spec.mode = Mode::AllReduce;
+  spec.in = spec.wire = spec.out = t;
+  spec.op = op;
+  spec.nthreads = 512;
+  if (!kernel_exists(spec)) fail(Result::InvalidArgument, "no kernel for this type / operator combination");
+  const size_t cap = (shared_stage_bytes_ / esz) & ~size_t(15);
+  const double factor = scale * (op == RedOp::Avg ? 1.0 / static_cast<double>(size_) : 1.0);
+  for (size_t off = 0; off < count; off += cap) {
+    const size_t n = std::min(cap, count - off);
+    RT_CHECK(cudaMemcpyAsync(shared_stage_, static_cast<const char*>(send) + off * esz, n * esz, cudaMemcpyDefault, stream),
+             "cudaMemcpyAsync(stage)");
+    RT_CHECK(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+    host_barrier();  // every rank's piece is staged
+    KParams kp;
+    memset(&kp, 0, sizeof(kp));
+    kp.comm = dev_;
+    CollArgs& a = kp.args;
+    for (int r = 0; r < size_; ++r) a.in_peer[r] = shared_peer_stage_[r];
+    char* dst = static_cast<char*>(recv) + off * esz;
+    const bool to_host = rk != MemKind::Device;
+    a.recv = to_host ? static_cast<void*>(shared_out_) : static_cast<void*>(dst);
+    a.count = n;
+    a.scale_f = static_cast<float>(factor);
+    a.scale_d = factor;
+    a.int_div = (op == RedOp::Avg && !is_float) ? size_ : 0;
+    const size_t vecs = (n * esz + 15) / 16;
+    spec.nblocks = static_cast<int>(std::min<size_t>(std::max<size_t>(vecs / 2048, 1), 592));
+    RT_CHECK(launch_collective(spec, kp, stream), "kernel launch");
+    if (to_host) RT_CHECK(cudaMemcpyAsync(dst, shared_out_, n * esz, cudaMemcpyDeviceToHost, stream), "cudaMemcpyAsync(result)");
+    RT_CHECK(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+    host_barrier();  // every rank has read every staging: it may be overwritten
+  }
+}
+
 void Comm::init_net_plane() {
   std::string kind = cfg_.transport;
   if (kind == "nvlink" || kind.empty()) kind = "auto";
@@ -392,6 +519,12 @@ Comm::~Comm() {
     cudaFree(solo_stage_);
     solo_stage_ = nullptr;
   }
+  for (int r = 0; r < static_cast<int>(shared_peer_stage_.size()); ++r)
+    if (r != rank_ && shared_peer_stage_[r]) cudaIpcCloseMemHandle(shared_peer_stage_[r]);
+  shared_peer_stage_.clear();
+  if (shared_stage_) cudaFree(shared_stage_);
+  if (shared_out_) cudaFree(shared_out_);
+  shared_stage_ = shared_out_ = nullptr;
   ring_.reset();
   transport_.reset();
   {
@@ -538,6 +671,7 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
   a.int_div = (op == RedOp::Avg && !is_float) ? size_ : 0;
   a.copy_in = plan.copy_in ? 1 : 0;
   a.copy_out = plan.copy_out ? 1 : 0;
+  a.pipe_ramp = plan.pipe_ramp;
   if (size_ > 1 && (plan.spec.algo == Algo::TwoShot || plan.spec.algo == Algo::Nvls)) {
     const bool zc_in = !plan.copy_in && mode != Mode::AllGather;
     const bool zc_out = !plan.copy_out && mode != Mode::ReduceScatter;
@@ -811,9 +945,17 @@ void Comm::all_reduce(const void* send, DType send_t, void* recv, DType recv_t, 
       if (gpu_plane_)
         MNCCL_INFO("Mini-NCCL", "CUDA Graph capture detected: the collective is captured as one kernel node; flags and epochs are device-resident, so replays are safe.");
       else
-        log_always("Mini-NCCL", "[Warning] CUDA Graph capture detected, but the network data plane is driven by the host and cannot be captured.");
+        log_always("Mini-NCCL", "[Warning] CUDA Graph capture detected, but this data plane is driven by the host and cannot be captured.");
     }
     if (!gpu_plane_) fail(Result::InvalidUsage, "the network data plane cannot run under CUDA Graph capture");
+  }
+  if (shared_plane_) {
+    if (send_t != recv_t || send_t != wire_t) fail(Result::InvalidArgument, "ranks that share a GPU reduce homogeneous types");
+    shared_gpu_all_reduce(send, recv, count, send_t, op, scale, stream);
+    stats_.calls++;
+    stats_.bytes += count * dtype_size(send_t);
+    stats_.by_algo[static_cast<int>(Algo::HostSync)]++;
+    return;
   }
   if (!gpu_plane_) {
     if (send_t != recv_t || send_t != wire_t || scale != 1.0)
@@ -1054,10 +1196,10 @@ Algo Comm::query_algo(size_t bytes, DType t, RedOp op, bool registered) {
 
 std::string Comm::stats_json() {
   std::ostringstream o;
-  o << "{\"rank\":" << rank_ << ",\"size\":" << size_ << ",\"plane\":\"" << (gpu_plane_ ? "nvlink" : (transport_ ? transport_->name() : "none"))
+  o << "{\"rank\":" << rank_ << ",\"size\":" << size_ << ",\"plane\":\"" << (gpu_plane_ ? "nvlink" : (shared_plane_ ? "shared-gpu" : (transport_ ? transport_->name() : "none")))
     << "\",\"device\":" << device_ << ",\"symmetric_provider\":\"" << (symm_ ? symm_->provider() : "none") << "\",\"nvls\":"
     << (caps_.nvls ? "true" : "false") << ",\"calls\":" << stats_.calls << ",\"bytes\":" << stats_.bytes << ",\"algo\":{";
-  const Algo algos[] = {Algo::LL, Algo::OneShot, Algo::TwoShot, Algo::Nvls, Algo::Ring, Algo::Local, Algo::Pipe};
+  const Algo algos[] = {Algo::LL, Algo::OneShot, Algo::TwoShot, Algo::Nvls, Algo::Ring, Algo::Local, Algo::Pipe, Algo::HostSync};
   bool first = true;
   for (Algo a : algos) {
     if (!first) o << ",";

@@ -33,7 +33,7 @@ namespace hera { class Worker; }
 
 struct CommStats {
   uint64_t calls = 0, bytes = 0;
-  uint64_t by_algo[8] = {0};
+  uint64_t by_algo[12] = {0};
   uint64_t zero_copy_in = 0, zero_copy_out = 0, staged_passes = 0, pipelined = 0;
   uint64_t graph_captures_seen = 0, errors = 0;
 };
@@ -91,6 +91,9 @@ class Comm {
                         cudaStream_t stream, bool host_in, bool host_out);
   void ensure_pipeline();
   void ring_all_reduce(const void* send, void* recv, size_t count, DType t, RedOp op, cudaStream_t stream);
+  void init_shared_gpu_plane();
+  void host_barrier();
+  void shared_gpu_all_reduce(const void* send, void* recv, size_t count, DType t, RedOp op, double scale, cudaStream_t stream);
   // Segment containing [ptr, ptr+bytes) on this rank; offset returned.
   std::shared_ptr<Segment> find_segment(const void* ptr, size_t bytes, size_t* offset);
   void wait_blocking(cudaStream_t stream);
@@ -140,6 +143,14 @@ class Comm {
   // single rank with pinned-host buffers: private device staging (two halves per direction)
   char* solo_stage_ = nullptr;
   size_t solo_stage_half_ = 0;
+
+  // plane for ranks that share a GPU: host-synchronised, staging exchanged over CUDA IPC
+  bool shared_plane_ = false;
+  char* shared_stage_ = nullptr;        // this rank's staging (cudaMalloc)
+  char* shared_out_ = nullptr;          // result staging for host-memory recv buffers
+  size_t shared_stage_bytes_ = 0;
+  std::vector<char*> shared_peer_stage_;  // every rank's staging as mapped here
+  uint32_t shared_epoch_ = 0;
 
   // network plane
   std::unique_ptr<OneSidedTransport> transport_;

@@ -240,6 +240,7 @@ MNCCL_EXPORT int mncclEmuCollective(void* world, int mode, const void* const* se
     a.int_div = (pi.op == RedOp::Avg && !is_float) ? N : 0;
     a.copy_in = plan.copy_in;
     a.copy_out = plan.copy_out;
+    a.pipe_ramp = plan.pipe_ramp;
     if (w->deaf[r]) {  // takes no part: moves nothing, signals nobody
       kp.comm.nranks = 0;
       a.count = 0;

@@ -68,6 +68,53 @@ __device__ __forceinline__ void local_body(const KParams& P, int blk, int nblk) 
   }
 }
 
+// -------------------------------------------------------------------- host-synchronised reduction
+// out = scale * op over ranks of in_peer[r][0 .. count), in rank order, fp32 accumulation.  No flag, no
+// wait, no control segment: the HOST orders the ranks (staging filled, barrier, this kernel, barrier).
+// This is the data plane for ranks that share one GPU, where kernels of different processes can never
+// be assumed to run at the same time and so must not wait for one another.
+template <typename InT, typename WireT, typename OutT, int OP>
+__device__ __forceinline__ void gather_reduce_body(const KParams& P, int blk, int nblk) {
+  const CollArgs& a = P.args;
+  const int N = P.comm.nranks;
+  using Acc = typename Elem<WireT>::Acc;
+  constexpr int VW = 16 / sizeof(typename Elem<WireT>::Raw);
+  constexpr int U = 4;
+  const bool out_al = vec_aligned<OutT, VW>(a.recv);
+  const uint64_t nvec = (a.count + VW - 1) / VW;
+  const uint64_t stride = uint64_t(nblk) * blockDim.x;
+  for (uint64_t v0 = uint64_t(blk) * blockDim.x + threadIdx.x; v0 < nvec; v0 += U * stride) {
+    Acc acc[U][VW];
+    for (int r = 0; r < N; ++r) {
+      uint4 got[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint64_t v = v0 + u * stride;
+        got[u] = make_uint4(0, 0, 0, 0);
+        if (v < nvec) got[u] = ld_cg_v4(a.in_peer[r] + v * 16);  // staging is rewritten between calls by other processes
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        Packed<WireT, VW> in;
+        in.vec.q[0] = got[u];
+        Acc val[VW];
+        in.to_acc(val);
+#pragma unroll
+        for (int k = 0; k < VW; ++k) acc[u][k] = (r == 0) ? val[k] : combine<OP>(acc[u][k], val[k]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint64_t v = v0 + u * stride;
+      if (v >= nvec) continue;
+      typename Elem<OutT>::Acc y[VW];
+#pragma unroll
+      for (int k = 0; k < VW; ++k) y[k] = finalize<OutT>(static_cast<typename Elem<OutT>::Acc>(acc[u][k]), a);
+      store_vec<OutT, VW>(a.recv, v * VW, a.count, out_al, y);
+    }
+  }
+}
+
 // -------------------------------------------------------------------- LL
 template <typename InT, typename WireT, typename OutT, int OP>
 __device__ __forceinline__ void ll_body(const KParams& P, int blk, int nblk, BlockCtl& ctl) {
@@ -448,6 +495,32 @@ __device__ __forceinline__ void twoshot_body(const KParams& P, int blk, int nblk
 // every rank's staging, the reader's own included.
 constexpr int kPipeAhead = 4;  // chunks of one block whose completion may be outstanding; size of BlockCtl::pipe_done
 
+// Chunk geometry with a ramp: the first R chunks are CE / 2^R, CE / 2^(R-1), ... CE / 2 elements, the
+// rest CE each.  The first chunk's way through the three roles (copy, flags, reduce, flags, copy) is
+// what the whole message waits for at the start; a small first chunk shortens it (measured: the
+// pipelined kernel took a constant ~60 us more than the zero-copy one with uniform 512 KB chunks).
+__host__ __device__ __forceinline__ void pipe_chunk_geom(uint32_t ch, uint64_t CE, uint32_t R, uint64_t* begin, uint64_t* size) {
+  if (ch < R) {
+    const uint64_t unit = CE >> R;
+    *begin = unit * ((uint64_t(1) << ch) - 1);
+    *size = unit << ch;
+  } else {
+    *begin = (CE >> R) * ((uint64_t(1) << R) - 1) + uint64_t(ch - R) * CE;
+    *size = CE;
+  }
+}
+__host__ __device__ __forceinline__ uint32_t pipe_chunk_count(uint64_t count, uint64_t CE, uint32_t R) {
+  uint32_t n = 0;
+  uint64_t begin = 0, size = 0;
+  for (; n < R; ++n) {
+    pipe_chunk_geom(n, CE, R, &begin, &size);
+    if (begin >= count) return n;
+  }
+  pipe_chunk_geom(R, CE, R, &begin, &size);
+  if (begin >= count) return R;
+  return R + static_cast<uint32_t>((count - begin + CE - 1) / CE);
+}
+
 template <int NVLS>
 __device__ __forceinline__ void pipe_roles(int nblk, int& n_in, int& n_red) {
   // switch path: the reduction needs fewer blocks than peer-to-peer loads and stores
@@ -536,7 +609,8 @@ __device__ __forceinline__ void pipe_body(const KParams& P, int blk, int nblk, B
     const uint32_t base = pc->base;  // written only by the last block of a call, after everyone read it
     const uint64_t E = a.shard_elems;
     const uint64_t CE = E * uint64_t(N);              // elements per chunk
-    const uint32_t nchunks = static_cast<uint32_t>((a.count + CE - 1) / CE);
+    const uint32_t ramp = static_cast<uint32_t>(a.pipe_ramp);
+    const uint32_t nchunks = pipe_chunk_count(a.count, CE, ramp);
     const uint64_t stride = c.stage_bytes / kPipeSlots;  // bytes per slot in both staging areas
     constexpr size_t kOffIn = offsetof(PipeCtl, in_ready), kOffRed = offsetof(PipeCtl, red_done),
                      kOffOut = offsetof(PipeCtl, out_done);
@@ -602,16 +676,19 @@ __device__ __forceinline__ void pipe_body(const KParams& P, int blk, int nblk, B
         const uint32_t ch = rb + i * nrb;
         const uint32_t g = base + ch;
         const int slot = static_cast<int>(g % kPipeSlots);
+        uint64_t cb, cs;                 // first element and length of this chunk
+        pipe_chunk_geom(ch, CE, ramp, &cb, &cs);
+        const uint64_t Ec = cs / uint64_t(N);  // shard length inside this chunk (a multiple of the vector width)
         if (role == 0) {
           // -------------------------------------------------------------- copy-in
-          const uint64_t e_begin = uint64_t(ch) * CE;
-          const uint64_t e_end = (e_begin + CE < a.count) ? e_begin + CE : a.count;
+          const uint64_t e_begin = cb;
+          const uint64_t e_end = (e_begin + cs < a.count) ? e_begin + cs : a.count;
           const uint64_t nvec = (e_end - e_begin + VW - 1) / VW;
           char* dst = my_a + uint64_t(slot) * stride;
           const uint64_t full = (e_end - e_begin) / VW;  // vectors that lie wholly inside the chunk
           // peer-to-peer path: vectors [own_lo, own_hi) are my own shard, which is not staged
-          const uint64_t own_lo = NVLS ? nvec : uint64_t(me) * (E / VW);
-          const uint64_t own_hi = NVLS ? nvec : own_lo + E / VW;
+          const uint64_t own_lo = NVLS ? nvec : uint64_t(me) * (Ec / VW);
+          const uint64_t own_hi = NVLS ? nvec : own_lo + Ec / VW;
           for (uint64_t v0 = wt; v0 < nvec; v0 += ctile) {
             if (v0 >= own_lo && v0 + uint64_t(UC - 1) * nwork < own_hi) continue;  // the whole step lies in my shard
             if (NVLS && kSameIn && in_al && v0 + uint64_t(UC - 1) * nwork < full) {
@@ -655,12 +732,12 @@ __device__ __forceinline__ void pipe_body(const KParams& P, int blk, int nblk, B
           }
         } else if (role == 1) {
           // -------------------------------------------------------------- reduce my shard
-          const uint64_t e_begin = uint64_t(ch) * CE + uint64_t(me) * E;  // my shard of this chunk
-          uint64_t e_end = e_begin + E;
+          const uint64_t e_begin = cb + uint64_t(me) * Ec;  // my shard of this chunk
+          uint64_t e_end = e_begin + Ec;
           if (e_end > a.count) e_end = a.count;
           const uint64_t nvec = e_begin < e_end ? (e_end - e_begin + VW - 1) / VW : 0;
-          const uint64_t in_off = uint64_t(slot) * stride + uint64_t(me) * E * sizeof(WRaw);
-          const uint64_t out_off = uint64_t(slot) * stride + uint64_t(me) * E * sizeof(ORaw);
+          const uint64_t in_off = uint64_t(slot) * stride + uint64_t(me) * Ec * sizeof(WRaw);
+          const uint64_t out_off = uint64_t(slot) * stride + uint64_t(me) * Ec * sizeof(ORaw);
           for (uint64_t v0 = wt; v0 < nvec; v0 += tile) {
             Acc acc[U][VW];
             if constexpr (NVLS) {
@@ -745,13 +822,13 @@ __device__ __forceinline__ void pipe_body(const KParams& P, int blk, int nblk, B
           }
         } else {
           // -------------------------------------------------------------- copy-out
-          const uint64_t e_begin = uint64_t(ch) * CE;
-          const uint64_t e_end = (e_begin + CE < a.count) ? e_begin + CE : a.count;
+          const uint64_t e_begin = cb;
+          const uint64_t e_end = (e_begin + cs < a.count) ? e_begin + cs : a.count;
           const uint64_t nvec = (e_end - e_begin + VW - 1) / VW;
           const char* src = my_b + uint64_t(slot) * stride;
           const uint64_t full = (e_end - e_begin) / VW;
-          const uint64_t own_lo = NVLS ? nvec : uint64_t(me) * (E / VW);  // my shard is already in recv (peer-to-peer path)
-          const uint64_t own_hi = NVLS ? nvec : own_lo + E / VW;
+          const uint64_t own_lo = NVLS ? nvec : uint64_t(me) * (Ec / VW);  // my shard is already in recv (peer-to-peer path)
+          const uint64_t own_hi = NVLS ? nvec : own_lo + Ec / VW;
           for (uint64_t v0 = wt; v0 < nvec; v0 += ctile) {
             if (v0 >= own_lo && v0 + uint64_t(UC - 1) * nwork < own_hi) continue;
             if (out_al && v0 + uint64_t(UC - 1) * nwork < full) {

@@ -35,7 +35,7 @@ enum DevStatus : uint32_t {
 
 struct LocalState {
   uint32_t epoch[kMaxBlocks];    // per-block barrier epoch (monotonic)
-  uint32_t ll_seq[kMaxBlocks];   // per-block LL sequence (flag value source)
+  uint32_t ll_seq[kMaxBlocks];   // word 0: the communicator's LL sequence (flag value source); the rest is unused
   uint32_t ticket;               // blocks finished in the running kernel
   uint32_t started;              // collectives started on this rank
   uint32_t done;                 // collectives finished on this rank
@@ -88,6 +88,7 @@ struct CollArgs {
   char* out_mc;
   int32_t copy_in;           // 1: inputs are first staged from `send`
   int32_t copy_out;          // 1: outputs are copied from stage_b to `recv`
+  int32_t pipe_ramp;         // pipelined kernel: number of small first chunks (CE / 2^R ... CE / 2), see pipe_chunk_geom
 };
 
 struct KParams {

@@ -115,7 +115,11 @@ __device__ __forceinline__ void block_begin(const CommDev& c, int blk, BlockCtl&
   if (threadIdx.x == 0) {
     LocalState* ls = local_state(c);
     ctl.epoch = ls->epoch[blk];
-    ctl.ll_seq = ls->ll_seq[blk];
+    // ONE LL sequence per communicator (word 0), read by every block: inbox slots are addressed by unit
+    // offset, not by block, so a per-block sequence would go wrong as soon as two LL calls split their
+    // units over a different number of blocks (a block could meet a stale packet carrying the very
+    // flag it waits for).
+    ctl.ll_seq = ls->ll_seq[0];
     ctl.fail = 0;
     for (int i = 0; i < 4; ++i) ctl.pipe_done[i] = 0;
     ctl.pipe_ready = 0;
@@ -135,11 +139,11 @@ __device__ __forceinline__ void block_end(const CommDev& c, int blk, int nblk, B
   if (threadIdx.x == 0) {
     LocalState* ls = local_state(c);
     ls->epoch[blk] = ctl.epoch;
-    ls->ll_seq[blk] = ctl.ll_seq;
     __threadfence();
     uint32_t t = atomicAdd(&ls->ticket, 1u);
     if (t == static_cast<uint32_t>(nblk - 1)) {
       ls->ticket = 0;
+      ls->ll_seq[0] = ctl.ll_seq;  // every block of an LL kernel holds the same new value; others leave it unchanged
       uint32_t d = ls->done + 1;
       ls->done = d;
       if (c.host_progress) st_volatile_u32(c.host_progress + 1, d);

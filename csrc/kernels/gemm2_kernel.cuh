@@ -70,7 +70,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     epi.comm_cta(g, s_epoch, static_cast<int>(blockIdx.x) - n_gemm, static_cast<int>(gridDim.x) - n_gemm, &s_abort, smem, base);
     __syncthreads();
     if (threadIdx.x == 0) {
-      if (s_abort != 0u && g.err != nullptr) atomicCAS(g.err, 0u, s_abort);
+      report_failure(g, s_abort);
       finish_epoch(g, s_epoch);
     }
     return;
@@ -93,6 +93,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     }
     ctl->abort = 0;
     ctl->epoch = g.epoch_ptr ? *g.epoch_ptr + 1u : 1u;
+    fused_kernel_started(g);
     fence_barrier_init();
     fence_proxy_async();
   }
@@ -138,8 +139,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             const uint64_t t0 = globaltimer_ns();
             uint32_t spins = 0;
             while (static_cast<int32_t>(ld_acquire_sys_u32(g.a_ready + c) - target) < 0) {
-              if ((++spins & 255u) == 0u && (ctl->abort != 0u || globaltimer_ns() - t0 > budget)) {
-                ctl->abort = 2u;
+              if ((++spins & 255u) == 0u && (comm_aborted(g) || ctl->abort != 0u || globaltimer_ns() - t0 > budget)) {
+                if (ctl->abort == 0u) ctl->abort = comm_aborted(g) ? kGemmAborted : kGemmRowsTimeout;
                 ok = false;
                 break;
               }
@@ -230,7 +231,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     tmem_dealloc_pair(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0) {
-    if (ctl->abort != 0u && g.err != nullptr) atomicCAS(g.err, 0u, ctl->abort);
+    report_failure(g, ctl->abort);
     finish_epoch(g, epoch);
   }
 }

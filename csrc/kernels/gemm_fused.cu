@@ -25,7 +25,9 @@
 // are what "AllReduce fused with the adjacent compute" means for this library.
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 
+#include "kernels/comm_dev.h"
 #include "kernels/gemm2_kernel.cuh"
 #include "kernels/gemm_kernel.cuh"
 
@@ -47,17 +49,24 @@ __device__ __forceinline__ void epilogue_warps_sync() {
   asm volatile("bar.sync 1, 128;" ::: "memory");
 }
 
-// Bounded wait for *p >= target (wrap-safe) with system-scope acquire.
+// Bounded wait for *p >= target (wrap-safe) with system-scope acquire.  Gives up when the budget runs
+// out, when another role of the CTA has given up (*abort_flag) or when the communicator's abort word
+// is set (the watchdog of this or of another local rank tripped): the kernel then winds down and the
+// failure reaches the communicator through report_failure().
 __device__ __forceinline__ bool wait_flag_sys(const uint32_t* p, uint32_t target, volatile uint32_t* abort_flag,
-                                              uint64_t budget_ns) {
+                                              const GemmArgs& g) {
   if (static_cast<int32_t>(ld_acquire_sys_u32(p) - target) >= 0) return true;
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {
     if (static_cast<int32_t>(ld_acquire_sys_u32(p) - target) >= 0) return true;
     if ((it & 255u) == 0u) {
       if (*abort_flag != 0u) return false;
-      if (globaltimer_ns() - t0 > budget_ns) {
-        *abort_flag = 3u;
+      if (comm_aborted(g)) {
+        *abort_flag = kGemmAborted;
+        return false;
+      }
+      if (globaltimer_ns() - t0 > g.wait_budget_ns) {
+        *abort_flag = kGemmFlagTimeout;
         return false;
       }
     }
@@ -177,8 +186,7 @@ struct RsEpilogue {
       const int ltm = tile / tiles_n, tn = tile - ltm * tiles_n;
       if (tile != last_tile) {
         if (tid < nranks) {
-          wait_flag_sys(flags[rank] + (static_cast<size_t>(tid) * tiles_m_local + ltm) * tiles_n + tn, epoch, abort_flag,
-                        g.wait_budget_ns);
+          wait_flag_sys(flags[rank] + (static_cast<size_t>(tid) * tiles_m_local + ltm) * tiles_n + tn, epoch, abort_flag, g);
         }
         epilogue_warps_sync();
         if (*abort_flag != 0u) return;
@@ -317,7 +325,7 @@ struct AgEpilogue {
     const int t = threadIdx.x;
     if (t < nranks && t != rank) {
       st_release_sys_u32(bar[t] + cta * nranks + rank, epoch);
-      wait_flag_sys(bar[rank] + cta * nranks + t, epoch, abort_flag, g.wait_budget_ns);
+      wait_flag_sys(bar[rank] + cta * nranks + t, epoch, abort_flag, g);
     }
     if (t == 0) {
       for (int i = 0; i < kAgSlots; ++i) mbar_init(smem_u32(&s_full[i]), 1);
@@ -375,6 +383,24 @@ struct AgEpilogue {
 
 namespace {
 
+// What a fused kernel needs of a communicator: parsed from the bytes mncclCommDeviceHandle returns.
+struct CommBinding {
+  const volatile uint32_t* abort_word = nullptr;
+  volatile uint32_t* progress = nullptr;
+  uint64_t budget_ns = 2000000000ull;   // without a communicator: two seconds per wait
+};
+
+CommBinding bind_comm(const void* handle, size_t bytes) {
+  CommBinding b;
+  if (handle == nullptr || bytes < sizeof(CommDev)) return b;
+  CommDev d;
+  memcpy(&d, handle, sizeof(d));
+  b.abort_word = d.abort_word;
+  b.progress = d.host_progress;
+  if (d.spin_timeout_ns != 0) b.budget_ns = d.spin_timeout_ns;
+  return b;
+}
+
 bool check_common(int M, int N, int K, int rank, int nranks, const char* who) {
   if (M <= 0 || N <= 0 || K <= 0 || nranks < 1 || nranks > kMaxTpRanks || rank < 0 || rank >= nranks) {
     fprintf(stderr, "[Mini-NCCL] %s: bad shape or rank\n", who);
@@ -411,9 +437,9 @@ MNCCL_EXPORT size_t mncclAgGemmBarWords(int nranks, int n_comm) { return size_t(
 // out[M/nranks, N] (rows of this rank) = sum over ranks of A_r[M, K] * B_r[N, K]^T, bf16.
 // stage_peers / flag_peers: the staging / flag buffers of EVERY rank as mapped here
 // (Communicator.peer_pointers); state: two zero-initialised device words of this rank.
-MNCCL_EXPORT int mncclGemmReduceScatterBf16(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb,
-                                            int ldo, int rank, int nranks, void* const* stage_peers,
-                                            void* const* flag_peers, uint32_t* state, cudaStream_t stream) {
+static int gemm_rs_launch(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldo, int rank,
+                          int nranks, void* const* stage_peers, void* const* flag_peers, uint32_t* state,
+                          const CommBinding& cb, cudaStream_t stream) {
   if (!A || !B || !out || !stage_peers || !flag_peers || !state) return -1;
   if (!check_common(M, N, K, rank, nranks, "GEMM->reduce-scatter")) return -2;
   if (lda == 0) lda = K;
@@ -453,7 +479,9 @@ MNCCL_EXPORT int mncclGemmReduceScatterBf16(const void* A, const void* B, void* 
   g.N = N;
   g.K = K;
   g.err = error_word();
-  g.wait_budget_ns = 2000000000ull;
+  g.wait_budget_ns = cb.budget_ns;
+  g.comm_abort = cb.abort_word;
+  g.comm_progress = cb.progress;
   const int tiles_m_local = epi.rows_per_rank / kBM;
   g.group_m = tiles_m_local;
   g.m_tile_rotate = ((rank + 1) % nranks) * tiles_m_local;  // next rank's rows first, own rows last
@@ -471,6 +499,24 @@ MNCCL_EXPORT int mncclGemmReduceScatterBf16(const void* A, const void* B, void* 
   return e == cudaSuccess ? 0 : static_cast<int>(e) + 1000;
 }
 
+MNCCL_EXPORT int mncclGemmReduceScatterBf16(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb,
+                                            int ldo, int rank, int nranks, void* const* stage_peers,
+                                            void* const* flag_peers, uint32_t* state, cudaStream_t stream) {
+  return gemm_rs_launch(A, B, out, M, N, K, lda, ldb, ldo, rank, nranks, stage_peers, flag_peers, state, CommBinding(), stream);
+}
+
+// The same under a communicator's failure model: `comm_handle` are the bytes mncclCommDeviceHandle
+// returns.  Every wait on a peer then polls the communicator's abort word and takes its budget from
+// MINI_NCCL_WATCHDOG_TIMEOUT_MS; the watchdog times the kernel like a collective; a wait that gives up
+// is reported to the communicator, which fails for good (mncclCommGetAsyncError, every later call).
+MNCCL_EXPORT int mncclGemmReduceScatterBf16Comm(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb,
+                                                int ldo, int rank, int nranks, void* const* stage_peers,
+                                                void* const* flag_peers, uint32_t* state, const void* comm_handle,
+                                                size_t comm_handle_bytes, cudaStream_t stream) {
+  return gemm_rs_launch(A, B, out, M, N, K, lda, ldb, ldo, rank, nranks, stage_peers, flag_peers, state,
+                        bind_comm(comm_handle, comm_handle_bytes), stream);
+}
+
 // C[M, N] = X[M, K] * B[N, K]^T where X is the row-wise concatenation of every rank's shard.
 // xg_peers: the gather buffer [M, K] of EVERY rank as mapped here; this rank's shard must
 // already be at rows [rank * M/nranks, ...) of its own buffer.  ready_peers / bar_peers: counter
@@ -478,7 +524,7 @@ MNCCL_EXPORT int mncclGemmReduceScatterBf16(const void* A, const void* B, void* 
 // n_comm_ctas CTAs of the grid move data instead of computing (0 = default).
 static int ag_gemm_launch(void* const* xg_peers, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                           int rank, int nranks, void* const* ready_peers, void* const* bar_peers, uint32_t* state,
-                          int n_comm_ctas, bool swiglu, cudaStream_t stream) {
+                          int n_comm_ctas, bool swiglu, const CommBinding& cb, cudaStream_t stream) {
   if (!xg_peers || !B || !C || !state) return -1;
   if (!check_common(M, N, K, rank, nranks, "all-gather->GEMM")) return -2;
   if (swiglu && (N % 32 != 0 || (ldc != 0 && ldc % 8 != 0) || (reinterpret_cast<uintptr_t>(C) & 15u) != 0)) {
@@ -542,7 +588,9 @@ static int ag_gemm_launch(void* const* xg_peers, const void* B, void* C, int M, 
   g.c = C;
   g.ldc = ldc;
   g.err = error_word();
-  g.wait_budget_ns = 2000000000ull;
+  g.wait_budget_ns = cb.budget_ns;
+  g.comm_abort = cb.abort_word;
+  g.comm_progress = cb.progress;
   const int tiles_m_local = epi.rows_per_rank / kBM;
   g.group_m = tiles_m_local;
   g.m_tile_rotate = rank * tiles_m_local;  // local rows first, then the shards in arrival order
@@ -570,7 +618,7 @@ MNCCL_EXPORT int mncclAllGatherGemmBf16(void* const* xg_peers, const void* B, vo
                                         int ldc, int rank, int nranks, void* const* ready_peers, void* const* bar_peers,
                                         uint32_t* state, int n_comm_ctas, cudaStream_t stream) {
   return ag_gemm_launch(xg_peers, B, C, M, N, K, lda, ldb, ldc, rank, nranks, ready_peers, bar_peers, state, n_comm_ctas, false,
-                        stream);
+                        CommBinding(), stream);
 }
 
 // The same with SwiGLU applied in the epilogue: act[M, N / 2] = silu(gate) * up, where B's rows are
@@ -580,7 +628,63 @@ MNCCL_EXPORT int mncclAllGatherGemmSwiGluBf16(void* const* xg_peers, const void*
                                               int ldb, int ldc, int rank, int nranks, void* const* ready_peers,
                                               void* const* bar_peers, uint32_t* state, int n_comm_ctas, cudaStream_t stream) {
   return ag_gemm_launch(xg_peers, B, act, M, N, K, lda, ldb, ldc, rank, nranks, ready_peers, bar_peers, state, n_comm_ctas, true,
-                        stream);
+                        CommBinding(), stream);
+}
+
+// all-gather -> GEMM (swiglu = 0) or all-gather -> GEMM with SwiGLU (swiglu = 1) under a communicator's
+// failure model; see mncclGemmReduceScatterBf16Comm.
+MNCCL_EXPORT int mncclAllGatherGemmBf16Comm(void* const* xg_peers, const void* B, void* C, int M, int N, int K, int lda, int ldb,
+                                            int ldc, int rank, int nranks, void* const* ready_peers, void* const* bar_peers,
+                                            uint32_t* state, int n_comm_ctas, int swiglu, const void* comm_handle,
+                                            size_t comm_handle_bytes, cudaStream_t stream) {
+  return ag_gemm_launch(xg_peers, B, C, M, N, K, lda, ldb, ldc, rank, nranks, ready_peers, bar_peers, state, n_comm_ctas,
+                        swiglu != 0, bind_comm(comm_handle, comm_handle_bytes), stream);
+}
+
+// One thread waits (bounded by budget_ns) for a flag that nothing sets, the way the fused kernels wait
+// for a peer, and reports like they do.  abort_first: an abort word is pre-set, so the wait must
+// return at once.  status: the GemmAbort code the wait left; words[4]: what reached the stand-in
+// progress words {status, detail, started, done}.  Host-made failure for tests: nothing faults.
+__global__ void flag_wait_probe(GemmArgs g, uint32_t* flag, uint32_t* out) {
+  __shared__ volatile uint32_t s_abort;
+  s_abort = 0;
+  fused_kernel_started(g);
+  const uint64_t t0 = globaltimer_ns();
+  wait_flag_sys(flag, 1u, &s_abort, g);
+  out[0] = s_abort;
+  out[1] = static_cast<uint32_t>((globaltimer_ns() - t0) / 1000ull);
+  report_failure(g, s_abort);
+}
+
+MNCCL_EXPORT int mncclGemmProbeFlagWait(uint64_t budget_ns, int abort_first, uint32_t* status, uint32_t* waited_us,
+                                        uint32_t* words) {
+  uint32_t* buf = nullptr;  // [0] flag, [1] abort, [2..3] out, [4..7] err words, [8..15] progress stand-in
+  if (cudaMalloc(&buf, 64) != cudaSuccess) return -2;
+  cudaMemset(buf, 0, 64);
+  if (abort_first) {
+    const uint32_t one = 1;
+    cudaMemcpy(buf + 1, &one, 4, cudaMemcpyHostToDevice);
+  }
+  GemmArgs g{};
+  g.err = buf + 4;
+  g.wait_budget_ns = budget_ns;
+  g.comm_abort = buf + 1;
+  g.comm_progress = buf + 8;
+  flag_wait_probe<<<1, 1>>>(g, buf, buf + 2);
+  uint32_t host[16] = {0};
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpy(host, buf, 64, cudaMemcpyDeviceToHost);
+  cudaFree(buf);
+  if (e != cudaSuccess) return static_cast<int>(e) + 1000;
+  if (status) *status = host[2];
+  if (waited_us) *waited_us = host[3];
+  if (words) {
+    words[0] = host[10];  // status
+    words[1] = host[11];  // detail
+    words[2] = host[12];  // started
+    words[3] = host[13];  // done (the probe never finishes an epoch: stays 0)
+  }
+  return 0;
 }
 
 }  // extern "C"

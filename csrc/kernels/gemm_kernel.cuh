@@ -21,6 +21,30 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
   return v;
 }
 
+// Words of the per-device error buffer (error_word()): [0] first failed wait, [1] fused kernels
+// started, [2] fused kernels finished (device-resident counters behind the watchdog's view).
+__device__ __forceinline__ void st_volatile_sys_u32(volatile uint32_t* p, uint32_t v) {
+  asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// First CTA in: a fused kernel is in flight (what the communicator's watchdog times).
+__device__ __forceinline__ void fused_kernel_started(const GemmArgs& g) {
+  if (g.comm_progress == nullptr || g.err == nullptr || blockIdx.x != 0) return;
+  const uint32_t s = atomicAdd(g.err + 1, 1u) + 1u;
+  st_volatile_sys_u32(g.comm_progress + 4, s);
+}
+
+// A CTA's waits gave up with `code` (GemmAbort): device error word, and the communicator's status
+// words, which make the watchdog set the abort word and the communicator fail for good.
+__device__ __forceinline__ void report_failure(const GemmArgs& g, uint32_t code) {
+  if (code == 0u || g.err == nullptr) return;
+  if (atomicCAS(g.err, 0u, code) == 0u && g.comm_progress != nullptr) {
+    st_volatile_sys_u32(g.comm_progress + 3, (static_cast<uint32_t>(blockIdx.x) << 16) | 0x8000u | code);
+    __threadfence_system();
+    st_volatile_sys_u32(g.comm_progress + 2, code == kGemmAborted ? 2u /*kDevAborted*/ : 1u /*kDevTimeout*/);
+  }
+}
+
 // Last CTA out publishes the new epoch of a fused op (see GemmArgs::epoch_ptr).
 __device__ __forceinline__ void finish_epoch(const GemmArgs& g, uint32_t epoch) {
   if (g.epoch_ptr == nullptr) return;
@@ -30,8 +54,15 @@ __device__ __forceinline__ void finish_epoch(const GemmArgs& g, uint32_t epoch) 
     *g.ticket_ptr = 0;
     *g.epoch_ptr = epoch;
     __threadfence();
+    if (g.comm_progress != nullptr && g.err != nullptr) {
+      const uint32_t d = atomicAdd(g.err + 2, 1u) + 1u;
+      st_volatile_sys_u32(g.comm_progress + 5, d);
+    }
   }
 }
+
+// True when the communicator's abort word is set (polled by every wait on a peer).
+__device__ __forceinline__ bool comm_aborted(const GemmArgs& g) { return g.comm_abort != nullptr && *g.comm_abort != 0u; }
 
 struct __align__(8) SharedCtl {
   uint64_t full[kStages];
@@ -69,12 +100,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     if (threadIdx.x == 0) {
       s_epoch = g.epoch_ptr ? *g.epoch_ptr + 1u : 1u;
       s_abort = 0;
+      fused_kernel_started(g);
     }
     __syncthreads();
     epi.comm_cta(g, s_epoch, static_cast<int>(blockIdx.x) - n_gemm, static_cast<int>(gridDim.x) - n_gemm, &s_abort, smem, base);
     __syncthreads();
     if (threadIdx.x == 0) {
-      if (s_abort != 0u && g.err != nullptr) atomicCAS(g.err, 0u, s_abort);
+      report_failure(g, s_abort);
       finish_epoch(g, s_epoch);
     }
     return;
@@ -96,6 +128,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
     ctl->abort = 0;
     ctl->epoch = g.epoch_ptr ? *g.epoch_ptr + 1u : 1u;
+    fused_kernel_started(g);
     fence_barrier_init();
     fence_proxy_async();
   }
@@ -134,10 +167,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             const uint64_t t0 = globaltimer_ns();
             uint32_t spins = 0;
             while (static_cast<int32_t>(ld_acquire_sys_u32(g.a_ready + c) - target) < 0) {
-              if ((++spins & 255u) == 0u && (ctl->abort != 0u || globaltimer_ns() - t0 > budget)) {
-                ctl->abort = 2u;
-                ok = false;
-                break;
+              if ((++spins & 255u) == 0u) {
+                const bool aborted = comm_aborted(g);
+                if (aborted || ctl->abort != 0u || globaltimer_ns() - t0 > budget) {
+                  if (ctl->abort == 0u) ctl->abort = aborted ? kGemmAborted : kGemmRowsTimeout;
+                  ok = false;
+                  break;
+                }
               }
             }
           }
@@ -236,7 +272,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     tmem_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0) {
-    if (ctl->abort != 0u && g.err != nullptr) atomicCAS(g.err, 0u, ctl->abort);
+    report_failure(g, ctl->abort);
     finish_epoch(g, epoch);
   }
 }

@@ -48,7 +48,15 @@ struct GemmArgs {
   // and its last CTA (ticket) stores it back, so a captured launch replays correctly.
   uint32_t* epoch_ptr;
   uint32_t* ticket_ptr;
+  // The communicator's failure model (null for the plain GEMM): its host-mapped abort word, which
+  // every wait on a peer polls, and its host-mapped progress words {.., status, detail, started, done}
+  // at indices 2..5, through which a failed wait and the kernel's start / end reach the watchdog.
+  const volatile uint32_t* comm_abort;
+  volatile uint32_t* comm_progress;
 };
+
+// Codes a CTA leaves in its shared abort flag (and the device error word).
+enum GemmAbort : uint32_t { kGemmOk = 0, kGemmMbarTimeout = 1, kGemmRowsTimeout = 2, kGemmFlagTimeout = 3, kGemmAborted = 4 };
 
 // Tile index -> (tm, tn).  m-tiles are visited in groups of `group_m` so that a
 // wave of CTAs reuses the same B tiles from L2; `m_tile_rotate` rotates the

@@ -36,6 +36,18 @@ __global__ void __launch_bounds__(512) oneshot_kernel_emu(const KParams* table, 
 }
 
 template <typename InT, typename WireT, typename OutT, int OP>
+__global__ void __launch_bounds__(512) gather_reduce_kernel(const __grid_constant__ KParams P) {
+  gather_reduce_body<InT, WireT, OutT, OP>(P, blockIdx.x, gridDim.x);
+}
+template <typename InT, typename WireT, typename OutT, int OP>
+struct GatherReduceF {
+  static cudaError_t go(const LaunchCtx& x) {
+    if (x.vranks > 1 || x.occupancy_out) return kNoKernel;  // one rank per launch by construction
+    return fire(gather_reduce_kernel<InT, WireT, OutT, OP>, gather_reduce_kernel<InT, WireT, OutT, OP>, x);
+  }
+};
+
+template <typename InT, typename WireT, typename OutT, int OP>
 struct LocalF {
   static cudaError_t go(const LaunchCtx& x) {
     if (OP != 0) return kNoKernel;
@@ -63,6 +75,7 @@ cudaError_t dispatch_local(const LaunchCtx& x) {
   y.spec = &s;
   return dispatch_all<LocalF>(y);
 }
+cudaError_t dispatch_gather_reduce(const LaunchCtx& x) { return dispatch_all<GatherReduceF>(x); }
 cudaError_t dispatch_ll(const LaunchCtx& x) { return dispatch_all<LLF>(x); }
 cudaError_t dispatch_oneshot(const LaunchCtx& x) { return dispatch_all<OneShotF>(x); }
 

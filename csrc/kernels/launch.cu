@@ -13,6 +13,7 @@ cudaError_t dispatch_rs(const LaunchCtx&);
 cudaError_t dispatch_rs_nvls(const LaunchCtx&);
 cudaError_t dispatch_ag(const LaunchCtx&);
 cudaError_t dispatch_pipe(const LaunchCtx&);
+cudaError_t dispatch_gather_reduce(const LaunchCtx&);
 cudaError_t dispatch_pipe_nvls(const LaunchCtx&);
 }  // namespace dev
 
@@ -28,6 +29,7 @@ cudaError_t route(const dev::LaunchCtx& x) {
         case Algo::TwoShot: return dev::dispatch_twoshot_ar(x);
         case Algo::Nvls: return dev::dispatch_nvls_ar(x);
         case Algo::Pipe: return s.pipe_nvls ? dev::dispatch_pipe_nvls(x) : dev::dispatch_pipe(x);
+        case Algo::HostSync: return dev::dispatch_gather_reduce(x);
         default: return dev::kNoKernel;
       }
     case Mode::ReduceScatter:
@@ -49,7 +51,7 @@ bool kernel_exists(const LaunchSpec& spec) {
 
 cudaError_t launch_collective(const LaunchSpec& spec, const KParams& p, cudaStream_t stream) {
   // Only kernels with per-block barrier state are bound by kMaxBlocks.
-  const int max_blocks = spec.algo == Algo::Local ? 65535 : kMaxBlocks;
+  const int max_blocks = (spec.algo == Algo::Local || spec.algo == Algo::HostSync) ? 65535 : kMaxBlocks;
   if (spec.nblocks < 1 || spec.nblocks > max_blocks || spec.nthreads < 32 || spec.nthreads > 512)
     return cudaErrorInvalidConfiguration;
   dev::LaunchCtx x{&spec, &p, nullptr, 1, stream, nullptr};

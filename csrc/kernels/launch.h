@@ -7,14 +7,14 @@
 
 namespace mnccl {
 
-enum class Algo : int { Auto = 0, LL = 1, OneShot = 2, TwoShot = 3, Nvls = 4, Ring = 5, Local = 6, Pipe = 7 };
+enum class Algo : int { Auto = 0, LL = 1, OneShot = 2, TwoShot = 3, Nvls = 4, Ring = 5, Local = 6, Pipe = 7, HostSync = 8 };
 enum class Mode : int { AllReduce = 0, ReduceScatter = 1, AllGather = 2 };
 
 inline const char* algo_name(Algo a) {
   switch (a) {
     case Algo::Auto: return "auto"; case Algo::LL: return "ll"; case Algo::OneShot: return "oneshot";
     case Algo::TwoShot: return "twoshot"; case Algo::Nvls: return "nvls"; case Algo::Ring: return "ring";
-    case Algo::Local: return "local"; case Algo::Pipe: return "pipe";
+    case Algo::Local: return "local"; case Algo::Pipe: return "pipe"; case Algo::HostSync: return "hostsync";
   }
   return "?";
 }

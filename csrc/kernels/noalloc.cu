@@ -6,6 +6,7 @@
 
 #include <cuda_runtime.h>
 
+#include <cstddef>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -85,6 +86,45 @@ extern "C" {
 #define MNCCL_EXPORT __attribute__((visibility("default")))
 
 MNCCL_EXPORT size_t mncclNoAllocScratchBytes(void) { return kScratchBytes; }
+
+// What the last call on the current device left in the static scratch: 0 when every wait of its
+// kernel completed, else the status of the first wait that gave up (1 = ran out of its two seconds,
+// 2 = aborted) with, in *detail, (block << 16) | virtual rank waited for.  A kernel whose wait gave up
+// returns early, so the output of that call is incomplete although the call itself returned
+// ncclSuccess: callers that must know ask here.  Synchronises `stream` and copies eight bytes per
+// virtual rank out of the scratch; allocates nothing.  The next call's clearing erases the record.
+MNCCL_EXPORT ncclResult_t mncclNoAllocLastStatus(cudaStream_t stream, unsigned* status, unsigned* detail) {
+  if (!status) return ncclInvalidArgument;
+  unsigned char* scratch = nullptr;
+  cudaError_t e = scratch_for_current_device(&scratch);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  *status = 0;
+  if (detail) *detail = 0;
+  for (int r = 0; r < kNoAllocMaxRanks && e == cudaSuccess; ++r) {
+    unsigned words[2] = {0, 0};
+    e = cudaMemcpy(words, scratch + size_t(r) * kCtrlBytes + kSigBytes + offsetof(LocalState, status), sizeof(words),
+                   cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && words[0] != 0 && *status == 0) {
+      *status = words[0];
+      if (detail) *detail = words[1];
+    }
+  }
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return ncclUnhandledCudaError;
+  }
+  return ncclSuccess;
+}
+
+// Fills the control part (barrier words, per-rank state) of every virtual rank's scratch with `byte`, as
+// a call that was cut short might leave it; the next call must not care.  For the test-suite.
+MNCCL_EXPORT int mncclNoAllocDirtyControlForTest(int byte) {
+  unsigned char* scratch = nullptr;
+  if (scratch_for_current_device(&scratch) != cudaSuccess) return 1;
+  for (int r = 0; r < kNoAllocMaxRanks; ++r)
+    if (cudaMemset(scratch + size_t(r) * kCtrlBytes, byte, kClearBytes) != cudaSuccess) return 2;
+  return cudaDeviceSynchronize() == cudaSuccess ? 0 : 3;
+}
 
 MNCCL_EXPORT ncclResult_t mncclLocalAllReduceNoAlloc(const void* const* send, void* const* recv, int nbuffers,
                                                      size_t count, ncclDataType_t datatype, ncclRedOp_t op,

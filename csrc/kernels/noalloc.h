@@ -56,6 +56,13 @@ ncclResult_t mncclLocalAllReduceNoAlloc(const void* const* send, void* const* re
 /* Size in bytes of the static scratch array (per GPU). */
 size_t mncclNoAllocScratchBytes(void);
 
+/* Outcome of the last call on the current device: *status 0 when every wait inside its kernel completed,
+ * 1 when one ran out of its two-second budget, 2 when it was aborted; *detail (may be NULL) names the
+ * block and the virtual rank that was waited for.  A call whose kernel gave up returns ncclSuccess all
+ * the same and leaves its output incomplete, so a caller that cannot tolerate that asks here.
+ * Synchronises `stream`, reads a few bytes of the scratch, allocates nothing. */
+ncclResult_t mncclNoAllocLastStatus(cudaStream_t stream, unsigned* status, unsigned* detail);
+
 #ifdef __cplusplus
 }
 #endif

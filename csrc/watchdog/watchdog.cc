@@ -24,6 +24,9 @@ void Watchdog::step(std::chrono::steady_clock::time_point now) {
   const uint32_t started = __atomic_load_n(progress_ + 0, __ATOMIC_ACQUIRE);
   const uint32_t done = __atomic_load_n(progress_ + 1, __ATOMIC_ACQUIRE);
   const uint32_t status = __atomic_load_n(progress_ + 2, __ATOMIC_ACQUIRE);
+  // kernels that fuse a GEMM with a collective count themselves in words 4 and 5
+  const uint32_t fused_started = __atomic_load_n(progress_ + 4, __ATOMIC_ACQUIRE);
+  const uint32_t fused_done = __atomic_load_n(progress_ + 5, __ATOMIC_ACQUIRE);
   if (__atomic_load_n(abort_, __ATOMIC_ACQUIRE) != 0 && !saw_abort_.exchange(true)) {
     if (!tripped_.load()) stats_.remote_aborts++;
   }
@@ -37,15 +40,16 @@ void Watchdog::step(std::chrono::steady_clock::time_point now) {
     if (on_trip_) on_trip_(status);
     return;
   }
-  const bool busy = started != done;
+  const bool busy = started != done || fused_started != fused_done;
+  const uint32_t finished = done + fused_done;  // any kernel finishing is progress
   if (!busy) {
     in_flight_ = false;
-    last_done_ = done;
+    last_done_ = finished;
     return;
   }
-  if (!in_flight_ || done != last_done_) {
+  if (!in_flight_ || finished != last_done_) {
     in_flight_ = true;
-    last_done_ = done;
+    last_done_ = finished;
     since_ = now;
     return;
   }

@@ -108,6 +108,10 @@ def lib() -> C.CDLL:
         sig("mncclGemmReduceScatterBf16", i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, P(vp), P(vp), vp, vp)
         sig("mncclAllGatherGemmBf16", i32, P(vp), vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, P(vp), P(vp), vp, i32, vp)
         sig("mncclAllGatherGemmSwiGluBf16", i32, P(vp), vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, P(vp), P(vp), vp, i32, vp)
+        sig("mncclGemmReduceScatterBf16Comm", i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, P(vp), P(vp), vp, C.c_char_p, sz, vp)
+        sig("mncclAllGatherGemmBf16Comm", i32, P(vp), vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, P(vp), P(vp), vp, i32, i32,
+            C.c_char_p, sz, vp)
+        sig("mncclGemmProbeFlagWait", i32, u64, i32, P(u32), P(u32), P(u32))
     # emulation + probes
     sig("mncclEmuCreate", i32, i32, sz, P(vp))
     sig("mncclEmuDestroy", i32, vp)

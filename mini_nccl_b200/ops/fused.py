@@ -7,6 +7,11 @@ the local shard to the peers while the others already compute on the local rows.
 
 Workspaces come from ``Communicator.empty`` (symmetric memory), so creating these objects is
 collective: every rank, same order, same shapes.  With one rank they run the same kernels locally.
+
+Both kernels run under the communicator's failure model: every wait on a peer polls the
+communicator's abort word and takes its budget from ``MINI_NCCL_WATCHDOG_TIMEOUT_MS``, the watchdog
+times the kernel like a collective, and a wait that gives up fails the communicator for good
+(``Communicator.async_error()``; every later call raises).
 """
 from __future__ import annotations
 
@@ -35,6 +40,15 @@ def _sym(comm, numel, dtype):
     return t
 
 
+def _check_comm(comm):
+    """A communicator that has failed (watchdog trip, a kernel's failed wait, abort) takes no more work."""
+    err = comm.async_error()
+    if err != 0:
+        from .._lib import MiniNcclError
+
+        raise MiniNcclError(err, "fused kernel on a failed communicator")
+
+
 def _peers(comm, tensor):
     if comm.size == 1:
         return (C.c_void_p * 1)(tensor.data_ptr())
@@ -59,6 +73,7 @@ class GemmReduceScatter:
             comm.barrier()
         self._stage_peers = _peers(comm, self.stage)
         self._flag_peers = _peers(comm, self.flags)
+        self._handle = comm.device_handle_bytes()
 
     def __call__(self, a, b, out=None, stream=None):
         """``a [M, K_r]``, ``b [N, K_r]`` bf16 -> ``out [M / ranks, N]`` bf16 (this rank's rows of the sum)."""
@@ -72,9 +87,11 @@ class GemmReduceScatter:
         if out is None:
             out = torch.empty((M // self.comm.size, N), dtype=torch.bfloat16, device=a.device)
         s = stream.cuda_stream if stream is not None else torch.cuda.current_stream().cuda_stream
-        rc = _native().mncclGemmReduceScatterBf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, a.shape[1], a.stride(0),
-                                                  b.stride(0), out.stride(0), self.comm.rank, self.comm.size,
-                                                  self._stage_peers, self._flag_peers, self.state.data_ptr(), s)
+        _check_comm(self.comm)
+        rc = _native().mncclGemmReduceScatterBf16Comm(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, a.shape[1], a.stride(0),
+                                                      b.stride(0), out.stride(0), self.comm.rank, self.comm.size,
+                                                      self._stage_peers, self._flag_peers, self.state.data_ptr(),
+                                                      self._handle, len(self._handle), s)
         if rc != 0:
             raise RuntimeError(f"mncclGemmReduceScatterBf16 failed with code {rc}")
         return out
@@ -99,6 +116,7 @@ class AllGatherGemm:
         self._xg = _peers(comm, self.gather)
         self._ready = _peers(comm, self.ready)
         self._bar = _peers(comm, self.bar)
+        self._handle = comm.device_handle_bytes()
 
     @property
     def local_shard(self):
@@ -124,9 +142,11 @@ class AllGatherGemm:
         if tuple(out.shape) != (self.M, n_out) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
             raise ValueError(f"out must be bf16 [{self.M}, {n_out}] with a unit inner stride")
         s = stream.cuda_stream if stream is not None else torch.cuda.current_stream().cuda_stream
-        fn = _native().mncclAllGatherGemmSwiGluBf16 if swiglu else _native().mncclAllGatherGemmBf16
-        rc = fn(self._xg, b.data_ptr(), out.data_ptr(), self.M, N, self.K, self.K, b.stride(0), out.stride(0), self.comm.rank,
-                self.comm.size, self._ready, self._bar, self.state.data_ptr(), self.n_comm, s)
+        _check_comm(self.comm)
+        rc = _native().mncclAllGatherGemmBf16Comm(self._xg, b.data_ptr(), out.data_ptr(), self.M, N, self.K, self.K, b.stride(0),
+                                                  out.stride(0), self.comm.rank, self.comm.size, self._ready, self._bar,
+                                                  self.state.data_ptr(), self.n_comm, 1 if swiglu else 0, self._handle,
+                                                  len(self._handle), s)
         if rc != 0:
             raise RuntimeError(f"all-gather->GEMM kernel failed with code {rc}")
         return out

@@ -6,9 +6,10 @@ real multi-process path on seeded random inputs (seed + rank), on symmetric and 
 buffers, fp32 and bf16, with one small and one large element count that the rank count does not
 divide, and compares with the rank-ordered host oracle:
 
-* peer-to-peer algorithms (LL, one-shot, two-shot, staged, pipelined): bit for bit;
-* NVLS (the switch defines the order of the sum): within a tolerance on random data, and bit for
-  bit on exactly representable data (small integers), where the order cannot matter;
+* peer-to-peer algorithms (LL, one-shot, two-shot, staged, the stream pipeline): bit for bit;
+* NVLS and the pipelined kernel where it reduces through the switch (the switch defines the order
+  of the sum): within a tolerance on random data, and bit for bit on exactly representable data
+  (small integers), where the order cannot matter;
 * the two fused GEMM kernels on a small shape: bit for bit on integer-valued operands (every
   product and sum is exact in fp32 whatever the tensor cores' order), within a tolerance on random
   operands.
@@ -80,7 +81,7 @@ def check_allreduce(comm, world: int, rank: int, small: int = 2051, large: int =
     for code in dtypes:
         dt = _torch_dt(code)
         esz = _lib.DTYPE_SIZES[code]
-        for count, algos in ((small, ("ll", "oneshot", "twoshot", "nvls")), (large * (4 // esz), ("twoshot", "nvls", "auto"))):
+        for count, algos in ((small, ("ll", "oneshot", "twoshot", "nvls")), (large * (4 // esz), ("twoshot", "nvls", "pipe", "auto"))):
             inputs = [O.make_input(code, count, r, dist="normal") for r in range(world)]
             want = O.oracle_allreduce(inputs, code, _lib.SUM, scale=scale)
             exact_in = [_exact_input(code, count, r) for r in range(world)]
@@ -91,8 +92,8 @@ def check_allreduce(comm, world: int, rank: int, small: int = 2051, large: int =
             plain_out = torch.empty(count, dtype=dt, device="cuda")
             for where, src, dst in (("symmetric", sym, sym), ("ordinary", plain, plain_out)):
                 for algo in algos:
-                    if algo == "auto" and where == "symmetric":
-                        continue  # same kernel as the forced ones
+                    if algo in ("auto", "pipe") and where == "symmetric":
+                        continue  # auto: same kernel as the forced ones; pipe: a kernel for ordinary buffers
                     before = comm.stats().get("algo", {})
                     _to_device(inputs[rank], code, src)
                     comm.all_reduce(src, "sum", out=dst, scale=scale, algo=algo)
@@ -100,7 +101,9 @@ def check_allreduce(comm, world: int, rank: int, small: int = 2051, large: int =
                     got = _to_host(dst, code)
                     after = comm.stats().get("algo", {})
                     used = [k for k in after if after[k] != before.get(k, 0)]
-                    switch = "nvls" in used
+                    # the pipelined kernel reduces through the switch too where the communicator has one
+                    # (more than two ranks): its sum is ordered by the switch, like the NVLS kernel's
+                    switch = "nvls" in used or ("pipe" in used and world > 2 and bool(comm.stats().get("nvls")))
                     name = "%s/%s/%s/%d" % (algo, where, O.DTYPE_NAMES[code], count)
                     res["algos"][name] = "+".join(used)
                     res["cases"] += 1

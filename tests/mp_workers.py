@@ -450,7 +450,106 @@ def gpu_tp(rank, n, kw):
     return {"rank": rank, "worst": worst, "oracle_cases": res["cases"]}
 
 
-FUNCS = {f.__name__: f for f in (cpu_ring, cpu_ring_fault, gpu_battery, gpu_stall, gpu_tp)}
+def gpu_tp_stall(rank, n, kw):
+    """GEMM -> reduce-scatter under the communicator's failure model: after two good steps the victim
+    stops launching (a stall made on the host, between steps, none of its kernels in flight); the other
+    ranks' kernels wait for its tiles, the watchdog sets the abort word after the configured bound, the
+    kernels return, the communicator reports an error and takes no more work."""
+    import torch
+
+    import mini_nccl_b200 as mn
+    from mini_nccl_b200.ops import GemmReduceScatter, gemm_status
+
+    torch.cuda.set_device(rank % torch.cuda.device_count())
+    comm = mn.Communicator(n, rank, "127.0.0.1")
+    M, N, K = 1024, 1024, 256
+    rs = GemmReduceScatter(comm, M, N)
+    g = torch.Generator(device="cuda").manual_seed(rank)
+    a = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    b = torch.randn(N, K, generator=g, device="cuda").to(torch.bfloat16)
+    for _ in range(2):
+        rs(a, b)
+    torch.cuda.synchronize()
+    comm.barrier()
+    t0 = time.time()
+    raised = 0
+    if rank == kw["victim"]:
+        while comm.async_error() in (0, 7) and time.time() - t0 < 60:  # learns of the failure on the host (shared abort page)
+            time.sleep(0.01)
+    else:
+        rs(a, b)                      # waits for the victim's tiles that never come
+        torch.cuda.synchronize()      # ... and returns within the bound
+    waited = time.time() - t0
+    err = comm.async_error()
+    try:
+        rs(a, b)
+    except mn.MiniNcclError as e:
+        raised = e.code
+    status = gemm_status()
+    stats = comm.stats()
+    comm.destroy()
+    return {"rank": rank, "async": err, "raised": raised, "waited": waited, "gemm_status": status, "stats": stats}
+
+
+def gpu_shared(rank, n, kw):
+    """Every rank on GPU 0 (the reference benchmark's layout): the host-synchronised plane.  Device and
+    pinned-host buffers, several types and operators, a message larger than the staging buffer, in
+    place and out of place, all bit for bit against the rank-ordered host oracle."""
+    import numpy as np
+    import torch
+
+    import mini_nccl_b200 as mn
+    from mini_nccl_b200 import _lib
+    from mini_nccl_b200.utils import oracle as O
+
+    torch.cuda.set_device(0)
+    comm = mn.Communicator(n, rank, "127.0.0.1")
+    stats0 = comm.stats()
+    cases = 0
+    tdt = {_lib.FLOAT32: torch.float32, _lib.BFLOAT16: torch.bfloat16, _lib.INT32: torch.int32, _lib.FLOAT64: torch.float64}
+    for code, op, opname, count in ((_lib.FLOAT32, _lib.SUM, "sum", 1 << 20), (_lib.FLOAT32, _lib.SUM, "sum", 5),
+                                    (_lib.BFLOAT16, _lib.SUM, "sum", (1 << 19) + 3), (_lib.INT32, _lib.MAX, "max", 70001),
+                                    (_lib.FLOAT64, _lib.PROD, "prod", 4099), (_lib.FLOAT32, _lib.AVG, "avg", 300001),
+                                    (_lib.FLOAT32, _lib.SUM, "sum", kw.get("big", (5 << 20) + 7))):
+        ins = [O.make_input(code, count, r, op=op) for r in range(n)]
+        want = O.oracle_allreduce(ins, code, op)
+        for where in ("device", "pinned"):
+            raw = torch.from_numpy(ins[rank].view(np.int16) if code == _lib.BFLOAT16 else ins[rank])
+            src = raw.view(tdt[code]) if code == _lib.BFLOAT16 else raw
+            if where == "device":
+                x = src.cuda()
+                y = torch.empty_like(x)
+            else:
+                x = src.clone().pin_memory()
+                y = torch.empty_like(x).pin_memory()
+            comm.all_reduce(x, opname, out=y)
+            torch.cuda.synchronize()
+            got = y.cpu()
+            got = got.view(torch.int16).numpy().view(np.uint16) if code == _lib.BFLOAT16 else got.numpy()
+            assert np.array_equal(got, want), f"{where} {O.DTYPE_NAMES[code]} {opname} {count}: {int(np.count_nonzero(got != want))} differ"
+            cases += 1
+        # in place on the device
+        x = (torch.from_numpy(ins[rank].view(np.int16)).view(torch.bfloat16) if code == _lib.BFLOAT16 else torch.from_numpy(ins[rank])).cuda()
+        comm.all_reduce(x, opname)
+        torch.cuda.synchronize()
+        got = x.cpu()
+        got = got.view(torch.int16).numpy().view(np.uint16) if code == _lib.BFLOAT16 else got.numpy()
+        assert np.array_equal(got, want)
+        cases += 1
+    # a rough rate on device buffers (host clock: the call is host-synchronous)
+    big = torch.ones(16 << 20, device="cuda")
+    comm.all_reduce(big, "sum")
+    t0 = time.time()
+    for _ in range(5):
+        comm.all_reduce(big, "sum")
+    dt = (time.time() - t0) / 5
+    stats = comm.stats()
+    comm.destroy()
+    return {"rank": rank, "cases": cases, "plane": stats0["plane"], "hostsync": stats["algo"].get("hostsync", 0),
+            "algbw_GBps": (64 << 20) / dt / 1e9}
+
+
+FUNCS = {f.__name__: f for f in (cpu_ring, cpu_ring_fault, gpu_battery, gpu_stall, gpu_tp, gpu_tp_stall, gpu_shared)}
 
 if __name__ == "__main__":
     fn, rank, n, kw = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), json.loads(sys.argv[4])

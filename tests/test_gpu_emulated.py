@@ -297,3 +297,14 @@ def test_pipe_kernel_few_blocks(worlds, lib):
             check_allreduce(w, 2 * 1024 * 1024 + 9, _lib.FLOAT32, _lib.SUM, ALGOS["pipe"], nblocks=nb, seed=nb)
     finally:
         lib.mncclEmuSetPipeChunk(w.h, 0)
+
+
+def test_ll_calls_with_changing_block_counts(worlds):
+    """LL inbox slots are addressed by unit offset, the flag comes from ONE sequence per communicator:
+    calls that split the same units over 1, 2, 3 ... blocks, with fresh data every time, must never
+    accept a packet of an earlier call."""
+    w = worlds(4, 0)
+    count = 3000                      # 12 KB fp32: a few blocks' worth of 8-byte units
+    for i, nb in enumerate([1, 2, 1, 3, 2, 4, 1, 4, 3, 1, 2, 2]):
+        check_allreduce(w, count, _lib.FLOAT32, _lib.SUM, ALGOS["ll"], nblocks=nb, seed=1000 + i)
+        assert w.last_plan() == ("ll", nb)

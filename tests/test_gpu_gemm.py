@@ -164,3 +164,24 @@ def test_all_gather_gemm_with_swiglu_in_the_epilogue(M, F, K):
         assert (u2.float() - ut).abs().max().item() / ut.abs().max().item() < 2e-2
     finally:
         comm.destroy()
+
+
+
+def test_fused_kernel_wait_is_bounded_and_reports_to_the_communicator():
+    """The wait the fused kernels use for a peer, on a flag that nothing sets: it gives up after its
+    budget (or at once when the abort word is set), and the failure reaches the communicator's status
+    words, from where the watchdog fails the communicator.  A failure made on the host; nothing faults."""
+    import ctypes as C
+
+    import mini_nccl_b200 as mn
+
+    L = mn.lib()
+    st, us, words = C.c_uint32(), C.c_uint32(), (C.c_uint32 * 4)()
+    assert L.mncclGemmProbeFlagWait(50_000_000, 0, C.byref(st), C.byref(us), words) == 0   # 50 ms budget
+    assert st.value == 3, "flag wait timed out"
+    assert 40_000 <= us.value < 2_000_000, us.value
+    assert words[0] == 1 and (words[1] & 0xffff) == (0x8000 | 3), "status = timeout, detail names the code"
+    assert words[2] == 1, "the kernel counted itself as started"
+    assert L.mncclGemmProbeFlagWait(2_000_000_000, 1, C.byref(st), C.byref(us), words) == 0
+    assert st.value == 4 and us.value < 100_000, "abort word set: the wait returns at once"
+    assert words[0] == 2, "status = aborted"

@@ -78,6 +78,23 @@ def test_fused_tensor_parallel_kernels(free_port):
     assert len(res) == n and all(r["worst"] < 3e-2 for r in res)
 
 
+@pytest.mark.multigpu(2)
+def test_fused_kernel_stall_fails_the_communicator_within_the_bound(free_port):
+    # NVLS off: a rank that leaves while its memory is bound to a multicast object can fault its peers.
+    env = {"MINI_NCCL_BOOTSTRAP_PORT": free_port, "MINI_NCCL_WATCHDOG_TIMEOUT_MS": 1500, "MINI_NCCL_NVLS_ENABLE": 0,
+           "NCCL_NVLS_ENABLE": 0}
+    res = run_ranks("gpu_tp_stall", 2, {"victim": 1}, env, timeout=300)
+    by_rank = {r["rank"]: r for r in res}
+    waiter = by_rank[0]
+    assert waiter["waited"] < 20, "the kernel returned within the bound"
+    assert waiter["gemm_status"] != 0, "the kernel recorded its failed wait"
+    assert waiter["stats"]["watchdog"]["trips"] + waiter["stats"]["watchdog"]["device_failures"] >= 1
+    for r in res:
+        assert r["async"] == _lib.INTERNAL_ERROR, r
+        assert r["raised"] == _lib.INTERNAL_ERROR, "a failed communicator takes no more fused kernels"
+        assert not r["stats"]["nvls"]
+
+
 @pytest.mark.multigpu(8)
 def test_fused_tensor_parallel_kernels_llama_shape(free_port):
     # Llama-3-8B block at TP=8: 4096 tokens, hidden 4096, FFN 14336 / 8 = 1792 per rank
