@@ -78,6 +78,18 @@ cudaError_t scratch_for_current_device(unsigned char** out) {
 }
 
 }  // namespace
+
+// Fills the control part (barrier words, per-rank state) of every virtual rank's scratch with `byte`, as
+// a call that was cut short might leave it; the next call must not care.  Not exported: reached through
+// the test-suite's own library only (csrc/testing/hooks.cc).
+int noalloc_dirty_control(int byte) {
+  unsigned char* scratch = nullptr;
+  if (scratch_for_current_device(&scratch) != cudaSuccess) return 1;
+  for (int r = 0; r < kNoAllocMaxRanks; ++r)
+    if (cudaMemset(scratch + size_t(r) * kCtrlBytes, byte, kClearBytes) != cudaSuccess) return 2;
+  return cudaDeviceSynchronize() == cudaSuccess ? 0 : 3;
+}
+
 }  // namespace mnccl
 
 using namespace mnccl;
@@ -114,16 +126,6 @@ MNCCL_EXPORT ncclResult_t mncclNoAllocLastStatus(cudaStream_t stream, unsigned* 
     return ncclUnhandledCudaError;
   }
   return ncclSuccess;
-}
-
-// Fills the control part (barrier words, per-rank state) of every virtual rank's scratch with `byte`, as
-// a call that was cut short might leave it; the next call must not care.  For the test-suite.
-MNCCL_EXPORT int mncclNoAllocDirtyControlForTest(int byte) {
-  unsigned char* scratch = nullptr;
-  if (scratch_for_current_device(&scratch) != cudaSuccess) return 1;
-  for (int r = 0; r < kNoAllocMaxRanks; ++r)
-    if (cudaMemset(scratch + size_t(r) * kCtrlBytes, byte, kClearBytes) != cudaSuccess) return 2;
-  return cudaDeviceSynchronize() == cudaSuccess ? 0 : 3;
 }
 
 MNCCL_EXPORT ncclResult_t mncclLocalAllReduceNoAlloc(const void* const* send, void* const* recv, int nbuffers,

@@ -32,6 +32,10 @@
 #include "ref/oracle.h"
 #include "watchdog/watchdog.h"
 
+namespace mnccl {
+int noalloc_dirty_control(int byte);  // csrc/kernels/noalloc.cu
+}
+
 using namespace mnccl;
 
 namespace {
@@ -103,6 +107,11 @@ MNCCL_EXPORT int mnccl_test_tuning_text(const char* text, int nranks, char* out,
     return 0;
   });
 }
+
+// Dirties the control words of the allocation-free entry point's static scratch (of THIS library's copy).
+#ifndef MNCCL_HOST_ONLY_SELFTEST  // the sanitizer self-test links no CUDA code
+MNCCL_EXPORT int mnccl_test_noalloc_dirty(int byte) { return noalloc_dirty_control(byte); }
+#endif
 
 // ---- chunk schedule of the pipeline -------------------------------------------
 // Writes up to `max` chunk sizes (elements) to `out`; returns the number of chunks or a negative code.

@@ -176,6 +176,16 @@ def lib() -> C.CDLL:
     return L
 
 
+def hooks_lib() -> C.CDLL:
+    """The test-suite's own copy of the library (libmini_nccl_testhooks.so): the same objects plus the
+    entry points of csrc/testing/hooks.cc.  It has its own static state, so a test that needs a hook to
+    act on library state (the allocation-free entry point's scratch) makes ALL its calls through it."""
+    path = lib_file().parent / "libmini_nccl_testhooks.so"
+    if not path.exists():
+        raise RuntimeError(f"{path} is missing (built by mini_nccl_b200.build)")
+    return C.CDLL(str(path), mode=C.RTLD_LOCAL)
+
+
 def check(code: int, where: str) -> None:
     if code != SUCCESS:
         raise MiniNcclError(code, where)

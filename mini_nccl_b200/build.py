@@ -226,7 +226,7 @@ def build_sanitized_selftest(kind: str = "address") -> Path:
     newest = max([s.stat().st_mtime for s in srcs] + [_newest_header_mtime()])
     if out.exists() and out.stat().st_mtime >= newest:
         return out
-    cmd = ["g++", "-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", "-ffp-contract=off", "-pthread", *flags,
+    cmd = ["g++", "-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", "-ffp-contract=off", "-pthread", "-DMNCCL_HOST_ONLY_SELFTEST=1", *flags,
            *_common_includes(), *map(str, srcs), "-o", str(out), "-lrt", "-ldl"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:

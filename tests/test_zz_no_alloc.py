@@ -78,7 +78,12 @@ def test_no_alloc_allocates_nothing_and_ignores_what_the_last_call_left():
     before it left behind: the scratch is dirtied with a direct copy between two calls."""
     import torch
 
-    L, lib = _lib()
+    L, _ = _lib()
+    # every call of this test goes through the test-suite's own copy of the library: the hook that
+    # dirties the scratch acts on that copy's static array
+    lib = L.hooks_lib()
+    lib.mncclLocalAllReduceNoAlloc.restype = C.c_int
+    lib.mncclLocalAllReduceNoAlloc.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int, C.c_size_t, C.c_int, C.c_int, C.c_void_p]
     rt = C.CDLL("libcudart.so.12")
     n, count = 4, 8192
     ins = [torch.full((count,), float(r + 1), device="cuda") for r in range(n)]
@@ -97,8 +102,7 @@ def test_no_alloc_allocates_nothing_and_ignores_what_the_last_call_left():
     assert free1.value == free0.value, "the call changed the amount of free device memory"
     assert all(torch.equal(o, torch.full_like(o, 10.0)) for o in outs)
     # leave garbage in the barrier words and the per-rank state (as an aborted call would), call again
-    lib.mncclNoAllocDirtyControlForTest.restype = C.c_int
-    assert lib.mncclNoAllocDirtyControlForTest(0xA5) == 0
+    assert lib.mnccl_test_noalloc_dirty(0xA5) == 0
     for o in outs:
         o.zero_()
     assert lib.mncclLocalAllReduceNoAlloc(sp, rp, n, count, L.FLOAT32, L.SUM, None) == 0
