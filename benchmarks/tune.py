@@ -3,7 +3,13 @@ csrc/algo/select.cc.  For every message size each applicable algorithm is timed 
 max over ranks) on symmetric and on ordinary buffers, with several grid caps and NVLS unroll
 factors; NCCL is timed eagerly and inside a CUDA graph for reference.
 
-  python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 benchmarks/tune.py --out tune8.json
+With ``--table FILE`` the measured crossovers are written as a tuning table that the library loads at
+start-up when MINI_NCCL_TUNING_FILE names it (lines ``<nranks> <KNOB> <value>``; rows of other rank
+counts already in the file are kept), so the choice of algorithm follows THIS machine's measured bus
+bandwidth; without a table the constants compiled into csrc/algo/select.cc apply.
+
+  python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 benchmarks/tune.py --out tune8.json --table tuning.txt
+  MINI_NCCL_TUNING_FILE=tuning.txt python ...
 """
 from __future__ import annotations
 
@@ -17,6 +23,61 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 from benchmarks.sweep import _time_loop  # noqa: E402
+
+
+def _best_time(row: dict, where: str, algo: str):
+    """Fastest measured time (us) of `algo` on `where` buffers in a row, over its launch variants."""
+    vals = [v for k, v in row.items() if isinstance(v, (int, float)) and not k.endswith("_graph")
+            and (k == f"{where}_{algo}" or k.startswith(f"{where}_{algo}_b"))]
+    return min(vals) if vals else None
+
+
+def crossovers(rows: list[dict], where: str = "sym") -> dict:
+    """Selection knobs from a sweep: LL up to the largest size where it is the fastest algorithm, one-shot
+    up to the largest size where it beats both two-phase kernels, NVLS from the smallest size where it
+    beats the peer-to-peer two-shot kernel.  Sizes without a measurement of an algorithm do not vote.
+    Pure function of the rows (tested without a GPU)."""
+    knobs = {}
+    ll_max = oneshot_max = 0
+    nvls_min = None
+    for row in sorted(rows, key=lambda r: r["bytes"]):
+        t = {a: _best_time(row, where, a) for a in ("ll", "oneshot", "twoshot", "nvls")}
+        have = {a: v for a, v in t.items() if v is not None}
+        if not have:
+            continue
+        best = min(have, key=have.get)
+        if best == "ll":
+            ll_max = row["bytes"]
+        two_phase = [v for a, v in have.items() if a in ("twoshot", "nvls")]
+        if "oneshot" in have and (best in ("ll", "oneshot") or not two_phase or have["oneshot"] <= min(two_phase)):
+            oneshot_max = max(oneshot_max, row["bytes"])
+        if "nvls" in have and "twoshot" in have and have["nvls"] < have["twoshot"] and nvls_min is None:
+            nvls_min = row["bytes"]
+    if ll_max:
+        knobs["LL_MAX_BYTES"] = ll_max
+    if oneshot_max:
+        knobs["ONESHOT_MAX_BYTES"] = max(oneshot_max, ll_max)
+    if nvls_min is not None:
+        knobs["NVLS_MIN_BYTES"] = max(nvls_min, knobs.get("ONESHOT_MAX_BYTES", 0) + 1)
+    return knobs
+
+
+def write_table(path: str, world: int, knobs: dict, note: str = "") -> None:
+    """Writes / updates the rows of `world` ranks in a tuning table, keeping the other rank counts' rows."""
+    keep = []
+    if os.path.exists(path):
+        for line in open(path):
+            body = line.split("#", 1)[0].split()
+            if len(body) == 3 and body[0] == str(world):
+                continue
+            if line.strip() and not line.startswith("# written by benchmarks/tune.py"):
+                keep.append(line.rstrip("\n"))
+    with open(path, "w") as f:
+        f.write("# written by benchmarks/tune.py: <nranks> <KNOB> <value>; loaded through MINI_NCCL_TUNING_FILE\n")
+        for line in keep:
+            f.write(line + "\n")
+        for k, v in sorted(knobs.items()):
+            f.write(f"{world} {k} {int(v)}" + (f"   # {note}" if note else "") + "\n")
 
 
 def graph_time(fn, world, inner=20, reps=5):
@@ -47,6 +108,7 @@ def main():
     ap.add_argument("--dtype", default="fp32")
     ap.add_argument("--blocks", default="16,24,32,64,96")
     ap.add_argument("--plain", action="store_true", help="also time ordinary (staged) buffers")
+    ap.add_argument("--table", default="", help="write the measured crossovers as a tuning table (MINI_NCCL_TUNING_FILE)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -116,6 +178,10 @@ def main():
     if rank == 0 and args.out:
         with open(args.out, "w") as f:
             json.dump({"world": world, "nvls": nvls, "rows": rows}, f)
+    if rank == 0 and args.table:
+        knobs = crossovers(rows)
+        write_table(args.table, world, knobs, note=f"{args.dtype}, symmetric buffers")
+        print("tuning table:", json.dumps(knobs), flush=True)
     dist.barrier()
     comm.free(sym)
     comm.destroy()

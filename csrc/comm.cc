@@ -42,6 +42,7 @@ struct PeerInfo {
   int32_t device;
   int32_t device_count;
   int32_t pid;
+  int32_t may_pick_device;  // this rank lets the library pick its GPU (Hera mode, automatic choice on, no device forced)
   char bus_id[32];
 };
 
@@ -63,6 +64,17 @@ constexpr size_t kShmBytes = 4096;
 constexpr int kProgressWords = 16;  // per local rank, 64 bytes
 
 enum class MemKind { Device, PinnedHost, PlainHost };
+
+// The driver's id of the allocation `p` lies in (unique per allocation for the life of the process);
+// 0 when it cannot be told.
+unsigned long long allocation_id(const void* p) {
+  const CudaDriver* d = CudaDriver::get();
+  unsigned long long id = 0;
+  if (!d || !d->PointerGetAttribute ||
+      d->PointerGetAttribute(&id, CU_POINTER_ATTRIBUTE_BUFFER_ID, reinterpret_cast<CUdeviceptr>(p)) != CUDA_SUCCESS)
+    return 0;
+  return id;
+}
 
 MemKind classify(const void* p, bool has_gpu) {
   if (!has_gpu) return MemKind::PlainHost;
@@ -153,6 +165,7 @@ void Comm::init(int nranks, int rank, const char* ip) {
   me.device = device_;
   me.device_count = ndev;
   me.pid = static_cast<int32_t>(getpid());
+  me.may_pick_device = (hera_mode && cfg_.auto_device && has_gpu_ && cfg_.cuda_device < 0) ? 1 : 0;
   if (has_gpu_) cudaDeviceGetPCIBusId(me.bus_id, sizeof(me.bus_id), device_);
   std::vector<PeerInfo> all(size_);
   store_->all_gather(&me, all.data(), sizeof(me));
@@ -172,7 +185,12 @@ void Comm::init(int nranks, int rank, const char* ip) {
   // Hera mode: ranks that were all started on the same device (the reference
   // benchmark pins every rank to GPU 0, reference: tests/perf_test.cpp:46)
   // spread over the host's GPUs by local rank.
-  if (hera_mode && cfg_.auto_device && has_gpu_ && cfg_.cuda_device < 0 && one_host && all_gpu && size_ > 1) {
+  // Whether this second exchange happens is decided from the GATHERED data only, so that every rank
+  // takes the same branch even when their environments differ (one rank with MINI_NCCL_CUDA_DEVICE set
+  // would otherwise skip an all_gather the others wait in).
+  bool all_may_pick = true;
+  for (int r = 0; r < size_; ++r) all_may_pick = all_may_pick && all[r].may_pick_device != 0;
+  if (all_may_pick && one_host && all_gpu && size_ > 1) {
     bool shared = true;
     for (int r = 0; r < size_; ++r) shared = shared && all[r].device == all[0].device;
     if (shared && ndev >= local_size_) {
@@ -594,6 +612,22 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
   if (size_ > 1) {
     in_seg = find_segment(send, in_bytes, &in_off);
     out_seg = find_segment(recv, out_bytes, &out_off);
+    // A registered buffer that was freed and whose address range now belongs to another allocation: the
+    // peers' mappings point at the old memory.  Nothing can be reduced into the right place any more
+    // (and the ranks could disagree on whether the buffer still counts as registered), so the call is
+    // refused: buffers are deregistered before they are freed.
+    for (const auto* sp : {&in_seg, &out_seg}) {
+      if (*sp && (*sp)->buffer_id != 0) {
+        const void* p = sp == &in_seg ? send : recv;
+        const unsigned long long now = allocation_id(p);
+        if (now != 0 && now != (*sp)->buffer_id) {
+          stats_.stale_registrations++;
+          fail(Result::InvalidUsage, "a buffer registered with mncclCommRegister was freed and its address range allocated "
+                                     "again; call mncclCommDeregister before freeing a registered buffer");
+        }
+      }
+    }
+
     pi.in_symmetric = in_seg && (reinterpret_cast<uintptr_t>(send) & 15u) == 0;
     pi.out_symmetric = out_seg && (reinterpret_cast<uintptr_t>(recv) & 15u) == 0;
     pi.in_has_mc = in_seg && in_seg->mc;
@@ -1090,6 +1124,7 @@ void Comm::register_buffer(void* ptr, size_t bytes) {
   seg->mapped_bytes = bytes;
   seg->local = ptr;
   seg->peer.assign(size_, nullptr);
+  seg->buffer_id = allocation_id(ptr);
   std::vector<std::string> keys;
   bool ok = true;
   for (int r = 0; r < size_; ++r) {
@@ -1208,7 +1243,7 @@ std::string Comm::stats_json() {
   }
   o << "},\"zero_copy_in\":" << stats_.zero_copy_in << ",\"zero_copy_out\":" << stats_.zero_copy_out
     << ",\"ipc_cache\":{\"hits\":" << ipc_hits_ << ",\"misses\":" << ipc_misses_ << ",\"open\":" << ipc_cache_.size() << "}"
-    << ",\"staged_calls\":" << stats_.staged_passes << ",\"pipelined_calls\":" << stats_.pipelined << ",\"graph_captures_seen\":" << stats_.graph_captures_seen;
+    << ",\"stale_registrations\":" << stats_.stale_registrations << ",\"staged_calls\":" << stats_.staged_passes << ",\"pipelined_calls\":" << stats_.pipelined << ",\"graph_captures_seen\":" << stats_.graph_captures_seen;
   if (watchdog_) {
     o << ",\"watchdog\":{\"polls\":" << watchdog_->stats().polls.load() << ",\"trips\":" << watchdog_->stats().trips.load()
       << ",\"device_failures\":" << watchdog_->stats().device_failures.load() << ",\"remote_aborts\":"

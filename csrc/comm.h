@@ -34,6 +34,7 @@ namespace hera { class Worker; }
 struct CommStats {
   uint64_t calls = 0, bytes = 0;
   uint64_t by_algo[12] = {0};
+  uint64_t stale_registrations = 0;
   uint64_t zero_copy_in = 0, zero_copy_out = 0, staged_passes = 0, pipelined = 0;
   uint64_t graph_captures_seen = 0, errors = 0;
 };

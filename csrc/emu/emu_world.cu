@@ -165,6 +165,26 @@ MNCCL_EXPORT int mncclEmuSetPipeChunk(void* world, size_t bytes) {
   return 0;
 }
 
+// The size of the staging areas as the KERNELS are told it, without changing the allocation or the
+// planning: a smaller claim makes staged accesses cross the claimed end while they stay inside memory
+// the world owns.  For the checked build (MNCCL_DEVICE_CHECKS), whose kernels must record and skip such
+// accesses; 0 restores the true size.
+MNCCL_EXPORT int mncclEmuClaimStageBytes(void* world, size_t bytes) {
+  auto* w = static_cast<EmuWorld*>(world);
+  if (!w || bytes > w->caps.stage_bytes) return 4;
+  for (auto& d : w->dev) d.stage_bytes = bytes ? bytes : w->caps.stage_bytes;
+  return 0;
+}
+
+// 1 when this library was compiled with the device-side checks.
+MNCCL_EXPORT int mncclBuiltWithDeviceChecks(void) {
+#ifdef MNCCL_DEVICE_CHECKS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
 // A deaf rank takes no part in the collective (its kernel sees zero ranks and
 // zero elements): it neither signals nor waits, so its peers' bounded waits
 // run out.  Host-made failure for tests.

@@ -292,6 +292,7 @@ __device__ __forceinline__ void twoshot_core(const CommDev& c, const CollArgs& a
             for (int k = 0; k < VW; ++k) w[k] = static_cast<Acc>(x[k]);
             Packed<WireT, VW> pk;
             pk.from_acc(w);
+            if (!MNCCL_STAGE_OK(c, (uint64_t(j) * SV + i) * 16, 16)) continue;
             *reinterpret_cast<uint4*>(a.in_peer[me] + (uint64_t(j) * SV + i) * 16) = pk.vec.q[0];
           }
         }
@@ -320,6 +321,7 @@ __device__ __forceinline__ void twoshot_core(const CommDev& c, const CollArgs& a
           for (int k = 0; k < N; ++k) {
             const int p = (me + k) % N;
             if (staged_out) {
+              if (!MNCCL_STAGE_OK(c, (uint64_t(me) * SV + i) * OUT_VB, OUT_VB)) continue;
               store_vec<OutT, VW>(a.out_peer[p] + (uint64_t(me) * SV + i) * OUT_VB, 0, VW, true, y);
             } else {
               store_vec<OutT, VW>(a.out_peer[p], uint64_t(me) * E + e0, uint64_t(me) * E + E, recv_al, y);
@@ -339,6 +341,7 @@ __device__ __forceinline__ void twoshot_core(const CommDev& c, const CollArgs& a
           const uint64_t e0 = uint64_t(me) * E + (v0 + i) * VW;
           valid[u] = i < sv && e0 < lim_me;
           off[u] = staged_in ? (uint64_t(me) * SV + i) * 16 : e0 * sizeof(typename Elem<WireT>::Raw);
+          if (staged_in && valid[u] && !MNCCL_STAGE_OK(c, off[u], 16)) valid[u] = false;
         }
         if constexpr (NVLS) {
           uint4 r[kUnroll];
@@ -388,10 +391,12 @@ __device__ __forceinline__ void twoshot_core(const CommDev& c, const CollArgs& a
               static_assert(OUT_VB % 16 == 0, "NVLS output vectors are whole 16-byte units");
               Packed<OutT, VW> pk;
               pk.from_acc(y);
+              if (!MNCCL_STAGE_OK(c, (uint64_t(me) * SV + i) * OUT_VB, OUT_VB)) continue;
               char* dst = a.out_mc + (uint64_t(me) * SV + i) * OUT_VB;
 #pragma unroll
               for (int q = 0; q < OUT_VB / 16; ++q) multimem_st_v4(dst + q * 16, pk.vec.q[q]);
             } else {
+              if (!MNCCL_STAGE_OK(c, (uint64_t(me) * SV + i) * OUT_VB, OUT_VB)) continue;
               for (int k = 0; k < N; ++k) {
                 const int p = (me + k) % N;
                 store_vec<OutT, VW>(a.out_peer[p] + (uint64_t(me) * SV + i) * OUT_VB, 0, VW, true, y);
@@ -434,6 +439,7 @@ __device__ __forceinline__ void twoshot_core(const CommDev& c, const CollArgs& a
             uint64_t lim = uint64_t(j) * E + E;
             if (lim > total) lim = total;
             if (i >= sv || e0 >= lim) continue;
+            if (!MNCCL_STAGE_OK(c, (uint64_t(j) * SV + i) * OUT_VB, OUT_VB)) continue;
             OAcc y[VW];
             load_vec<OutT, VW>(a.out_peer[me] + (uint64_t(j) * SV + i) * OUT_VB, 0, VW, true, y);
             store_vec<OutT, VW>(a.recv, e0, lim, recv_al, y);

@@ -31,6 +31,7 @@ enum DevStatus : uint32_t {
   kDevOk = 0,
   kDevTimeout = 1,   // a bounded wait ran out
   kDevAborted = 2,   // the abort word was set while waiting
+  kDevBadIndex = 3,  // checked build only (MNCCL_DEVICE_CHECKS): a staging access fell outside its area or off alignment
 };
 
 struct LocalState {

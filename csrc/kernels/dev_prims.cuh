@@ -96,6 +96,22 @@ __device__ __forceinline__ void record_failure(const CommDev& c, uint32_t code, 
   }
 }
 
+// Checked build (-DMNCCL_DEVICE_CHECKS=1, libmini_nccl_devcheck.so): every access to a staging area
+// is tested against the area's size and the 16-byte alignment first; a bad one is RECORDED in the
+// status word (kDevBadIndex, detail = offset / 16) and skipped -- never a trap, never the access.
+// The product build compiles the test away.  (compute-sanitizer is not available everywhere this
+// library is developed; these checks and the host oracle stand in for it.)
+#ifdef MNCCL_DEVICE_CHECKS
+__device__ __forceinline__ bool stage_access_ok(const CommDev& c, uint64_t off, uint32_t bytes) {
+  if (off + bytes <= c.stage_bytes && (off & 15u) == 0u) return true;
+  record_failure(c, kDevBadIndex, static_cast<uint32_t>(off >> 4));
+  return false;
+}
+#define MNCCL_STAGE_OK(c, off, bytes) ::mnccl::dev::stage_access_ok((c), (off), (bytes))
+#else
+#define MNCCL_STAGE_OK(c, off, bytes) true
+#endif
+
 // Waits until *p >= target (wrap-safe).  Returns kDevOk, kDevTimeout or
 // kDevAborted; never spins for longer than c.spin_timeout_ns.
 __device__ __forceinline__ uint32_t wait_ge(const uint32_t* p, uint32_t target, const CommDev& c) {

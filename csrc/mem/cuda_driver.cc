@@ -54,6 +54,7 @@ const CudaDriver* CudaDriver::get() {
     resolve("cuStreamWriteValue32", &d->StreamWriteValue32);
     resolve("cuTensorMapEncodeTiled", &d->TensorMapEncodeTiled);
     resolve("cuMemGetAddressRange", &d->MemGetAddressRange);
+    resolve("cuPointerGetAttribute", &d->PointerGetAttribute);
     drv = d;
   });
   return drv;

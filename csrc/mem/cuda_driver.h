@@ -32,6 +32,7 @@ struct CudaDriver {
   decltype(&cuStreamWriteValue32) StreamWriteValue32 = nullptr;
   decltype(&cuTensorMapEncodeTiled) TensorMapEncodeTiled = nullptr;
   decltype(&cuMemGetAddressRange) MemGetAddressRange = nullptr;
+  decltype(&cuPointerGetAttribute) PointerGetAttribute = nullptr;
 
   bool has_vmm = false;        // every VMM entry point resolved
   bool has_multicast = false;  // every multicast entry point resolved

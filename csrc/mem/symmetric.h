@@ -37,6 +37,10 @@ struct Segment {
   void* local = nullptr;     // this rank's copy (== peer[rank])
   std::vector<void*> peer;   // every rank's copy as mapped in this process
   void* mc = nullptr;        // multicast address or null
+  // Buffers registered over CUDA IPC (mncclCommRegister): the driver's id of the allocation at the time
+  // of registration (0 = not tracked).  An address range that was freed and allocated again carries
+  // another id, so a stale registration is noticed before a kernel uses the peers' old mappings.
+  unsigned long long buffer_id = 0;
   struct Impl;
   std::shared_ptr<Impl> impl;
 };

@@ -134,7 +134,10 @@ ncclResult_t mncclMemPeerPointers(ncclComm_t comm, void* ptr, void** peer_ptrs, 
 /* Registration of ordinary device buffers (cudaMalloc family): a collective call that exchanges
  * CUDA IPC handles once and keeps the opened mappings in a handle cache, after which the
  * peer-to-peer algorithms use the buffer in place (no staging).  NVLS needs memory from
- * mncclMemAlloc.  Every rank registers a buffer of the same size in the same call. */
+ * mncclMemAlloc.  Every rank registers a buffer of the same size in the same call.
+ * A registered buffer must be deregistered BEFORE it is freed: the registration is keyed by address,
+ * and a later allocation in the same range would be reduced through the peers' mappings of the old
+ * memory.  The library notices the change of allocation and refuses such a call (ncclInvalidUsage). */
 ncclResult_t mncclCommRegister(ncclComm_t comm, void* buff, size_t bytes);
 ncclResult_t mncclCommDeregister(ncclComm_t comm, void* buff);
 

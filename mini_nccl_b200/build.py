@@ -178,6 +178,42 @@ def build(verbose: bool = False, programs: bool = True, jobs: int | None = None)
     return lib
 
 
+def build_devcheck_variant(verbose: bool = False, jobs: int | None = None) -> Path:
+    """The checked build: the collective kernels compiled with -DMNCCL_DEVICE_CHECKS=1 (every staging
+    access is tested against its area and alignment first; a bad one is recorded in the status word and
+    skipped, never trapped) and linked with the normal host objects into libmini_nccl_devcheck.so.  The
+    stand-in for compute-sanitizer where that tool is not available."""
+    lib = build(verbose=verbose, programs=False)
+    out = LIBDIR / "libmini_nccl_devcheck.so"
+    hdr = _newest_header_mtime()
+    checked = ["kernels/k_small.cu", "kernels/k_twoshot.cu", "kernels/k_rsag.cu", "kernels/k_nvls.cu", "kernels/k_pipe.cu",
+               "kernels/launch.cu", "emu/emu_world.cu"]
+
+    def compile_checked(rel: str) -> Path:
+        src = CSRC / rel
+        obj = BUILD / f"devcheck-{src.stem}.o"
+        if obj.exists() and obj.stat().st_mtime >= max(src.stat().st_mtime, hdr):
+            return obj
+        cmd = [NVCC, "-std=c++17", "-O3", *ARCH, "-lineinfo", "-DMNCCL_DEVICE_CHECKS=1", "-Xcompiler", "-fPIC,-fvisibility=hidden",
+               *_common_includes(), "-c", str(src), "-o", str(obj)]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"compile failed: {src}\n{r.stderr}")
+        return obj
+
+    with cf.ThreadPoolExecutor(max_workers=jobs or max(1, (os.cpu_count() or 4))) as ex:
+        objs = list(ex.map(compile_checked, checked))
+    others = [s for s in HOST_SOURCES] + [c for c in CUDA_SOURCES + OPTIONAL_CUDA if c not in checked and (CSRC / c).exists()]
+    objs += [_obj_path(CSRC / s) for s in others]
+    if not out.exists() or out.stat().st_mtime < max(o.stat().st_mtime for o in objs):
+        cmd = [NVCC, "-shared", *ARCH, "-cudart", "static", "-Xlinker", "-Bsymbolic-functions", "-o", str(out),
+               *map(str, objs), "-lpthread", "-lrt", "-ldl"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed\n{r.stdout}\n{r.stderr}")
+    return out
+
+
 def build_fake_verbs_variant(verbose: bool = False) -> Path:
     """Test-only variant of the library with the verbs provider compiled against the stand-in
     header and implementation under tests/fake_verbs (no libibverbs needed).  Reuses the objects

@@ -236,6 +236,27 @@ def gpu_battery(rank, n, kw):
     comm.register(view)
     assert comm.stats()["ipc_cache"]["hits"] >= 0
     comm.deregister(reg)
+    # A registered buffer that is freed and whose range is allocated again: the library notices the new
+    # allocation (driver buffer id) and refuses the call instead of reducing through stale peer mappings.
+    rt = C.CDLL("libcudart.so.12")
+    pa, pb = C.c_void_p(), C.c_void_p()
+    assert rt.cudaMalloc(C.byref(pa), C.c_size_t(4 << 20)) == 0
+    _lib.check(_lib.lib().mncclCommRegister(comm.handle, pa, 4 << 20), "mncclCommRegister")
+    assert rt.cudaFree(pa) == 0
+    assert rt.cudaMalloc(C.byref(pb), C.c_size_t(4 << 20)) == 0
+    same = torch.tensor([1.0 if pb.value == pa.value else 0.0], device="cuda")
+    comm.all_reduce(same, "min")
+    res["stale_registration_checked"] = bool(same.item() == 1.0)
+    if res["stale_registration_checked"]:      # every rank got its old range back
+        rc = _lib.lib().mncclAllReduce(pb, pb, 1 << 20, _lib.FLOAT32, _lib.SUM, comm.handle, None)
+        assert rc == _lib.INVALID_USAGE, f"stale registration not refused: rc {rc}"
+        assert comm.stats()["stale_registrations"] >= 1
+    _lib.check(_lib.lib().mncclCommDeregister(comm.handle, pa), "mncclCommDeregister")
+    assert rt.cudaFree(pb) == 0
+    x = torch.ones(1 << 20, device="cuda")
+    comm.all_reduce(x, "sum")                   # the communicator is as usable as before
+    torch.cuda.synchronize()
+    assert torch.all(x == float(n)).item()
     # NVLS on exactly representable data is bit-exact whatever the order
     if res["nvls"]:
         count = 1 << 18

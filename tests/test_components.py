@@ -157,6 +157,37 @@ garbage here
     assert got["applied"] == 2 and got["oneshot_max_bytes"] == 1048576 and got["ll_max_bytes"] == 0
 
 
+def test_tune_script_derives_a_table_the_library_loads(lib, tmp_path):
+    """benchmarks/tune.py: crossovers from a (here synthetic) sweep, written as a table, read back by the
+    library's loader; rows of another rank count survive an update."""
+    import json
+
+    from benchmarks.tune import crossovers, write_table
+
+    rows = [
+        {"bytes": 8192, "sym_ll": 9.0, "sym_oneshot": 12.0},
+        {"bytes": 65536, "sym_ll": 11.0, "sym_oneshot": 12.5, "sym_twoshot_b32": 20.0, "sym_nvls_b32_u4": 19.0},
+        {"bytes": 262144, "sym_oneshot": 14.0, "sym_twoshot_b32": 19.0, "sym_nvls_b32_u4": 16.5, "sym_nvls_b16_u4": 15.0},
+        {"bytes": 1048576, "sym_oneshot": 28.0, "sym_twoshot_b32": 24.0, "sym_nvls_b32_u4": 21.0, "sym_oneshot_graph": 1.0},
+        {"bytes": 4194304, "sym_twoshot_b96": 40.0, "sym_nvls_b32_u4": 30.0},
+    ]
+    knobs = crossovers(rows)
+    assert knobs == {"LL_MAX_BYTES": 65536, "ONESHOT_MAX_BYTES": 262144, "NVLS_MIN_BYTES": 262145}
+    path = tmp_path / "tuning.txt"
+    path.write_text("4 ONESHOT_MAX_BYTES 524288\n")
+    write_table(str(path), 8, knobs, note="test")
+    write_table(str(path), 8, knobs, note="again")            # an update replaces the rows of 8 ranks only
+    text = path.read_text()
+    assert text.count("8 LL_MAX_BYTES") == 1 and "4 ONESHOT_MAX_BYTES 524288" in text
+    buf = C.create_string_buffer(2048)
+    assert lib.mnccl_test_tuning_text(text.encode(), 8, buf, len(buf)) == 0
+    got = json.loads(buf.value.decode())
+    assert got["applied"] == 3 and got["ll_max_bytes"] == 65536 and got["oneshot_max_bytes"] == 262144 and got["nvls_min_bytes"] == 262145
+    assert got["errors"] == ""
+    assert lib.mnccl_test_tuning_text(text.encode(), 4, buf, len(buf)) == 0
+    assert json.loads(buf.value.decode())["oneshot_max_bytes"] == 524288
+
+
 def test_planner_picks_by_size(lib):
     assert plan(lib, 8, 2048)["algo"] == "ll"                      # 8 KB
     assert plan(lib, 8, 16384)["algo"] == "ll"                     # 64 KB
