@@ -7,6 +7,11 @@ larger than the L2 but far below a GB, so that a capture ends by itself within a
   python benchmarks/profile_targets.py --target twoshot     # emulated 4-rank two-shot AllReduce, 64 MiB per rank
   python benchmarks/profile_targets.py --target oneshot     # emulated 4-rank one-shot AllReduce, 256 KiB per rank
   python benchmarks/profile_targets.py --target gemm_rs     # fused GEMM->reduce-scatter kernel, one rank, 4096 x 4096 x 1792
+  python benchmarks/profile_targets.py --target ag_gemm     # fused all-gather->GEMM kernel with the SwiGLU epilogue, one rank, 4096 x 3584 x 4096
+  python benchmarks/profile_targets.py --target swiglu      # one-pass SwiGLU kernel, 4096 x 2 x 14336 bf16 in
+  python benchmarks/profile_targets.py --target ll          # emulated 4-rank LL AllReduce, 32 KiB per rank
+  python benchmarks/profile_targets.py --target pipe        # emulated 4-rank pipelined AllReduce (peer-to-peer form), 64 MiB per rank, ordinary buffers
+  python benchmarks/profile_targets.py --target noalloc     # allocation-free one-shot AllReduce over 4 buffers of 64 KiB
 """
 from __future__ import annotations
 
@@ -27,7 +32,7 @@ def main():
     from mini_nccl_b200 import _lib
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("--target", required=True, choices=["gemm", "gemm_pair", "copy", "twoshot", "oneshot", "gemm_rs"])
+    ap.add_argument("--target", required=True, choices=["gemm", "gemm_pair", "copy", "twoshot", "oneshot", "gemm_rs", "ag_gemm", "swiglu", "ll", "pipe", "noalloc"])
     ap.add_argument("--launches", type=int, default=4)
     args = ap.parse_args()
     torch.cuda.set_device(0)
@@ -59,6 +64,57 @@ def main():
         torch.cuda.synchronize()
         assert gemm_status() == 0
         comm.destroy()
+    elif args.target == "ag_gemm":
+        # single rank: the kernel's own code path (rows already local, no communication CTAs) with the
+        # SwiGLU epilogue the tensor-parallel block uses: act [4096, 1792] out of a 4096 x 3584 x 4096 product
+        from mini_nccl_b200.ops import AllGatherGemm, gemm_status, interleave_gate_up
+
+        comm = mn.Communicator(1, 0)
+        ag = AllGatherGemm(comm, 4096, 4096)
+        ag.local_shard.copy_(torch.randn(4096, 4096, device="cuda").to(torch.bfloat16))
+        w = interleave_gate_up((torch.randn(1792, 4096, device="cuda") * 0.02).to(torch.bfloat16),
+                               (torch.randn(1792, 4096, device="cuda") * 0.02).to(torch.bfloat16))
+        act = torch.empty(4096, 1792, device="cuda", dtype=torch.bfloat16)
+        for _ in range(args.launches):
+            ag(w, out=act, swiglu=True)
+        torch.cuda.synchronize()
+        assert gemm_status() == 0
+        comm.destroy()
+    elif args.target == "swiglu":
+        from mini_nccl_b200.ops import swiglu_bf16
+
+        h = torch.randn(4096, 2 * 14336, device="cuda").to(torch.bfloat16)      # 235 MB in, 117 MB out: larger than the L2
+        out = torch.empty(4096, 14336, device="cuda", dtype=torch.bfloat16)
+        for _ in range(args.launches):
+            swiglu_bf16(h, out=out)
+        torch.cuda.synchronize()
+    elif args.target == "noalloc":
+        n, count = 4, 16384
+        ins = [torch.randn(count, device="cuda") for _ in range(n)]
+        outs = [torch.empty_like(t) for t in ins]
+        sp = (C.c_void_p * n)(*[t.data_ptr() for t in ins])
+        rp = (C.c_void_p * n)(*[t.data_ptr() for t in outs])
+        lib.mncclLocalAllReduceNoAlloc.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int, C.c_size_t, C.c_int, C.c_int, C.c_void_p]
+        for _ in range(args.launches):
+            assert lib.mncclLocalAllReduceNoAlloc(sp, rp, n, count, _lib.FLOAT32, _lib.SUM, None) == 0
+        torch.cuda.synchronize()
+    elif args.target in ("ll", "pipe"):
+        n = 4
+        world = C.c_void_p()
+        assert lib.mncclEmuCreate(n, 64 << 20, C.byref(world)) == 0
+        count = (8 << 10) if args.target == "ll" else (16 << 20)
+        algo = _lib.ALGO_LL if args.target == "ll" else 7
+        ins = [torch.randn(count, device="cuda") for _ in range(n)]        # ordinary buffers
+        outs = [torch.empty_like(t) for t in ins]
+        sp = (C.c_void_p * n)(*[t.data_ptr() for t in ins])
+        rp = (C.c_void_p * n)(*[t.data_ptr() for t in outs])
+        for _ in range(args.launches):
+            rc = lib.mncclEmuCollective(world, 0, sp, rp, count, _lib.FLOAT32, _lib.FLOAT32, _lib.FLOAT32, _lib.SUM, 0.25, algo, 0, None)
+            assert rc == 0, rc
+        torch.cuda.synchronize()
+        st = (C.c_uint32 * n)()
+        assert lib.mncclEmuStatus(world, st, None) == 0 and list(st) == [0] * n
+        lib.mncclEmuDestroy(world)
     elif args.target == "copy":
         comm = mn.Communicator(1, 0)
         x = torch.randn(64 << 20, device="cuda")           # 256 MiB fp32

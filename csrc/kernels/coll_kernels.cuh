@@ -603,8 +603,10 @@ __device__ __forceinline__ void pipe_body(const KParams& P, int blk, int nblk, B
   constexpr int VW = 16 / sizeof(WRaw);
   constexpr int OUT_VB = VW * sizeof(ORaw);
   static_assert(OUT_VB % 16 == 0, "output vectors are whole 16-byte units for every supported type triple");
-  constexpr int U = NVLS ? 4 : 8;  // vectors in flight per thread in the reduction (peer loads: two round trips per step)
-  constexpr int UC = (OUT_VB > 16) ? 8 : 16;  // ... and in the two copies (bound by loads in flight, not by arithmetic)
+  // Vectors in flight per thread in the reduction and in the two copies.  The switch form keeps its
+  // arrays in registers (126 of the 128 a 512-thread block may use, no spills).
+  constexpr int U = 4;
+  constexpr int UC = (NVLS && OUT_VB == 16) ? 16 : 8;
   constexpr bool kSameIn = std::is_same<InT, WireT>::value;
   block_begin(c, blk, ctl);
   const int N = c.nranks, me = c.rank;
