@@ -81,6 +81,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   const int tiles_n = (g.N + kBN - 1) / kBN;
   const int num_tiles = tiles_m2 * tiles_n;
   const int num_kb = (g.K + kBK - 1) / kBK;
+  const int num_items = pair_work_items(g, num_tiles);  // tiles, the last wave's cut into K-slices
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -124,9 +125,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += n_pairs) {
+      for (int t = pair; t < num_items && ok; t += n_pairs) {
+        const PairWork w = pair_work(g, t, num_kb);
         int tm2, tn;
-        tile_coords(g2, t, tiles_m2, tiles_n, &tm2, &tn);
+        tile_coords(g2, w.tile, tiles_m2, tiles_n, &tm2, &tn);
         const int tm = tm2 * 2 + static_cast<int>(cta);
         if (g.a_ready != nullptr) {
           const int chunk = (tm * kBM) / g.rows_per_chunk;
@@ -149,7 +151,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           if (!ok) break;
           if (waited) asm volatile("fence.proxy.async.global;" ::: "memory");
         }
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const uint32_t s = it % NS;
           const uint32_t ph = (it / NS) & 1u;
           if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1u, &ctl->abort, budget)) { ok = false; break; }
@@ -167,13 +169,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       constexpr uint32_t idesc = make_idesc_bf16(2 * kBM, kBN);
       uint32_t it = 0, local = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += n_pairs, ++local) {
+      for (int t = pair; t < num_items && ok; t += n_pairs, ++local) {
+        const PairWork w = pair_work(g, t, num_kb);
         const uint32_t buf = local & 1u;
         const uint32_t acc_ph = (local >> 1) & 1u;
         if (!mbar_wait(smem_u32(&ctl->tmem_empty[buf]), acc_ph ^ 1u, &ctl->abort, budget)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d = tmem_base + buf * kBN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const uint32_t s = it % NS;
           const uint32_t ph = (it / NS) & 1u;
           if (!mbar_wait(smem_u32(&ctl->full[s]), ph, &ctl->abort, budget)) { ok = false; break; }
@@ -184,7 +187,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k)
             umma_bf16_pair(d, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), idesc,
-                           (kb | k) != 0 ? 1u : 0u);
+                           ((kb - w.kb0) | k) != 0 ? 1u : 0u);
           umma_commit_pair(smem_u32(&ctl->empty[s]), 3);  // the stage is free in both CTAs
         }
         if (ok) umma_commit_pair(smem_u32(&ctl->tmem_full[buf]), 3);
@@ -197,9 +200,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     epi.warp_begin(warp_smem, lane);
     uint32_t local = 0;
     bool ok = true;
-    for (int t = pair; t < num_tiles && ok; t += n_pairs, ++local) {
+    for (int t = pair; t < num_items && ok; t += n_pairs, ++local) {
+      const PairWork w = pair_work(g, t, num_kb);
       int tm2, tn;
-      tile_coords(g2, t, tiles_m2, tiles_n, &tm2, &tn);
+      tile_coords(g2, w.tile, tiles_m2, tiles_n, &tm2, &tn);
       const int tm = tm2 * 2 + static_cast<int>(cta);
       const uint32_t buf = local & 1u;
       const uint32_t acc_ph = (local >> 1) & 1u;
@@ -207,17 +211,87 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       tc_fence_after_sync();
       const int row = tm * kBM + q * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kBN;
+      if (!w.split) {
+#pragma unroll 1
+        for (int c = 0; c < kBN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          epi.store(g, epoch, row, tn * kBN + c * 32, r, c, warp_smem, lane);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->tmem_empty[buf]), 0));
+        if (tm * kBM < g.M) epi.tile_done(g, epoch, tm, tn, q, lane, warp_smem);
+        continue;
+      }
+      // ---- one K-slice of a tile of the last wave: accumulators -> workspace, laid out so that a store
+      // instruction of the warp writes 512 contiguous bytes: float4 index ((c * 8 + j) * 32 + lane)
+      constexpr int kQuarterF4 = (kBN / 32) * 8 * 32;               // float4 per (slice, 32-row quarter): 32 KB
+      const int tile_r = w.tile - g.split_first;
+      const int quarter = (tile_r * 2 + static_cast<int>(cta)) * 4 + q;  // this warp's 32 rows of this tile
+      float4* mine = reinterpret_cast<float4*>(g.split_ws) + (static_cast<size_t>(quarter) * g.split_s + w.slice) * kQuarterF4;
 #pragma unroll 1
       for (int c = 0; c < kBN / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
-        epi.store(g, epoch, row, tn * kBN + c * 32, r, c, warp_smem, lane);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          mine[(c * 8 + j) * 32 + lane] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                      __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->tmem_empty[buf]), 0));
-      if (tm * kBM < g.M) epi.tile_done(g, epoch, tm, tn, q, lane, warp_smem);
+      // All slices of a tile are in flight at once (they form one wave by construction), so the warps that
+      // hold the same 32 rows may wait for one another: when every slice has been delivered, slice s adds
+      // up, IN SLICE ORDER, the 32-column pieces c = s, s + slices, ... and stores them.  (Leaving the sum
+      // to the last warp to arrive made one warp read all slices: 16 x 32 KB at one warp's L2 rate cost
+      // more than the wave the split saves.)
+      const int slices = (num_kb + g.split_kb - 1) / g.split_kb;
+      uint32_t* cnt = g.split_cnt + quarter;
+      bool all_in = true;
+      if (lane == 0) {
+        __threadfence();
+        atomicAdd(cnt, 1u);
+        const uint64_t t0 = globaltimer_ns();
+        uint32_t spins = 0;
+        while (ld_acquire_sys_u32(cnt) < static_cast<uint32_t>(slices)) {
+          if ((++spins & 255u) == 0u && (ctl->abort != 0u || globaltimer_ns() - t0 > budget)) {
+            if (ctl->abort == 0u) ctl->abort = kGemmFlagTimeout;
+            all_in = false;
+            break;
+          }
+        }
+      }
+      all_in = __shfl_sync(0xffffffffu, all_in ? 1 : 0, 0) != 0;
+      if (!all_in) { ok = false; break; }
+      const float4* all = reinterpret_cast<const float4*>(g.split_ws) + static_cast<size_t>(quarter) * g.split_s * kQuarterF4;
+#pragma unroll 1
+      for (int c = w.slice; c < kBN / 32; c += slices) {
+        float acc[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
+#pragma unroll 2
+        for (int sl = 0; sl < slices; ++sl) {
+          float4 v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = __ldcg(all + static_cast<size_t>(sl) * kQuarterF4 + (c * 8 + j) * 32 + lane);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            acc[4 * j] += v[j].x; acc[4 * j + 1] += v[j].y; acc[4 * j + 2] += v[j].z; acc[4 * j + 3] += v[j].w;
+          }
+        }
+        uint32_t r[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(acc[i]);
+        epi.store(g, epoch, row, tn * kBN + c * 32, r, c, warp_smem, lane);
+      }
+      // the last reader leaves the counter clean for the next launch
+      __syncwarp();
+      if (lane == 0 && atomicAdd(cnt, 1u) == static_cast<uint32_t>(2 * slices - 1)) *cnt = 0;
+      if (w.slice == 0 && tm * kBM < g.M) epi.tile_done(g, epoch, tm, tn, q, lane, warp_smem);
     }
     // the single-CTA numbering of CTAs for the epilogues' follow-up pass
     epi.after_tiles(g, epoch, static_cast<int>(blockIdx.x), n_gemm, q, lane, &ctl->abort, warp_smem);

@@ -18,6 +18,7 @@
 // tensor memory is freed and the kernel reports an error word to the host.
 // The reference has no GEMM and no tensor-core code; this exists because the
 // tensor-parallel workload fuses it with the collectives of this library.
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <mutex>
@@ -42,6 +43,9 @@ int pair_mode_from_env() {
 }
 int g_use_pair = pair_mode_from_env();
 uint32_t* g_err_dev[kMaxDevices] = {};  // one error word per device of the process
+float* g_split_ws[kMaxDevices] = {};    // split-K workspace per device (fp32 partial tiles), allocated on first use
+uint32_t* g_split_cnt[kMaxDevices] = {};
+constexpr int kSplitMaxItems = 80;      // K-slices in flight: at most one per CTA pair
 
 }  // namespace
 
@@ -82,6 +86,59 @@ uint32_t* error_word() {
     g_err_dev[dev] = p;
   }
   return g_err_dev[dev];
+}
+
+// Workspace of the split last wave: kSplitMaxItems partial tiles of 256 x 256 fp32 (20 MB) and one
+// counter per 32-row quarter.  Allocated once per device, the first time a shape is split (not under
+// stream capture: call the GEMM once before capturing).  Null when the allocation fails: no split then.
+bool split_workspace(float** ws, uint32_t** cnt) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= kMaxDevices) dev = 0;
+  if (g_split_ws[dev] == nullptr) {
+    float* w = nullptr;
+    uint32_t* c = nullptr;
+    if (cudaMalloc(&w, size_t(kSplitMaxItems) * 256 * 256 * 4) != cudaSuccess ||
+        cudaMalloc(&c, size_t(kSplitMaxItems) * 8 * 4) != cudaSuccess) {
+      (void)cudaGetLastError();
+      if (w) cudaFree(w);
+      return false;
+    }
+    cudaMemset(c, 0, size_t(kSplitMaxItems) * 8 * 4);
+    g_split_ws[dev] = w;
+    g_split_cnt[dev] = c;
+  }
+  *ws = g_split_ws[dev];
+  *cnt = g_split_cnt[dev];
+  return true;
+}
+
+// Split-K plan of the CTA-pair kernel: tiles2 tiles on n_pairs pairs, num_kb k-blocks per tile.  When
+// the last wave holds at most half as many tiles as there are pairs, each of its tiles is cut into at
+// most 8 slices of at least 4 k-blocks so that all slices still form ONE wave (their warps wait for one
+// another, which is only safe because they are all resident at the same time).  Returns false for "no split".
+bool plan_split(int tiles2, int n_pairs, int num_kb, int* first, int* s, int* kb) {
+  const char* e = getenv("MINI_NCCL_GEMM_SPLIT_K");
+  if (e != nullptr && *e == '0') return false;
+  if (n_pairs < 2 || tiles2 <= n_pairs) return false;        // a single wave: nothing to balance
+  const int rem = tiles2 % n_pairs;
+  if (rem == 0 || 2 * rem > n_pairs) return false;
+  int slices = n_pairs / rem;
+  if (slices > kBN / 32) slices = kBN / 32;                     // a slice's warp sums whole 32-column pieces
+  if (slices > num_kb / 4) slices = num_kb / 4;
+  if (slices * rem > kSplitMaxItems) slices = kSplitMaxItems / rem;
+  if (slices < 2) return false;
+  const int per = (num_kb + slices - 1) / slices;
+  *first = tiles2 - rem;
+  *kb = per;
+  *s = (num_kb + per - 1) / per;                                // no empty slice
+  if (*s < 2) return false;
+  // Measured on B200: a 256 x 256 pair tile takes about 3 us + 0.33 us per k-block, and cutting it costs
+  // about 7 us (partial sums to the workspace, the meeting of the slices, the sum): 4096 x 3584 x 4096
+  // gains 12 us with 8 slices, 4096 x 4096 x 1792 loses 1 us with 2, 4096 x 4096 x 512 loses 4 us.
+  const long tile_ns = 3000 + 330L * num_kb;
+  return tile_ns * (*s - 1) / *s > 9000;
 }
 
 int pick_tile_n(int M, int N, int ctas, bool allow_224) {
@@ -177,6 +234,13 @@ MNCCL_EXPORT int mncclGemmBf16(const void* A, const void* B, void* C, int M, int
     const int tiles2 = ((M + 2 * kBM - 1) / (2 * kBM)) * ((N + kBN - 1) / kBN);
     int grid = 2 * tiles2;
     if (grid > (sm_count() & ~1)) grid = sm_count() & ~1;
+    const int pairs = std::min(grid / 2, max_pairs<StoreEpilogue<false>>());
+    int first = 0, slices = 0, per = 0;
+    if (plan_split(tiles2, pairs, (K + kBK - 1) / kBK, &first, &slices, &per) && split_workspace(&g.split_ws, &g.split_cnt)) {
+      g.split_first = first;
+      g.split_s = slices;
+      g.split_kb = per;
+    }
     e = out_f32 ? launch_pair(ta, tb, g, StoreEpilogue<true>{}, grid, stream) : launch_pair(ta, tb, g, StoreEpilogue<false>{}, grid, stream);
   } else {
     const int bn = pick_tile_n(M, N, sm_count(), true);
@@ -203,6 +267,20 @@ MNCCL_EXPORT void mncclGemmSetPairMode(int mode) { set_pair_mode(mode); }
 MNCCL_EXPORT void mncclGemmPlan(int M, int N, int ctas, int narrow, int* tile_n, int* pair) {
   if (tile_n) *tile_n = pick_tile_n(M, N, ctas, narrow != 0);
   if (pair) *pair = want_pair(M, N, ctas) ? 1 : 0;
+}
+
+// The split-K plan of the CTA-pair kernel for an M x N x K product on `pairs` CTA pairs, without launching
+// anything (needs no GPU): returns 1 and the first split work item, the slices per tile and the k-blocks
+// per slice when the last, partial wave is cut along K, else 0.
+MNCCL_EXPORT int mncclGemmSplitPlan(int M, int N, int K, int pairs, int* first, int* slices, int* kb_per_slice) {
+  if (M <= 0 || N <= 0 || K <= 0 || pairs <= 0) return 0;
+  const int tiles2 = ((M + 2 * kBM - 1) / (2 * kBM)) * ((N + kBN - 1) / kBN);
+  int f = 0, s = 0, k = 0;
+  if (!plan_split(tiles2, pairs, (K + kBK - 1) / kBK, &f, &s, &k)) return 0;
+  if (first) *first = f;
+  if (slices) *slices = s;
+  if (kb_per_slice) *kb_per_slice = k;
+  return 1;
 }
 
 // The tiles worker `worker` of `n_workers` visits, in order, exactly as the kernels walk them (host

@@ -53,7 +53,38 @@ struct GemmArgs {
   // at indices 2..5, through which a failed wait and the kernel's start / end reach the watchdog.
   const volatile uint32_t* comm_abort;
   volatile uint32_t* comm_progress;
+  // Split-K of the last, partial wave of the CTA-pair kernel (plain store epilogue only; 0 = off).
+  // Work items [0, split_first) are whole 256 x 256 tiles; each of the remaining tiles is cut along K
+  // into split_s slices of split_kb k-blocks, one work item each, so that the pairs a partial wave would
+  // leave idle share its tiles.  A slice's fp32 accumulators go to split_ws; the last epilogue warp to
+  // arrive for its 32 rows (split_cnt) adds the slices IN SLICE ORDER and stores the result.
+  int split_first, split_s, split_kb;
+  float* split_ws;
+  uint32_t* split_cnt;
 };
+
+// One unit of work of the pair kernel: a whole tile, or one K-slice of a tile of the last wave.
+struct PairWork {
+  int tile, kb0, kb1, slice;
+  bool split;
+};
+__host__ __device__ __forceinline__ int pair_work_items(const GemmArgs& g, int num_tiles) {
+  return g.split_s > 1 ? g.split_first + (num_tiles - g.split_first) * g.split_s : num_tiles;
+}
+__host__ __device__ __forceinline__ PairWork pair_work(const GemmArgs& g, int t, int num_kb) {
+  PairWork w;
+  if (g.split_s <= 1 || t < g.split_first) {
+    w.tile = t; w.kb0 = 0; w.kb1 = num_kb; w.slice = 0; w.split = false;
+  } else {
+    const int u = t - g.split_first;
+    w.tile = g.split_first + u / g.split_s;
+    w.slice = u % g.split_s;
+    w.kb0 = w.slice * g.split_kb;
+    w.kb1 = w.kb0 + g.split_kb < num_kb ? w.kb0 + g.split_kb : num_kb;
+    w.split = true;
+  }
+  return w;
+}
 
 // Codes a CTA leaves in its shared abort flag (and the device error word).
 enum GemmAbort : uint32_t { kGemmOk = 0, kGemmMbarTimeout = 1, kGemmRowsTimeout = 2, kGemmFlagTimeout = 3, kGemmAborted = 4 };

@@ -237,6 +237,28 @@ def test_planner_pipelined_kernel_for_large_ordinary_buffers(lib):
     assert plan(lib, 8, 1 << 26, mode=1)["algo"] == "twoshot"                        # only AllReduce is pipelined
 
 
+def test_gemm_split_k_plan_of_the_last_wave(lib):
+    """Host arithmetic of the CTA-pair kernel's split-K: only a last wave that leaves at least half of the
+    pairs idle is cut, and only where the measured cost model says the cut pays; every slice has at least
+    4 k-blocks, all slices fit one wave, none is empty."""
+    if not hasattr(lib, "mncclGemmSplitPlan"):
+        pytest.skip("library built without the GEMM translation unit")
+    f, s, k = C.c_int(), C.c_int(), C.c_int()
+    plan_of = lambda M, N, K, pairs=74: (lib.mncclGemmSplitPlan(M, N, K, pairs, C.byref(f), C.byref(s), C.byref(k)), f.value, s.value, k.value)
+    ok, first, slices, per = plan_of(4096, 3584, 4096)           # 224 tiles on 74 pairs: 3 waves + 2 tiles
+    assert ok == 1 and first == 222 and slices == 8 and per == 8
+    assert plan_of(8192, 8192, 8192)[0] == 0                      # 1024 tiles: the last wave holds 62 of 74
+    assert plan_of(4096, 4096, 1792)[0] == 0                      # 3 waves + 34 tiles: two slices would save less than the cut costs
+    assert plan_of(4096, 4096, 512)[0] == 0
+    assert plan_of(4096, 9216, 1792)[0] == 0                      # 576 tiles = 7 waves + 58: more than half of the pairs busy
+    assert plan_of(2048, 2048, 4096)[0] == 0                      # 64 tiles: a single wave
+    ok, first, slices, per = plan_of(4096, 3584, 256)             # 4 k-blocks: too short to cut
+    assert ok == 0
+    assert plan_of(4096, 4864, 1024, 74)[0] == 0                  # 16 k-blocks: the tile is shorter than the cut's cost
+    ok, first, slices, per = plan_of(4096, 4864, 4096, 74)        # 16 x 19 = 304 tiles = 4 waves + 8; 64 k-blocks
+    assert ok == 1 and first == 296 and slices == 8 and per == 8 and slices * 8 <= 74
+
+
 def test_gemm_host_plan_picks_tiles_and_cta_pairs():
     """Host-side choice of the GEMM kernel (no GPU needed): CTA pairs for products whose 256 x 256
     tiles fill the SM pairs, narrower single-CTA tiles for small products, and the pinned modes."""
