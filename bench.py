@@ -211,8 +211,10 @@ def main():
         bad_any = int(max_over_ranks(float(bad)))
         checked = {"cases": ar["cases"] + gm["cases"], "failed": bad_any, "nvls": ar["nvls"],
                    "fused_gemm_cases": gm["cases"], "failures": (ar["failures"] + gm["failures"])[:8],
+                   "notes": gm.get("notes", []),
                    "rule": "P2P algorithms bit-exact against the rank-ordered host oracle; NVLS within tolerance on random "
-                           "data and bit-exact on exactly representable data; fused GEMMs bit-exact on integer operands"}
+                           "data and bit-exact on exactly representable data; fused GEMMs bit-exact on integer operands "
+                           "(GEMM->reduce-scatter summed by the switch: ties may round to the other bf16 neighbour)"}
         sync_all()
 
     # ---- sweep (ours vs NCCL), attached for context

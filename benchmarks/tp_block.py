@@ -56,7 +56,7 @@ def main():
         ms_fused = _time_loop(lambda: mlp.forward(), 30, 5, world)
         res[f"ncomm{n_comm}"] = {"ag_gemm_us": round(ms_ag * 1e3, 1), "gemm_rs_us": round(ms_rs * 1e3, 1),
                                  "mlp_fused_us": round(ms_fused * 1e3, 1), "rel_err_vs_unfused": round(err, 5),
-                                 "status": gemm_status()}
+                                 "rs_in_switch": bool(mlp.gemm_rs.in_switch), "status": gemm_status()}
         if n_comm == 0:
             ms_unf = _time_loop(lambda: mlp.forward_unfused(x), 30, 5, world)
             res["mlp_cublas_nccl_us"] = round(ms_unf * 1e3, 1)

@@ -87,6 +87,12 @@ struct RsEpilogue {
   int ldo;
   int bn;                            // tile width of this launch (256 or 192)
   int tiled;                         // staging layout: 0 row-major [rows_per_rank][N] (default), 1 tile by tile (MINI_NCCL_RS_TILED=1)
+  // Switch mode (mc_stage != null): the partial tiles stay in THIS rank's staging, laid out [2][M][N], and
+  // the owner of a row block sums all ranks' copies with one multimem.ld_reduce through the NVSwitch
+  // multicast mapping of the staging: a GPU receives M / nranks reduced rows instead of nranks - 1 partial
+  // copies, and the sum is taken while the other tiles are still being computed.
+  const char* mc_stage;              // multicast address of the staging (same offset on every rank), or null
+  uint32_t* work;                    // ticket counter of the reduction items (reset by the last CTA out)
 
   // One source rank's partial sums of the rows one rank owns.  Row-major by default.  The tiled
   // layout (a 128 x bn tile is one contiguous block) looked better in a two-GPU store test (compact
@@ -128,8 +134,10 @@ struct RsEpilogue {
     const int row_base = row - lane;        // first row of this warp's 32
     const int col_base = col - 32;          // first of the 64 columns
     const int owner = row_base / rows_per_rank;   // a 128-row tile never straddles owners
-    __nv_bfloat16* slot = reinterpret_cast<__nv_bfloat16*>(stage[owner]) +
-                          (static_cast<size_t>(epoch & 1u) * nranks + rank) * slot_elems(g);
+    const bool sw = mc_stage != nullptr;
+    __nv_bfloat16* slot = sw ? reinterpret_cast<__nv_bfloat16*>(stage[rank]) + static_cast<size_t>(epoch & 1u) * g.M * g.N
+                             : reinterpret_cast<__nv_bfloat16*>(stage[owner]) +
+                                   (static_cast<size_t>(epoch & 1u) * nranks + rank) * slot_elems(g);
 #pragma unroll
     for (int it = 0; it < 8; ++it) {
       const int rr = it * 4 + (lane >> 3);  // 4 rows per instruction
@@ -138,7 +146,8 @@ struct RsEpilogue {
       const int gcol = col_base + seg * 8;
       if (grow < g.M && gcol < g.N) {
         const uint4 v = *reinterpret_cast<const uint4*>(warp_smem + rr * kEpiRowBytes + seg * 16);
-        *reinterpret_cast<uint4*>(slot + elem_offset(g, grow - owner * rows_per_rank, gcol)) = v;
+        const size_t off = sw ? static_cast<size_t>(grow) * g.N + gcol : elem_offset(g, grow - owner * rows_per_rank, gcol);
+        *reinterpret_cast<uint4*>(slot + off) = v;
       }
     }
     __syncwarp();  // the scratch is reused by the next pair of pieces
@@ -164,6 +173,10 @@ struct RsEpilogue {
   // of ranks: NR sources x U vectors.
   __device__ __forceinline__ void after_tiles(const GemmArgs& g, uint32_t epoch, int cta, int n_cta, int q, int lane,
                                               volatile uint32_t* abort_flag, uint8_t* /*warp_smem*/) const {
+    if (mc_stage != nullptr) {
+      reduce_switch<128, false>(g, epoch, ((q + 2) & 3) * 32 + lane, abort_flag);
+      return;
+    }
     if (nranks <= 1) reduce_owned<1, 16>(g, epoch, cta, n_cta, q, lane, abort_flag);
     else if (nranks <= 2) reduce_owned<2, 16>(g, epoch, cta, n_cta, q, lane, abort_flag);
     else if (nranks <= 4) reduce_owned<4, 8>(g, epoch, cta, n_cta, q, lane, abort_flag);
@@ -239,7 +252,67 @@ struct RsEpilogue {
     }
   }
 
-  __device__ __forceinline__ void comm_cta(const GemmArgs&, uint32_t, int, int, volatile uint32_t*, uint8_t*, uint32_t) const {}
+  // Switch mode.  Items are 32 rows x one tile width of the rows this rank owns, numbered in the order
+  // the tiles are finished (every rank walks the tiles column by column, so all partial copies of a tile
+  // appear at about the same time and every wave holds rows of every owner).  Whoever has nothing else
+  // to do takes the next item from a counter: the communication CTAs from the start, the epilogue warps
+  // of a compute CTA once its tiles are done.  An item waits (bounded) for the tile's flag from every
+  // rank, then each thread sums 16 bytes of all ranks' copies in the switch (fp32 accumulation, one
+  // rounding to bf16) and writes them to the output.  NT threads take part; WHOLE_CTA picks the barrier.
+  template <int NT, bool WHOLE_CTA>
+  __device__ __forceinline__ void reduce_switch(const GemmArgs& g, uint32_t epoch, int tid, volatile uint32_t* abort_flag) const {
+    __shared__ int s_item;
+    __shared__ int s_stop;
+    const int tiles_n = (g.N + bn - 1) / bn;
+    const int tiles_m_local = rows_per_rank / kBM;
+    constexpr int kParts = 4, kRows = kBM / kParts;
+    constexpr int U = (kRows * (kBN / 8) + NT - 1) / NT;       // 16-byte vectors per thread and item
+    const int items = tiles_m_local * tiles_n * kParts;
+    const char* mc = mc_stage + static_cast<size_t>(epoch & 1u) * g.M * g.N * sizeof(__nv_bfloat16);
+    for (;;) {
+      if (tid == 0) s_item = static_cast<int>(atomicAdd(work, 1u));
+      if (WHOLE_CTA) __syncthreads(); else epilogue_warps_sync();
+      const int item = s_item;
+      if (item >= items) break;                                // the same for every thread
+      const int tile = item / kParts, part = item - tile * kParts;
+      const int tn = tile / tiles_m_local, ltm = tile - tn * tiles_m_local;
+      if (tid < nranks) wait_flag_sys(flags[rank] + (static_cast<size_t>(tid) * tiles_m_local + ltm) * tiles_n + tn, epoch, abort_flag, g);
+      if (WHOLE_CTA) __syncthreads(); else epilogue_warps_sync();
+      if (tid == 0) s_stop = *abort_flag != 0u ? 1 : 0;
+      if (WHOLE_CTA) __syncthreads(); else epilogue_warps_sync();  // also: s_item has been read by everyone
+      if (s_stop) break;
+      const int lrow0 = ltm * kBM + part * kRows;              // within this rank's rows
+      const int col0 = tn * bn;
+      const int vec_per_row = min(bn, g.N - col0) / 8;
+      const int nvec = kRows * vec_per_row;
+      uint4 x[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = tid + u * NT;
+        if (v < nvec) {
+          const int rr = lrow0 + v / vec_per_row, cc = col0 + (v % vec_per_row) * 8;
+          const char* src = mc + (static_cast<size_t>(rank * rows_per_rank + rr) * g.N + cc) * sizeof(__nv_bfloat16);
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(x[u].x), "=r"(x[u].y), "=r"(x[u].z), "=r"(x[u].w)
+                       : "l"(src)
+                       : "memory");
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = tid + u * NT;
+        if (v < nvec) {
+          const int rr = lrow0 + v / vec_per_row, cc = col0 + (v % vec_per_row) * 8;
+          *reinterpret_cast<uint4*>(out + static_cast<size_t>(rr) * ldo + cc) = x[u];
+        }
+      }
+    }
+  }
+
+  __device__ __forceinline__ void comm_cta(const GemmArgs& g, uint32_t epoch, int /*cta*/, int /*n_comm*/,
+                                           volatile uint32_t* abort_flag, uint8_t*, uint32_t) const {
+    if (mc_stage != nullptr) reduce_switch<kThreads, true>(g, epoch, static_cast<int>(threadIdx.x), abort_flag);
+  }
 };
 
 // ------------------------------------------------------------------ all-gather -> GEMM
@@ -439,7 +512,7 @@ MNCCL_EXPORT size_t mncclAgGemmBarWords(int nranks, int n_comm) { return size_t(
 // (Communicator.peer_pointers); state: two zero-initialised device words of this rank.
 static int gemm_rs_launch(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldo, int rank,
                           int nranks, void* const* stage_peers, void* const* flag_peers, uint32_t* state,
-                          const CommBinding& cb, cudaStream_t stream) {
+                          const CommBinding& cb, cudaStream_t stream, const void* mc_stage = nullptr, int n_comm_ctas = 0) {
   if (!A || !B || !out || !stage_peers || !flag_peers || !state) return -1;
   if (!check_common(M, N, K, rank, nranks, "GEMM->reduce-scatter")) return -2;
   if (lda == 0) lda = K;
@@ -448,9 +521,17 @@ static int gemm_rs_launch(const void* A, const void* B, void* out, int M, int N,
   CUtensorMap ta, tb;
   std::string why;
   // CTA pairs need every rank's rows to be whole 256-row tiles (the rasterisation works on pairs of m-tiles)
-  const bool pair = ((M / nranks) % (2 * kBM)) == 0 && want_pair(M, N, sm_count()) &&
+  const bool sw = mc_stage != nullptr && nranks > 1;
+  if (sw && (ldo % 8 != 0 || (reinterpret_cast<uintptr_t>(out) & 15u) != 0)) {
+    fprintf(stderr, "[Mini-NCCL] GEMM->reduce-scatter through the switch: needs ldo a multiple of 8 and out 16-byte aligned\n");
+    return -2;
+  }
+  // switch mode: a few CTAs only sum finished tiles (16 unless told otherwise; whole clusters)
+  int n_comm = sw ? (n_comm_ctas > 0 ? ((n_comm_ctas + 1) & ~1) : 16) : 0;
+  if (n_comm > sm_count() / 2) n_comm = (sm_count() / 2) & ~1;
+  const bool pair = ((M / nranks) % (2 * kBM)) == 0 && want_pair(M, N, sm_count() - n_comm) &&
                     2 * max_pairs<RsEpilogue>() >= (sm_count() & ~1);
-  const int bn = pair ? kBN : pick_tile_n(M, N, sm_count(), false);
+  const int bn = pair ? kBN : pick_tile_n(M, N, sm_count() - n_comm, false);
   if (!make_tensor_map_bf16(&ta, A, M, K, lda, kBM, kBK, &why) ||
       !make_tensor_map_bf16(&tb, B, N, K, ldb, pair ? kBN / 2 : bn, kBK, &why)) {
     fprintf(stderr, "[Mini-NCCL] GEMM->reduce-scatter: %s\n", why.c_str());
@@ -474,6 +555,9 @@ static int gemm_rs_launch(const void* A, const void* B, void* out, int M, int N,
     epi.stage[r] = static_cast<char*>(stage_peers[r]);
     epi.flags[r] = static_cast<uint32_t*>(flag_peers[r]);
   }
+  epi.mc_stage = sw ? static_cast<const char*>(mc_stage) : nullptr;
+  epi.work = state + 2;
+  if (sw) epi.tiled = 0;
   GemmArgs g{};
   g.M = M;
   g.N = N;
@@ -483,18 +567,28 @@ static int gemm_rs_launch(const void* A, const void* B, void* out, int M, int N,
   g.comm_abort = cb.abort_word;
   g.comm_progress = cb.progress;
   const int tiles_m_local = epi.rows_per_rank / kBM;
-  g.group_m = tiles_m_local;
-  g.m_tile_rotate = ((rank + 1) % nranks) * tiles_m_local;  // next rank's rows first, own rows last
+  if (sw) {
+    g.group_m = M / kBM;                                     // column by column, the same on every rank
+    g.m_tile_rotate = 0;
+  } else {
+    g.group_m = tiles_m_local;
+    g.m_tile_rotate = ((rank + 1) % nranks) * tiles_m_local;  // next rank's rows first, own rows last
+  }
   g.epoch_ptr = state;
   g.ticket_ptr = state + 1;
+  g.work_ptr = sw ? state + 2 : nullptr;
   const int tiles = (M / kBM) * ((N + bn - 1) / bn);
   cudaError_t e;
   if (pair) {
-    const int grid = tiles < (sm_count() & ~1) ? tiles : (sm_count() & ~1);  // tiles is even: M / kBM is
-    e = launch_pair(ta, tb, g, epi, grid, stream);
+    const int sms = (sm_count() & ~1) - n_comm;
+    const int n_gemm = tiles < sms ? tiles : sms;             // tiles is even: M / kBM is
+    if (sw) g.n_gemm_ctas = n_gemm;
+    e = launch_pair(ta, tb, g, epi, n_gemm + n_comm, stream);
   } else {
-    const int grid = tiles < sm_count() ? tiles : sm_count();
-    e = launch(ta, tb, g, epi, grid, stream, bn);
+    const int sms = sm_count() - n_comm;
+    const int n_gemm = tiles < sms ? tiles : sms;
+    if (sw) g.n_gemm_ctas = n_gemm;
+    e = launch(ta, tb, g, epi, n_gemm + n_comm, stream, bn);
   }
   return e == cudaSuccess ? 0 : static_cast<int>(e) + 1000;
 }
@@ -515,6 +609,20 @@ MNCCL_EXPORT int mncclGemmReduceScatterBf16Comm(const void* A, const void* B, vo
                                                 size_t comm_handle_bytes, cudaStream_t stream) {
   return gemm_rs_launch(A, B, out, M, N, K, lda, ldb, ldo, rank, nranks, stage_peers, flag_peers, state,
                         bind_comm(comm_handle, comm_handle_bytes), stream);
+}
+
+// The same with the sum taken in the NVSwitch: `mc_stage` is the multicast address of the staging
+// (mncclMemPeerPointers); state needs three zero-initialised words; n_comm_ctas CTAs only sum finished
+// tiles (0 = 16).  Partial sums are bf16, the switch adds them in fp32 in ITS order and rounds once, so
+// the result may differ from the peer-to-peer kernel's in the last bit.  With mc_stage null or one
+// rank this is mncclGemmReduceScatterBf16Comm.
+MNCCL_EXPORT int mncclGemmReduceScatterBf16Switch(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb,
+                                                  int ldo, int rank, int nranks, void* const* stage_peers,
+                                                  void* const* flag_peers, uint32_t* state, const void* mc_stage,
+                                                  int n_comm_ctas, const void* comm_handle, size_t comm_handle_bytes,
+                                                  cudaStream_t stream) {
+  return gemm_rs_launch(A, B, out, M, N, K, lda, ldb, ldo, rank, nranks, stage_peers, flag_peers, state,
+                        bind_comm(comm_handle, comm_handle_bytes), stream, mc_stage, n_comm_ctas);
 }
 
 // C[M, N] = X[M, K] * B[N, K]^T where X is the row-wise concatenation of every rank's shard.

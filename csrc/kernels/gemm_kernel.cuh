@@ -52,6 +52,7 @@ __device__ __forceinline__ void finish_epoch(const GemmArgs& g, uint32_t epoch) 
   const uint32_t t = atomicAdd(g.ticket_ptr, 1u);
   if (t == gridDim.x - 1) {
     *g.ticket_ptr = 0;
+    if (g.work_ptr != nullptr) *g.work_ptr = 0;
     *g.epoch_ptr = epoch;
     __threadfence();
     if (g.comm_progress != nullptr && g.err != nullptr) {

@@ -48,6 +48,7 @@ struct GemmArgs {
   // and its last CTA (ticket) stores it back, so a captured launch replays correctly.
   uint32_t* epoch_ptr;
   uint32_t* ticket_ptr;
+  uint32_t* work_ptr;    // optional work counter of an epilogue, cleared by the last CTA out
   // The communicator's failure model (null for the plain GEMM): its host-mapped abort word, which
   // every wait on a peer polls, and its host-mapped progress words {.., status, detail, started, done}
   // at indices 2..5, through which a failed wait and the kernel's start / end reach the watchdog.

@@ -109,6 +109,8 @@ def lib() -> C.CDLL:
         sig("mncclAllGatherGemmBf16", i32, P(vp), vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, P(vp), P(vp), vp, i32, vp)
         sig("mncclAllGatherGemmSwiGluBf16", i32, P(vp), vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, P(vp), P(vp), vp, i32, vp)
         sig("mncclGemmReduceScatterBf16Comm", i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, P(vp), P(vp), vp, C.c_char_p, sz, vp)
+        sig("mncclGemmReduceScatterBf16Switch", i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, P(vp), P(vp), vp, vp, i32,
+            C.c_char_p, sz, vp)
         sig("mncclAllGatherGemmBf16Comm", i32, P(vp), vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, P(vp), P(vp), vp, i32, i32,
             C.c_char_p, sz, vp)
         sig("mncclGemmProbeFlagWait", i32, u64, i32, P(u32), P(u32), P(u32))

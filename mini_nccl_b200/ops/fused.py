@@ -1,7 +1,10 @@
 """The two tensor-parallel fusions as Python objects that own their workspaces.
 
-``GemmReduceScatter``: ``out[M/R, N] = reduce_scatter(A_r[M, K_r] @ B_r[N, K_r].T)`` -- one kernel;
-tiles are pushed to their owner over NVLink while the remaining tiles are computed.
+``GemmReduceScatter``: ``out[M/R, N] = reduce_scatter(A_r[M, K_r] @ B_r[N, K_r].T)`` -- one kernel.
+Where the NVSwitch can reduce (NVLS), the partial tiles stay on their rank and the owner of a row block
+sums all ranks' copies in the switch (``multimem.ld_reduce``) while the remaining tiles are computed;
+otherwise (two GPUs without a multicast mapping, ``MINI_NCCL_NVLS_ENABLE=0``, ``MINI_NCCL_RS_SWITCH=0``)
+tiles are pushed to their owner over NVLink and summed there in rank order.
 ``AllGatherGemm``: ``C[M, N_r] = all_gather(X_r)[M, K] @ B_r[N_r, K].T`` -- one kernel; a few CTAs push
 the local shard to the peers while the others already compute on the local rows.
 
@@ -16,6 +19,7 @@ times the kernel like a collective, and a wait that gives up fails the communica
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 from .._lib import lib
 
@@ -74,6 +78,17 @@ class GemmReduceScatter:
         self._stage_peers = _peers(comm, self.stage)
         self._flag_peers = _peers(comm, self.flags)
         self._handle = comm.device_handle_bytes()
+        # multicast address of the staging: the in-switch sum needs it (0: peer-to-peer kernel)
+        self._mc = 0
+        if R > 1 and os.environ.get("MINI_NCCL_RS_SWITCH", "1") != "0" and hasattr(L, "mncclGemmReduceScatterBf16Switch"):
+            self._mc = comm.peer_pointers(self.stage)[1]
+        # CTAs that only sum finished tiles in the switch form (0: the kernel's default of 16)
+        self.n_comm_ctas = int(os.environ.get("MINI_NCCL_RS_COMM_CTAS", "0"))
+
+    @property
+    def in_switch(self) -> bool:
+        """True when the sum of the partial tiles is taken by the NVSwitch."""
+        return self._mc != 0
 
     def __call__(self, a, b, out=None, stream=None):
         """``a [M, K_r]``, ``b [N, K_r]`` bf16 -> ``out [M / ranks, N]`` bf16 (this rank's rows of the sum)."""
@@ -88,10 +103,17 @@ class GemmReduceScatter:
             out = torch.empty((M // self.comm.size, N), dtype=torch.bfloat16, device=a.device)
         s = stream.cuda_stream if stream is not None else torch.cuda.current_stream().cuda_stream
         _check_comm(self.comm)
-        rc = _native().mncclGemmReduceScatterBf16Comm(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, a.shape[1], a.stride(0),
-                                                      b.stride(0), out.stride(0), self.comm.rank, self.comm.size,
-                                                      self._stage_peers, self._flag_peers, self.state.data_ptr(),
-                                                      self._handle, len(self._handle), s)
+        if self._mc and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
+            rc = _native().mncclGemmReduceScatterBf16Switch(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, a.shape[1],
+                                                            a.stride(0), b.stride(0), out.stride(0), self.comm.rank,
+                                                            self.comm.size, self._stage_peers, self._flag_peers,
+                                                            self.state.data_ptr(), self._mc, self.n_comm_ctas,
+                                                            self._handle, len(self._handle), s)
+        else:
+            rc = _native().mncclGemmReduceScatterBf16Comm(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, a.shape[1],
+                                                          a.stride(0), b.stride(0), out.stride(0), self.comm.rank,
+                                                          self.comm.size, self._stage_peers, self._flag_peers,
+                                                          self.state.data_ptr(), self._handle, len(self._handle), s)
         if rc != 0:
             raise RuntimeError(f"mncclGemmReduceScatterBf16 failed with code {rc}")
         return out

@@ -468,7 +468,7 @@ def gpu_tp(rank, n, kw):
     assert res["failed"] == 0, res["failures"]
     comm.barrier()
     comm.destroy()
-    return {"rank": rank, "worst": worst, "oracle_cases": res["cases"]}
+    return {"rank": rank, "worst": worst, "oracle_cases": res["cases"], "rs_in_switch": bool(rs.in_switch)}
 
 
 def gpu_tp_stall(rank, n, kw):

@@ -72,10 +72,16 @@ def test_hera_bootstrap_and_stall_bounded_failure(free_port, lib):
 
 
 @pytest.mark.multigpu(2)
-def test_fused_tensor_parallel_kernels(free_port):
+@pytest.mark.parametrize("in_switch", [1, 0])
+def test_fused_tensor_parallel_kernels(free_port, in_switch):
+    """Both forms of GEMM -> reduce-scatter: partial tiles summed by the switch (where it can), or pushed
+    to their owner and summed there."""
     n = 2
-    res = run_ranks("gpu_tp", n, {"M": 1024, "N": 1024, "K": 512}, {"MINI_NCCL_BOOTSTRAP_PORT": free_port}, timeout=300)
+    res = run_ranks("gpu_tp", n, {"M": 1024, "N": 1024, "K": 512},
+                    {"MINI_NCCL_BOOTSTRAP_PORT": free_port, "MINI_NCCL_RS_SWITCH": in_switch}, timeout=300)
     assert len(res) == n and all(r["worst"] < 3e-2 for r in res)
+    if not in_switch:
+        assert not any(r["rs_in_switch"] for r in res)
 
 
 @pytest.mark.multigpu(2)
