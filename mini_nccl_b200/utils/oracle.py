@@ -131,10 +131,11 @@ def oracle_gemm_bf16(a_bits: np.ndarray, b_bits: np.ndarray, out_fp32: bool = Fa
     return acc if out_fp32 else f32_to_bf16_bits(acc)
 
 
-def oracle_gemm_reduce_scatter(a_bits: list[np.ndarray], b_bits: list[np.ndarray], rank: int) -> np.ndarray:
+def oracle_gemm_reduce_scatter(a_bits: list[np.ndarray], b_bits: list[np.ndarray], rank: int, return_sum: bool = False):
     """GEMM -> reduce-scatter as the fused kernel computes it: every rank's partial product is rounded
     to bf16 before it travels, the owner adds the partial tiles in RANK ORDER in fp32 and rounds the sum
-    once.  ``a_bits[r]`` is ``[M, K_r]``, ``b_bits[r]`` is ``[N, K_r]``; returns the rows ``rank`` owns."""
+    once.  ``a_bits[r]`` is ``[M, K_r]``, ``b_bits[r]`` is ``[N, K_r]``; returns the rows ``rank`` owns
+    (with ``return_sum`` also the fp32 sum before its rounding)."""
     n = len(a_bits)
     M = a_bits[0].shape[0]
     if M % n:
@@ -145,7 +146,7 @@ def oracle_gemm_reduce_scatter(a_bits: list[np.ndarray], b_bits: list[np.ndarray
     for r in range(n):
         partial = bf16_bits_to_f32(oracle_gemm_bf16(a_bits[r][rows], b_bits[r]))  # what rank r sends
         acc = partial.copy() if acc is None else (acc + partial).astype(np.float32)
-    return f32_to_bf16_bits(acc)
+    return (f32_to_bf16_bits(acc), acc) if return_sum else f32_to_bf16_bits(acc)
 
 
 def oracle_all_gather_gemm(x_shards_bits: list[np.ndarray], b_bits: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
