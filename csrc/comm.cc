@@ -60,7 +60,19 @@ uint64_t host_hash() {
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-constexpr size_t kShmBytes = 4096;
+// One export table per rank behind the first 4 KB of the shared page (lazy direct access).
+struct AutoExport {
+  uint64_t id, base, size;
+  cudaIpcMemHandle_t handle;
+};
+struct AutoExportTable {
+  uint32_t count;   // entries published so far (only grows; written after the entry)
+  uint32_t pad;
+  AutoExport e[kAutoSlots];
+};
+constexpr size_t kAutoShmOffset = 4096;
+constexpr int kAutoShmRanks = 8;
+constexpr size_t kShmBytes = 4096 + ((kAutoShmRanks * sizeof(AutoExportTable) + 4095) / 4096) * 4096;
 constexpr int kProgressWords = 16;  // per local rank, 64 bytes
 
 enum class MemKind { Device, PinnedHost, PlainHost };
@@ -354,6 +366,8 @@ void Comm::init_gpu_plane() {
   off += align_up(sizeof(LocalState), 4096);
   dev_.off_pipe = off;
   off += align_up(sizeof(PipeCtl), 4096);
+  dev_.off_auto = off;
+  off += align_up(sizeof(AutoCtl), 4096);
   dev_.off_ll = off;
   off += 2 * size_t(size_) * caps_.ll_slot_bytes;
   dev_.off_inbox = off;
@@ -371,6 +385,28 @@ void Comm::init_gpu_plane() {
   for (int r = 0; r < size_; ++r) dev_.ctrl[r] = static_cast<char*>(ctrl_->peer[r]);
   dev_.ctrl_mc = static_cast<char*>(ctrl_->mc);
   caps_.nvls = ctrl_->mc != nullptr;
+
+  // lazy direct access: needs the page shared by the host's ranks and a table the kernels can read
+  if (cfg_.auto_map && shm_map_ && shm_registered_ && size_ <= kAutoShmRanks && local_size_ == size_) {
+    void* tab = nullptr;
+    if (cudaHostAlloc(&tab, sizeof(AutoMapEntry) * kMaxRanks * kAutoSlots, cudaHostAllocMapped) == cudaSuccess) {
+      memset(tab, 0, sizeof(AutoMapEntry) * kMaxRanks * kAutoSlots);
+      void* dtab = nullptr;
+      if (cudaHostGetDevicePointer(&dtab, tab, 0) == cudaSuccess && dtab) {
+        auto_map_host_ = static_cast<AutoMapEntry*>(tab);
+        dev_.auto_map = static_cast<const AutoMapEntry*>(dtab);
+        auto_shm_ = static_cast<char*>(shm_map_) + kAutoShmOffset;
+        memset(auto_shm_ + rank_ * sizeof(AutoExportTable), 0, sizeof(AutoExportTable));
+        auto_seen_.assign(size_, 0);
+        auto_mapped_.assign(size_, 0);
+      } else {
+        (void)cudaGetLastError();
+        cudaFreeHost(tab);
+      }
+    } else {
+      (void)cudaGetLastError();
+    }
+  }
 
   if (cfg_.watchdog_enable && dev_.host_progress) {
     watchdog_.reset(new Watchdog(progress_host_, abort_host_, cfg_.watchdog_timeout_ms, rank_));
@@ -551,6 +587,8 @@ Comm::~Comm() {
   }
   for (auto& kv : ipc_cache_) cudaIpcCloseMemHandle(kv.second.base);
   ipc_cache_.clear();
+  if (auto_map_host_) cudaFreeHost(auto_map_host_);
+  auto_map_host_ = nullptr;
   ctrl_.reset();
   symm_.reset();
   fds_.reset();
@@ -679,7 +717,37 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
     stats_.pipelined++;
     return;
   }
-  if (mode == Mode::AllReduce && size_ > 1 && (plan.copy_in || plan.copy_out) &&
+  // Ordinary device buffers of the peer-to-peer two-shot AllReduce: export what is new, map what the
+  // peers have exported, and let the kernel go direct as soon as every rank can (twoshot_auto_body).
+  // The choice of this kernel depends on the request only, never on what has been mapped so far, so
+  // every rank launches the same kernel.
+  uint64_t auto_send_id = 0, auto_recv_id = 0;
+  bool auto_direct = false;
+  if (auto_shm_ && cfg_.auto_map && mode == Mode::AllReduce && size_ > 1 && plan.spec.algo == Algo::TwoShot && plan.copy_in &&
+      plan.copy_out && !in_seg && !out_seg && send_t == wire_t && recv_t == wire_t && send_kind == MemKind::Device &&
+      recv_kind == MemKind::Device && !host_pipe) {
+    LaunchSpec probe = plan.spec;
+    probe.auto_direct = true;
+    if (kernel_exists(probe)) {
+      auto_direct = true;
+      cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+      if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess) (void)cudaGetLastError();
+      if (cs != cudaStreamCaptureStatusActive) {   // nothing is exported or mapped while a graph is being captured
+        auto_send_id = auto_export(send);
+        auto_recv_id = recv == send ? auto_send_id : auto_export(recv);
+        auto_import();
+      } else {
+        // buffers exported by an earlier call keep their ids
+        AutoExportTable* mine = reinterpret_cast<AutoExportTable*>(auto_shm_) + rank_;
+        const unsigned long long sid = allocation_id(send), rid = allocation_id(recv);
+        for (uint32_t i = 0; i < mine->count; ++i) {
+          if (mine->e[i].id == sid) auto_send_id = sid;
+          if (mine->e[i].id == rid) auto_recv_id = rid;
+        }
+      }
+    }
+  }
+  if (!auto_direct && mode == Mode::AllReduce && size_ > 1 && (plan.copy_in || plan.copy_out) &&
       (plan.spec.algo == Algo::TwoShot || plan.spec.algo == Algo::Nvls || host_pipe) &&
       ((cfg_.pipeline_min_bytes != 0 && count * dtype_size(wire_t) >= cfg_.pipeline_min_bytes) || host_pipe)) {
     launch_pipelined(send, send_t, recv, recv_t, wire_t, count, op, scale, forced, stream, host_pipe && host_in,
@@ -706,6 +774,12 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
   a.copy_in = plan.copy_in ? 1 : 0;
   a.copy_out = plan.copy_out ? 1 : 0;
   a.pipe_ramp = plan.pipe_ramp;
+  a.auto_send_id = auto_send_id;
+  a.auto_recv_id = auto_recv_id;
+  if (auto_direct) {
+    plan.spec.auto_direct = true;
+    if (plan.spec.nblocks > kAutoBlocks) plan.spec.nblocks = kAutoBlocks;
+  }
   if (size_ > 1 && (plan.spec.algo == Algo::TwoShot || plan.spec.algo == Algo::Nvls)) {
     const bool zc_in = !plan.copy_in && mode != Mode::AllGather;
     const bool zc_out = !plan.copy_out && mode != Mode::ReduceScatter;
@@ -1086,6 +1160,70 @@ void Comm::mem_free(void* ptr) {
   symm_->release(seg);
 }
 
+// Lazy direct access, host side.  Exporting and importing are one-sided and never wait for a peer:
+// the kernel finds out per call whether every rank can reach every buffer (twoshot_auto_body).
+uint64_t Comm::auto_export(const void* ptr) {
+  const unsigned long long id = allocation_id(ptr);
+  if (id == 0 || !auto_shm_) return 0;
+  AutoExportTable* mine = reinterpret_cast<AutoExportTable*>(auto_shm_) + rank_;
+  for (uint32_t i = 0; i < mine->count; ++i)
+    if (mine->e[i].id == id) return id;
+  for (unsigned long long r : auto_refused_)
+    if (r == id) return 0;
+  if (mine->count >= static_cast<uint32_t>(kAutoSlots)) return 0;   // the table only grows: later allocations stay staged
+  const CudaDriver* d = CudaDriver::get();
+  CUdeviceptr base = 0;
+  size_t alloc_size = 0;
+  AutoExport e{};
+  if (!d || !d->MemGetAddressRange ||
+      d->MemGetAddressRange(&base, &alloc_size, reinterpret_cast<CUdeviceptr>(ptr)) != CUDA_SUCCESS ||
+      cudaIpcGetMemHandle(&e.handle, reinterpret_cast<void*>(base)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    if (auto_refused_.size() < 64) auto_refused_.push_back(id);
+    return 0;
+  }
+  e.id = id;
+  e.base = static_cast<uint64_t>(base);
+  e.size = alloc_size;
+  mine->e[mine->count] = e;
+  __atomic_store_n(&mine->count, mine->count + 1, __ATOMIC_RELEASE);
+  stats_.auto_exports++;
+  return id;
+}
+
+void Comm::auto_import() {
+  if (!auto_shm_) return;
+  for (int r = 0; r < size_; ++r) {
+    if (r == rank_) continue;
+    AutoExportTable* t = reinterpret_cast<AutoExportTable*>(auto_shm_) + r;
+    const uint32_t n = std::min<uint32_t>(__atomic_load_n(&t->count, __ATOMIC_ACQUIRE), kAutoSlots);
+    for (uint32_t i = auto_seen_[r]; i < n; ++i) {
+      const AutoExport e = t->e[i];
+      std::string key(reinterpret_cast<const char*>(&e.handle), sizeof(cudaIpcMemHandle_t));
+      key.push_back(static_cast<char>(r));
+      auto it = ipc_cache_.find(key);
+      if (it == ipc_cache_.end()) {
+        void* opened = nullptr;
+        if (cudaIpcOpenMemHandle(&opened, e.handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+          (void)cudaGetLastError();
+          continue;   // stays unmapped: calls on that buffer keep staging
+        }
+        ++ipc_misses_;
+        it = ipc_cache_.emplace(key, IpcMapping{opened, 0}).first;
+      }
+      it->second.refs++;   // held until the communicator goes
+      AutoMapEntry* row = auto_map_host_ + r * kAutoSlots + auto_mapped_[r];
+      row->peer_base = e.base;
+      row->size = e.size;
+      row->local_base = reinterpret_cast<uint64_t>(it->second.base);
+      __atomic_store_n(&row->id, e.id, __ATOMIC_RELEASE);   // the kernel reads the id first
+      auto_mapped_[r]++;
+      stats_.auto_imports++;
+    }
+    auto_seen_[r] = n;
+  }
+}
+
 void Comm::register_buffer(void* ptr, size_t bytes) {
   std::lock_guard<std::mutex> lk(call_mu_);
   if (!gpu_plane_) fail(Result::InvalidUsage, "buffer registration needs the GPU data plane");
@@ -1243,7 +1381,9 @@ std::string Comm::stats_json() {
   }
   o << "},\"zero_copy_in\":" << stats_.zero_copy_in << ",\"zero_copy_out\":" << stats_.zero_copy_out
     << ",\"ipc_cache\":{\"hits\":" << ipc_hits_ << ",\"misses\":" << ipc_misses_ << ",\"open\":" << ipc_cache_.size() << "}"
-    << ",\"stale_registrations\":" << stats_.stale_registrations << ",\"staged_calls\":" << stats_.staged_passes << ",\"pipelined_calls\":" << stats_.pipelined << ",\"graph_captures_seen\":" << stats_.graph_captures_seen;
+    << ",\"stale_registrations\":" << stats_.stale_registrations << ",\"staged_calls\":" << stats_.staged_passes << ",\"pipelined_calls\":" << stats_.pipelined
+    << ",\"auto_map\":{\"exports\":" << stats_.auto_exports << ",\"imports\":" << stats_.auto_imports << ",\"direct_calls\":"
+    << (auto_shm_ && progress_host_ ? progress_host_[6] : 0u) << "}" << ",\"graph_captures_seen\":" << stats_.graph_captures_seen;
   if (watchdog_) {
     o << ",\"watchdog\":{\"polls\":" << watchdog_->stats().polls.load() << ",\"trips\":" << watchdog_->stats().trips.load()
       << ",\"device_failures\":" << watchdog_->stats().device_failures.load() << ",\"remote_aborts\":"

@@ -37,6 +37,7 @@ struct CommStats {
   uint64_t stale_registrations = 0;
   uint64_t zero_copy_in = 0, zero_copy_out = 0, staged_passes = 0, pipelined = 0;
   uint64_t graph_captures_seen = 0, errors = 0;
+  uint64_t auto_exports = 0, auto_imports = 0;
 };
 
 class Comm {
@@ -134,6 +135,17 @@ class Comm {
   std::map<std::string, IpcMapping> ipc_cache_;   // key: peer rank + handle bytes
   std::map<uintptr_t, std::vector<std::string>> registered_;  // local ptr -> cache keys it holds
   uint64_t ipc_hits_ = 0, ipc_misses_ = 0;
+
+  // Lazy direct access to ordinary device buffers (kernels/comm_dev.h, AutoCtl): every rank lists the
+  // allocations it has exported in the host's shared page; peers map them when they see them and note
+  // the mapping in a host-mapped table that the kernel reads.
+  char* auto_shm_ = nullptr;                 // export tables in the shared page, one per rank (null: off)
+  AutoMapEntry* auto_map_host_ = nullptr;    // [kMaxRanks][kAutoSlots]
+  std::vector<uint32_t> auto_seen_;          // per peer: entries of its export table already looked at
+  std::vector<uint32_t> auto_mapped_;        // per peer: rows of auto_map_host_ in use
+  std::vector<unsigned long long> auto_refused_;  // allocations of this rank that cannot be exported
+  uint64_t auto_export(const void* ptr);     // id of the (now) exported allocation of ptr, 0 if it cannot be
+  void auto_import();                        // map what the peers have exported since the last look
 
   // chunk pipeline for large AllReduces on ordinary buffers
   struct Pipeline {

@@ -35,6 +35,10 @@ struct EmuWorld {
   size_t ctrl_bytes = 0;
   int last_algo = 0, last_blocks = 0;
   Config cfg;
+  // lazy direct access: which virtual rank has which rank's buffers "mapped" (row q, column r), and the
+  // tables the kernel reads (device memory here; every buffer lives in the one address space)
+  std::vector<int> auto_mapped;
+  AutoMapEntry* auto_tab = nullptr;  // [n][kMaxRanks * kAutoSlots]
 };
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -91,6 +95,8 @@ MNCCL_EXPORT int mncclEmuCreate(int nranks, size_t staging_bytes, void** world) 
   off += align_up(sizeof(LocalState), 4096);
   proto.off_pipe = off;
   off += align_up(sizeof(PipeCtl), 4096);
+  proto.off_auto = off;
+  off += align_up(sizeof(AutoCtl), 4096);
   proto.off_ll = off;
   off += 2 * size_t(nranks) * w->caps.ll_slot_bytes;
   proto.off_inbox = off;
@@ -126,6 +132,7 @@ MNCCL_EXPORT int mncclEmuDestroy(void* world) {
   if (!w) return 4;
   cudaDeviceSynchronize();
   for (char* p : w->ctrl) cudaFree(p);
+  if (w->auto_tab) cudaFree(w->auto_tab);
   for (auto& a : w->segs)
     for (auto& pr : a) cudaFree(pr.first);
   cudaFree(w->table);
@@ -242,6 +249,38 @@ MNCCL_EXPORT int mncclEmuCollective(void* world, int mode, const void* const* se
   w->last_algo = static_cast<int>(plan.spec.algo);
   w->last_blocks = plan.spec.nblocks;
 
+  // Lazy direct access (mncclEmuSetAutoMap): the staged two-shot kernel that goes direct when every
+  // virtual rank has every rank's buffers in its table.
+  bool auto_direct = false;
+  if (!w->auto_mapped.empty() && pi.mode == Mode::AllReduce && plan.spec.algo == Algo::TwoShot && plan.copy_in && plan.copy_out &&
+      pi.in == pi.wire && pi.in == pi.out) {
+    LaunchSpec probe = plan.spec;
+    probe.auto_direct = true;
+    if (kernel_exists(probe)) {
+      auto_direct = true;
+      plan.spec.auto_direct = true;
+      if (plan.spec.nblocks > kAutoBlocks) plan.spec.nblocks = kAutoBlocks;
+      const int cap2 = max_emulated_blocks(plan.spec, N);
+      if (cap2 <= 0) return 4;
+      if (plan.spec.nblocks > cap2) plan.spec.nblocks = cap2;
+      w->last_blocks = plan.spec.nblocks;
+      std::vector<AutoMapEntry> tab(static_cast<size_t>(N) * kMaxRanks * kAutoSlots);
+      memset(tab.data(), 0, tab.size() * sizeof(AutoMapEntry));
+      const uint64_t bytes = count * dtype_size(pi.in);
+      for (int q = 0; q < N; ++q)
+        for (int r = 0; r < N; ++r) {
+          if (q == r || !w->auto_mapped[q * N + r]) continue;
+          AutoMapEntry* row = tab.data() + (static_cast<size_t>(q) * kMaxRanks + r) * kAutoSlots;
+          row[0] = AutoMapEntry{uint64_t(2 * r + 1), reinterpret_cast<uint64_t>(send[r]), bytes, reinterpret_cast<uint64_t>(send[r])};
+          if (recv[r] != send[r])
+            row[1] = AutoMapEntry{uint64_t(2 * r + 2), reinterpret_cast<uint64_t>(recv[r]), bytes, reinterpret_cast<uint64_t>(recv[r])};
+        }
+      if (!w->auto_tab) EMU_RT(cudaMalloc(&w->auto_tab, tab.size() * sizeof(AutoMapEntry)));
+      EMU_RT(cudaMemcpyAsync(w->auto_tab, tab.data(), tab.size() * sizeof(AutoMapEntry), cudaMemcpyHostToDevice, stream));
+      EMU_RT(cudaStreamSynchronize(stream));
+    }
+  }
+
   const bool is_float = pi.in == DType::Float16 || pi.in == DType::Bfloat16 || pi.in == DType::Float32 || pi.in == DType::Float64;
   std::vector<KParams> host(N);
   for (int r = 0; r < N; ++r) {
@@ -266,6 +305,11 @@ MNCCL_EXPORT int mncclEmuCollective(void* world, int mode, const void* const* se
       a.count = 0;
       a.shard_elems = 0;
     }
+    if (auto_direct) {
+      a.auto_send_id = 2 * r + 1;
+      a.auto_recv_id = recv[r] == send[r] ? a.auto_send_id : 2 * r + 2;
+      kp.comm.auto_map = w->auto_tab + static_cast<size_t>(r) * kMaxRanks * kAutoSlots;
+    }
     const bool zc_in = !plan.copy_in && pi.mode != Mode::AllGather;
     const bool zc_out = !plan.copy_out && pi.mode != Mode::ReduceScatter;
     const bool staged_algo = plan.spec.algo == Algo::TwoShot;
@@ -277,6 +321,31 @@ MNCCL_EXPORT int mncclEmuCollective(void* world, int mode, const void* const* se
   EMU_RT(cudaMemcpyAsync(w->table, host.data(), sizeof(KParams) * N, cudaMemcpyHostToDevice, stream));
   EMU_RT(cudaStreamSynchronize(stream));  // `host` goes out of scope; keep it simple
   EMU_RT(launch_collective_emulated(plan.spec, w->table, N, stream));
+  return 0;
+}
+
+// Lazy direct access in the emulated world.  mapped[q * nranks + r] != 0: virtual rank q has rank r's
+// buffers in its table; null switches the feature off again.  While set, AllReduce calls that plan as
+// the staged two-shot kernel (ordinary buffers, one type) run the kernel that goes direct when every
+// rank can reach every buffer.
+MNCCL_EXPORT int mncclEmuSetAutoMap(void* world, const int* mapped) {
+  auto* w = static_cast<EmuWorld*>(world);
+  if (!w) return 4;
+  if (!mapped) w->auto_mapped.clear();
+  else w->auto_mapped.assign(mapped, mapped + w->n * w->n);
+  return 0;
+}
+
+// direct[nranks]: how many calls of every virtual rank ran on the user buffers directly.
+MNCCL_EXPORT int mncclEmuDirectCalls(void* world, uint32_t* direct) {
+  auto* w = static_cast<EmuWorld*>(world);
+  if (!w || !direct) return 4;
+  EMU_RT(cudaDeviceSynchronize());
+  for (int r = 0; r < w->n; ++r) {
+    LocalState ls;
+    EMU_RT(cudaMemcpy(&ls, w->ctrl[r] + w->dev[r].off_local, sizeof(ls), cudaMemcpyDeviceToHost));
+    direct[r] = ls.pad[0];
+  }
   return 0;
 }
 

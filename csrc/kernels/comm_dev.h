@@ -10,6 +10,7 @@
 //   ll       [2][nranks][ll_slot_bytes]    one-shot "LL" inboxes (flag+data)
 //   inbox    [2][nranks][inbox_slot_bytes] one-shot inboxes (barrier flavour)
 //   pipe     PipeCtl                       chunk flags of the pipelined AllReduce
+//   auto     AutoCtl                       per-call buffer descriptors and votes (lazy direct access)
 //   stage_a  [stage_bytes]                 staged inputs  (wire type)
 //   stage_b  [stage_bytes]                 staged outputs (output type)
 //
@@ -60,6 +61,27 @@ struct PipeCtl {
   uint32_t pad[2];
 };
 
+// Lazy direct access to ordinary device buffers (coll_kernels.cuh, twoshot_auto_body).  A rank exports
+// the allocations its buffers live in (CUDA IPC) and maps what its peers have exported; which peer
+// allocation is mapped where is listed in a table in host-mapped memory, one row per peer.  Inside
+// the kernel every rank tells every peer which buffers it passed to THIS call (allocation id and
+// address, pushed into the peer's AutoCtl before a barrier), looks the peers' buffers up in its
+// table, and tells the peers whether it found them all; only when every rank did, the kernel reads
+// and writes the user buffers directly, otherwise it stages as before.  No host-side agreement is
+// needed and a rank that has not mapped a peer's buffer yet merely delays the switch.
+constexpr int kAutoSlots = 16;        // exported allocations per rank
+constexpr int kAutoBlocks = 128;      // grid cap of the kernel (rows of AutoCtl)
+struct AutoMapEntry {
+  uint64_t id;          // allocation id in the exporting process (0: empty; written last)
+  uint64_t peer_base;   // its address range in the exporting process
+  uint64_t size;
+  uint64_t local_base;  // where this process mapped it
+};
+struct AutoCtl {
+  uint64_t desc[kAutoBlocks][kMaxRanks][4];   // from every peer: send id, send address, recv id, recv address
+  uint32_t vote[kAutoBlocks][kMaxRanks];      // from every peer: 1 = it can reach every rank's buffers
+};
+
 struct CommDev {
   int32_t rank;
   int32_t nranks;
@@ -71,6 +93,8 @@ struct CommDev {
   uint64_t off_sig, off_local, off_ll, off_inbox, off_stage_a, off_stage_b;
   uint64_t off_pipe;              // PipeCtl
   uint64_t ll_slot_bytes, inbox_slot_bytes, stage_bytes;
+  uint64_t off_auto;              // AutoCtl
+  const AutoMapEntry* auto_map;   // [kMaxRanks][kAutoSlots] in host-mapped memory, or null
 };
 
 // Arguments of one AllReduce / ReduceScatter / AllGather launch.
@@ -90,6 +114,9 @@ struct CollArgs {
   int32_t copy_in;           // 1: inputs are first staged from `send`
   int32_t copy_out;          // 1: outputs are copied from stage_b to `recv`
   int32_t pipe_ramp;         // pipelined kernel: number of small first chunks (CE / 2^R ... CE / 2), see pipe_chunk_geom
+  int32_t pad0;
+  uint64_t auto_send_id;     // twoshot_auto_body: allocation ids of `send` and `recv` (0: not exported)
+  uint64_t auto_recv_id;
 };
 
 struct KParams {

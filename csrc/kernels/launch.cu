@@ -8,6 +8,7 @@ cudaError_t dispatch_local(const LaunchCtx&);
 cudaError_t dispatch_ll(const LaunchCtx&);
 cudaError_t dispatch_oneshot(const LaunchCtx&);
 cudaError_t dispatch_twoshot_ar(const LaunchCtx&);
+cudaError_t dispatch_twoshot_auto(const LaunchCtx&);
 cudaError_t dispatch_nvls_ar(const LaunchCtx&);
 cudaError_t dispatch_rs(const LaunchCtx&);
 cudaError_t dispatch_rs_nvls(const LaunchCtx&);
@@ -26,7 +27,7 @@ cudaError_t route(const dev::LaunchCtx& x) {
         case Algo::Local: return dev::dispatch_local(x);
         case Algo::LL: return dev::dispatch_ll(x);
         case Algo::OneShot: return dev::dispatch_oneshot(x);
-        case Algo::TwoShot: return dev::dispatch_twoshot_ar(x);
+        case Algo::TwoShot: return s.auto_direct ? dev::dispatch_twoshot_auto(x) : dev::dispatch_twoshot_ar(x);
         case Algo::Nvls: return dev::dispatch_nvls_ar(x);
         case Algo::Pipe: return s.pipe_nvls ? dev::dispatch_pipe_nvls(x) : dev::dispatch_pipe(x);
         case Algo::HostSync: return dev::dispatch_gather_reduce(x);
@@ -54,6 +55,7 @@ cudaError_t launch_collective(const LaunchSpec& spec, const KParams& p, cudaStre
   const int max_blocks = (spec.algo == Algo::Local || spec.algo == Algo::HostSync) ? 65535 : kMaxBlocks;
   if (spec.nblocks < 1 || spec.nblocks > max_blocks || spec.nthreads < 32 || spec.nthreads > 512)
     return cudaErrorInvalidConfiguration;
+  if (spec.auto_direct && spec.nblocks > kAutoBlocks) return cudaErrorInvalidConfiguration;
   dev::LaunchCtx x{&spec, &p, nullptr, 1, stream, nullptr};
   return route(x);
 }

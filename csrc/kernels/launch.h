@@ -28,6 +28,7 @@ struct LaunchSpec {
   int nthreads = 512;
   int unroll = 4;  // vectors in flight per thread in the NVLS kernels (4 or 8)
   bool pipe_nvls = false;  // Algo::Pipe: reduce through the switch (multimem) instead of peer loads / stores
+  bool auto_direct = false;  // Algo::TwoShot on ordinary buffers: the kernel that goes direct once every rank has mapped every buffer
 };
 
 // True when a kernel exists for this combination of algorithm, mode, types

@@ -123,6 +123,9 @@ def lib() -> C.CDLL:
     sig("mncclEmuSetPipeChunk", i32, vp, sz)
     sig("mncclEmuCollective", i32, vp, i32, P(vp), P(vp), sz, i32, i32, i32, i32, dbl, i32, i32, vp)
     sig("mncclEmuStatus", i32, vp, P(u32), P(u32))
+    if hasattr(L, "mncclEmuSetAutoMap"):
+        sig("mncclEmuSetAutoMap", i32, vp, P(C.c_int))
+        sig("mncclEmuDirectCalls", i32, vp, P(u32))
     sig("mncclEmuLastPlan", i32, vp, P(i32), P(i32))
     sig("mncclProbeBoundedWait", i32, u64, i32, P(u32), P(u32))
     # host oracle (csrc/ref/oracle_api.cc)

@@ -45,7 +45,7 @@ HOST_SOURCES = [
 # (libmini_nccl_testhooks.so), so that the product library exports the API and nothing else.
 TESTHOOK_SOURCES = ["testing/hooks.cc"]
 CUDA_SOURCES = [
-    "kernels/k_small.cu", "kernels/k_twoshot.cu", "kernels/k_rsag.cu", "kernels/k_nvls.cu", "kernels/k_pipe.cu",
+    "kernels/k_small.cu", "kernels/k_twoshot.cu", "kernels/k_rsag.cu", "kernels/k_nvls.cu", "kernels/k_pipe.cu", "kernels/k_auto.cu",
     "kernels/launch.cu", "emu/emu_world.cu",
 ]
 # Translation units compiled when present (a source tree may be trimmed to the collectives alone).
@@ -186,7 +186,7 @@ def build_devcheck_variant(verbose: bool = False, jobs: int | None = None) -> Pa
     lib = build(verbose=verbose, programs=False)
     out = LIBDIR / "libmini_nccl_devcheck.so"
     hdr = _newest_header_mtime()
-    checked = ["kernels/k_small.cu", "kernels/k_twoshot.cu", "kernels/k_rsag.cu", "kernels/k_nvls.cu", "kernels/k_pipe.cu",
+    checked = ["kernels/k_small.cu", "kernels/k_twoshot.cu", "kernels/k_rsag.cu", "kernels/k_nvls.cu", "kernels/k_pipe.cu", "kernels/k_auto.cu",
                "kernels/launch.cu", "emu/emu_world.cu"]
 
     def compile_checked(rel: str) -> Path:

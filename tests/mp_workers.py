@@ -570,7 +570,65 @@ def gpu_shared(rank, n, kw):
             "algbw_GBps": (64 << 20) / dt / 1e9}
 
 
-FUNCS = {f.__name__: f for f in (cpu_ring, cpu_ring_fault, gpu_battery, gpu_stall, gpu_tp, gpu_tp_stall, gpu_shared)}
+def gpu_auto_map(rank, n, kw):
+    """Ordinary torch tensors through the peer-to-peer two-shot AllReduce: the first call stages, later
+    calls on the same allocations run on the user buffers directly once every rank has mapped them.
+    Every result is compared bit for bit with the rank-ordered host oracle."""
+    import numpy as np
+    import torch
+
+    import mini_nccl_b200 as mn
+    from mini_nccl_b200 import _lib
+    from mini_nccl_b200.utils import oracle as O
+
+    torch.cuda.set_device(rank % torch.cuda.device_count())
+    comm = mn.Communicator(n, rank, "127.0.0.1")
+    want_direct = kw.get("expect_direct", True)
+    out = {"rank": rank, "cases": 0, "steps": []}
+
+    def run(count, dtype_code, tdt, in_place, seed, buf=None):
+        ins = [O.make_input(dtype_code, count, r, seed=seed, dist="normal") for r in range(n)]
+        want = O.oracle_allreduce(ins, dtype_code, _lib.SUM, scale=1.0)
+        if buf is None:
+            buf = (torch.empty(count, dtype=tdt, device="cuda"), None if in_place else torch.empty(count, dtype=tdt, device="cuda"))
+        src, dst = buf
+        raw = ins[rank].view(np.int16) if dtype_code == _lib.BFLOAT16 else ins[rank]
+        (src.view(torch.int16) if dtype_code == _lib.BFLOAT16 else src).copy_(torch.from_numpy(raw.copy()))
+        comm.all_reduce(src, "sum", out=dst, algo="twoshot")
+        torch.cuda.synchronize()
+        res = dst if dst is not None else src
+        got = (res.view(torch.int16) if dtype_code == _lib.BFLOAT16 else res).cpu().numpy()
+        got = got.view(np.uint16) if dtype_code == _lib.BFLOAT16 else got
+        assert np.array_equal(got, want), f"rank {rank}: count {count} seed {seed}: {int(np.count_nonzero(got != want))} elements differ"
+        out["cases"] += 1
+        comm.barrier()   # the next call finds this call's exports of every rank
+        out["steps"].append(comm.stats()["auto_map"]["direct_calls"])
+        return buf
+
+    # the same buffers again and again (a training loop's gradient bucket), 24 MB fp32, out of place
+    big = None
+    for it in range(4):
+        big = run((6 << 20) + 3, _lib.FLOAT32, torch.float32, False, 100 + it, big)
+    direct_after_reuse = comm.stats()["auto_map"]["direct_calls"]
+    # in place, bf16, a message above the stream pipeline's threshold
+    loop = None
+    for it in range(3):
+        loop = run(40 << 20, _lib.BFLOAT16, torch.bfloat16, True, 200 + it, loop)
+    # a buffer that was never seen: staged on its first call, and still right
+    run(1 << 20 | 1, _lib.FLOAT32, torch.float32, False, 300)
+    st = comm.stats()
+    out.update({"auto_map": st["auto_map"], "pipelined_calls": st["pipelined_calls"], "direct_after_reuse": direct_after_reuse,
+                "algo": st["algo"]})
+    if want_direct:
+        assert st["auto_map"]["exports"] >= 2 and st["auto_map"]["imports"] >= 2 * (n - 1), st["auto_map"]
+        assert direct_after_reuse >= 2, out["steps"]
+    else:
+        assert st["auto_map"]["direct_calls"] == 0 and st["auto_map"]["exports"] == 0
+    comm.destroy()
+    return out
+
+
+FUNCS = {f.__name__: f for f in (cpu_ring, cpu_ring_fault, gpu_battery, gpu_stall, gpu_tp, gpu_tp_stall, gpu_shared, gpu_auto_map)}
 
 if __name__ == "__main__":
     fn, rank, n, kw = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), json.loads(sys.argv[4])

@@ -308,3 +308,33 @@ def test_ll_calls_with_changing_block_counts(worlds):
     for i, nb in enumerate([1, 2, 1, 3, 2, 4, 1, 4, 3, 1, 2, 2]):
         check_allreduce(w, count, _lib.FLOAT32, _lib.SUM, ALGOS["ll"], nblocks=nb, seed=1000 + i)
         assert w.last_plan() == ("ll", nb)
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_lazy_direct_access_agrees_inside_the_kernel(lib, n):
+    """The two-shot kernel on ordinary buffers goes direct only when EVERY rank has EVERY rank's buffers
+    in its table; one missing row on one rank keeps all ranks on the staged path.  Bit-exact either way,
+    in place and out of place, with a message of several staging passes."""
+    w = World(lib, n, staging=1 << 20)
+    try:
+        direct = (C.c_uint32 * n)()
+        full = [1] * (n * n)
+        partial = list(full)
+        partial[1 * n + 0] = 0            # rank 1 has not mapped rank 0's buffers yet
+        seen = 0
+        for mapped, goes_direct in ((partial, False), (full, True), (partial, False), (full, True)):
+            assert lib.mncclEmuSetAutoMap(w.h, (C.c_int * (n * n))(*mapped)) == 0
+            for dtype, count, in_place in ((_lib.FLOAT32, (3 << 20) + 5, False), (_lib.BFLOAT16, 1 << 20, True),
+                                           (_lib.INT32, 70001, False)):
+                op = _lib.MAX if dtype == _lib.INT32 else _lib.SUM
+                check_allreduce(w, count, dtype, op, ALGOS["twoshot"], in_place=in_place, seed=77 + seen)
+                assert w.last_plan()[0] == "twoshot"
+                assert lib.mncclEmuDirectCalls(w.h, direct) == 0
+                seen += 1 if goes_direct else 0
+                assert list(direct) == [seen] * n, (list(direct), seen, mapped == full)
+        # buffers that are not 16-byte aligned stay staged although every table is complete
+        check_allreduce(w, 40000, _lib.FLOAT32, _lib.SUM, ALGOS["twoshot"], misalign=1)
+        assert lib.mncclEmuDirectCalls(w.h, direct) == 0 and list(direct) == [seen] * n
+        assert lib.mncclEmuSetAutoMap(w.h, None) == 0
+    finally:
+        w.close()

@@ -136,3 +136,17 @@ def test_reference_shaped_programs_on_gpus(free_port):
         assert all(p.returncode == 0 for p in ps), outs
         assert "BusBW(GB/s)" in outs[0][0] and "67108864" in outs[0][0] and "(FAIL)" not in outs[0][0]
         print(outs[0][0])
+
+
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("on", [1, 0])
+def test_ordinary_buffers_become_direct_after_first_sight(free_port, on):
+    """Lazy direct access: buffers that come back are exported and mapped without a collective call, the
+    kernel agrees per call whether it can use them directly; switched off, everything stays staged."""
+    res = run_ranks("gpu_auto_map", 2, {"expect_direct": bool(on)},
+                    {"MINI_NCCL_BOOTSTRAP_PORT": free_port, "MINI_NCCL_AUTO_MAP": on}, timeout=300)
+    assert len(res) == 2 and all(r["cases"] == 8 for r in res)
+    if on:
+        assert all(r["auto_map"]["direct_calls"] >= 4 for r in res), [r["steps"] for r in res]
+    else:
+        assert all(r["pipelined_calls"] >= 1 for r in res)
