@@ -386,25 +386,23 @@ void Comm::init_gpu_plane() {
   dev_.ctrl_mc = static_cast<char*>(ctrl_->mc);
   caps_.nvls = ctrl_->mc != nullptr;
 
-  // lazy direct access: needs the page shared by the host's ranks and a table the kernels can read
+  // lazy direct access: needs the page shared by the host's ranks and a table the kernels can read.
+  // The table lives in DEVICE memory: reads of host-mapped memory from many blocks at once take
+  // about a microsecond each, one after the other (measured: 96 blocks x 8 reads = 750 us per call).
   if (cfg_.auto_map && shm_map_ && shm_registered_ && size_ <= kAutoShmRanks && local_size_ == size_) {
     void* tab = nullptr;
-    if (cudaHostAlloc(&tab, sizeof(AutoMapEntry) * kMaxRanks * kAutoSlots, cudaHostAllocMapped) == cudaSuccess) {
-      memset(tab, 0, sizeof(AutoMapEntry) * kMaxRanks * kAutoSlots);
-      void* dtab = nullptr;
-      if (cudaHostGetDevicePointer(&dtab, tab, 0) == cudaSuccess && dtab) {
-        auto_map_host_ = static_cast<AutoMapEntry*>(tab);
-        dev_.auto_map = static_cast<const AutoMapEntry*>(dtab);
-        auto_shm_ = static_cast<char*>(shm_map_) + kAutoShmOffset;
-        memset(auto_shm_ + rank_ * sizeof(AutoExportTable), 0, sizeof(AutoExportTable));
-        auto_seen_.assign(size_, 0);
-        auto_mapped_.assign(size_, 0);
-      } else {
-        (void)cudaGetLastError();
-        cudaFreeHost(tab);
-      }
+    const size_t tab_bytes = sizeof(AutoMapEntry) * kMaxRanks * kAutoSlots;
+    if (cudaMalloc(&tab, tab_bytes) == cudaSuccess && cudaMemset(tab, 0, tab_bytes) == cudaSuccess &&
+        cudaStreamCreateWithFlags(&auto_stream_, cudaStreamNonBlocking) == cudaSuccess) {
+      auto_map_dev_ = static_cast<AutoMapEntry*>(tab);
+      dev_.auto_map = auto_map_dev_;
+      auto_shm_ = static_cast<char*>(shm_map_) + kAutoShmOffset;
+      memset(auto_shm_ + rank_ * sizeof(AutoExportTable), 0, sizeof(AutoExportTable));
+      auto_seen_.assign(size_, 0);
+      auto_mask_.assign(size_, 0);
     } else {
       (void)cudaGetLastError();
+      if (tab) cudaFree(tab);
     }
   }
 
@@ -587,8 +585,10 @@ Comm::~Comm() {
   }
   for (auto& kv : ipc_cache_) cudaIpcCloseMemHandle(kv.second.base);
   ipc_cache_.clear();
-  if (auto_map_host_) cudaFreeHost(auto_map_host_);
-  auto_map_host_ = nullptr;
+  if (auto_map_dev_) cudaFree(auto_map_dev_);
+  if (auto_stream_) cudaStreamDestroy(auto_stream_);
+  auto_map_dev_ = nullptr;
+  auto_stream_ = nullptr;
   ctrl_.reset();
   symm_.reset();
   fds_.reset();
@@ -721,7 +721,7 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
   // peers have exported, and let the kernel go direct as soon as every rank can (twoshot_auto_body).
   // The choice of this kernel depends on the request only, never on what has been mapped so far, so
   // every rank launches the same kernel.
-  uint64_t auto_send_id = 0, auto_recv_id = 0;
+  AutoDesc auto_desc{};
   bool auto_direct = false;
   if (auto_shm_ && cfg_.auto_map && mode == Mode::AllReduce && size_ > 1 && plan.spec.algo == Algo::TwoShot && plan.copy_in &&
       plan.copy_out && !in_seg && !out_seg && send_t == wire_t && recv_t == wire_t && send_kind == MemKind::Device &&
@@ -732,19 +732,16 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
       auto_direct = true;
       cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
       if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess) (void)cudaGetLastError();
-      if (cs != cudaStreamCaptureStatusActive) {   // nothing is exported or mapped while a graph is being captured
-        auto_send_id = auto_export(send);
-        auto_recv_id = recv == send ? auto_send_id : auto_export(recv);
-        auto_import();
-      } else {
-        // buffers exported by an earlier call keep their ids
-        AutoExportTable* mine = reinterpret_cast<AutoExportTable*>(auto_shm_) + rank_;
-        const unsigned long long sid = allocation_id(send), rid = allocation_id(recv);
-        for (uint32_t i = 0; i < mine->count; ++i) {
-          if (mine->e[i].id == sid) auto_send_id = sid;
-          if (mine->e[i].id == rid) auto_recv_id = rid;
-        }
-      }
+      const bool live = cs != cudaStreamCaptureStatusActive;   // nothing is exported or mapped while a graph is being captured
+      const int s_slot = auto_export(send, in_bytes, live);
+      const int r_slot = recv == send ? s_slot : auto_export(recv, out_bytes, live);
+      if (live) auto_import();
+      const bool usable = s_slot >= 0 && r_slot >= 0 &&
+                          ((reinterpret_cast<uintptr_t>(send) | reinterpret_cast<uintptr_t>(recv)) & 15u) == 0;
+      auto_desc.send_addr = reinterpret_cast<uint64_t>(send);
+      auto_desc.recv_addr = reinterpret_cast<uint64_t>(recv);
+      auto_desc.slots = usable ? (static_cast<uint32_t>(s_slot) | (static_cast<uint32_t>(r_slot) << 8) | (1u << 16)) : 0u;
+      for (int r = 0; r < size_ && r < kAutoRanks; ++r) auto_desc.mask[r] = auto_mask_[r];
     }
   }
   if (!auto_direct && mode == Mode::AllReduce && size_ > 1 && (plan.copy_in || plan.copy_out) &&
@@ -774,8 +771,7 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
   a.copy_in = plan.copy_in ? 1 : 0;
   a.copy_out = plan.copy_out ? 1 : 0;
   a.pipe_ramp = plan.pipe_ramp;
-  a.auto_send_id = auto_send_id;
-  a.auto_recv_id = auto_recv_id;
+  a.auto_desc = auto_desc;
   if (auto_direct) {
     plan.spec.auto_direct = true;
     if (plan.spec.nblocks > kAutoBlocks) plan.spec.nblocks = kAutoBlocks;
@@ -1162,15 +1158,17 @@ void Comm::mem_free(void* ptr) {
 
 // Lazy direct access, host side.  Exporting and importing are one-sided and never wait for a peer:
 // the kernel finds out per call whether every rank can reach every buffer (twoshot_auto_body).
-uint64_t Comm::auto_export(const void* ptr) {
+int Comm::auto_export(const void* ptr, size_t bytes, bool may_export) {
   const unsigned long long id = allocation_id(ptr);
-  if (id == 0 || !auto_shm_) return 0;
+  if (id == 0 || !auto_shm_) return -1;
   AutoExportTable* mine = reinterpret_cast<AutoExportTable*>(auto_shm_) + rank_;
+  const uint64_t addr = reinterpret_cast<uint64_t>(ptr);
   for (uint32_t i = 0; i < mine->count; ++i)
-    if (mine->e[i].id == id) return id;
+    if (mine->e[i].id == id) return (addr >= mine->e[i].base && addr + bytes <= mine->e[i].base + mine->e[i].size) ? static_cast<int>(i) : -1;
+  if (!may_export) return -1;
   for (unsigned long long r : auto_refused_)
-    if (r == id) return 0;
-  if (mine->count >= static_cast<uint32_t>(kAutoSlots)) return 0;   // the table only grows: later allocations stay staged
+    if (r == id) return -1;
+  if (mine->count >= static_cast<uint32_t>(kAutoSlots)) return -1;   // slots are never reused: later allocations stay staged
   const CudaDriver* d = CudaDriver::get();
   CUdeviceptr base = 0;
   size_t alloc_size = 0;
@@ -1180,15 +1178,16 @@ uint64_t Comm::auto_export(const void* ptr) {
       cudaIpcGetMemHandle(&e.handle, reinterpret_cast<void*>(base)) != cudaSuccess) {
     (void)cudaGetLastError();
     if (auto_refused_.size() < 64) auto_refused_.push_back(id);
-    return 0;
+    return -1;
   }
   e.id = id;
   e.base = static_cast<uint64_t>(base);
   e.size = alloc_size;
-  mine->e[mine->count] = e;
-  __atomic_store_n(&mine->count, mine->count + 1, __ATOMIC_RELEASE);
+  const uint32_t slot = mine->count;
+  mine->e[slot] = e;
+  __atomic_store_n(&mine->count, slot + 1, __ATOMIC_RELEASE);
   stats_.auto_exports++;
-  return id;
+  return (addr + bytes <= e.base + e.size) ? static_cast<int>(slot) : -1;
 }
 
 void Comm::auto_import() {
@@ -1212,12 +1211,16 @@ void Comm::auto_import() {
         it = ipc_cache_.emplace(key, IpcMapping{opened, 0}).first;
       }
       it->second.refs++;   // held until the communicator goes
-      AutoMapEntry* row = auto_map_host_ + r * kAutoSlots + auto_mapped_[r];
-      row->peer_base = e.base;
-      row->size = e.size;
-      row->local_base = reinterpret_cast<uint64_t>(it->second.base);
-      __atomic_store_n(&row->id, e.id, __ATOMIC_RELEASE);   // the kernel reads the id first
-      auto_mapped_[r]++;
+      // Row [peer][its slot] of the device table, on a stream of its own so that nothing queued on the
+      // caller's streams is waited for.  Kernels only look at rows whose bit their launch carried, and
+      // the bit is set after the copy has completed.
+      const AutoMapEntry row{e.id, e.base, e.size, reinterpret_cast<uint64_t>(it->second.base)};
+      if (cudaMemcpyAsync(auto_map_dev_ + r * kAutoSlots + i, &row, sizeof(row), cudaMemcpyHostToDevice, auto_stream_) != cudaSuccess ||
+          cudaStreamSynchronize(auto_stream_) != cudaSuccess) {
+        (void)cudaGetLastError();
+        continue;
+      }
+      auto_mask_[r] = static_cast<uint16_t>(auto_mask_[r] | (1u << i));
       stats_.auto_imports++;
     }
     auto_seen_[r] = n;

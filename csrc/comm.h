@@ -138,13 +138,14 @@ class Comm {
 
   // Lazy direct access to ordinary device buffers (kernels/comm_dev.h, AutoCtl): every rank lists the
   // allocations it has exported in the host's shared page; peers map them when they see them and note
-  // the mapping in a host-mapped table that the kernel reads.
+  // the mapping in a table in device memory that the kernel reads.
   char* auto_shm_ = nullptr;                 // export tables in the shared page, one per rank (null: off)
-  AutoMapEntry* auto_map_host_ = nullptr;    // [kMaxRanks][kAutoSlots]
+  AutoMapEntry* auto_map_dev_ = nullptr;     // [kMaxRanks][kAutoSlots], device memory
+  cudaStream_t auto_stream_ = nullptr;       // carries the table's updates
   std::vector<uint32_t> auto_seen_;          // per peer: entries of its export table already looked at
-  std::vector<uint32_t> auto_mapped_;        // per peer: rows of auto_map_host_ in use
+  std::vector<uint16_t> auto_mask_;          // per peer: its export slots that are mapped here
   std::vector<unsigned long long> auto_refused_;  // allocations of this rank that cannot be exported
-  uint64_t auto_export(const void* ptr);     // id of the (now) exported allocation of ptr, 0 if it cannot be
+  int auto_export(const void* ptr, size_t bytes, bool may_export);  // export slot of ptr's allocation (exported now if new), -1 if none
   void auto_import();                        // map what the peers have exported since the last look
 
   // chunk pipeline for large AllReduces on ordinary buffers

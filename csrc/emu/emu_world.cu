@@ -306,8 +306,12 @@ MNCCL_EXPORT int mncclEmuCollective(void* world, int mode, const void* const* se
       a.shard_elems = 0;
     }
     if (auto_direct) {
-      a.auto_send_id = 2 * r + 1;
-      a.auto_recv_id = recv[r] == send[r] ? a.auto_send_id : 2 * r + 2;
+      // slot 0 of every rank is its send buffer, slot 1 its recv buffer
+      const bool usable = ((reinterpret_cast<uintptr_t>(send[r]) | reinterpret_cast<uintptr_t>(recv[r])) & 15u) == 0;
+      a.auto_desc.send_addr = reinterpret_cast<uint64_t>(send[r]);
+      a.auto_desc.recv_addr = reinterpret_cast<uint64_t>(recv[r]);
+      a.auto_desc.slots = usable ? (0u | ((recv[r] == send[r] ? 0u : 1u) << 8) | (1u << 16)) : 0u;
+      for (int q = 0; q < N && q < kAutoRanks; ++q) a.auto_desc.mask[q] = (q != r && w->auto_mapped[r * N + q]) ? 3u : 0u;
       kp.comm.auto_map = w->auto_tab + static_cast<size_t>(r) * kMaxRanks * kAutoSlots;
     }
     const bool zc_in = !plan.copy_in && pi.mode != Mode::AllGather;

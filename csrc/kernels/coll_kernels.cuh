@@ -458,94 +458,91 @@ __device__ __forceinline__ void twoshot_body(const KParams& P, int blk, int nblk
 }
 
 // -------------------------------------------------------------------- two-shot with lazy direct access
-// Where the peer `peer` has its buffer (allocation `id`, address `addr` in ITS address space,
-// `bytes` long) mapped in this process, or null.  The table is written by the host, entry by
-// entry, the id last; it only grows.
-__device__ __forceinline__ char* auto_lookup(const CommDev& c, int peer, uint64_t id, uint64_t addr, uint64_t bytes) {
-  if (c.auto_map == nullptr || id == 0 || (addr & 15u) != 0) return nullptr;
-  const volatile AutoMapEntry* row = c.auto_map + peer * kAutoSlots;
-  for (int i = 0; i < kAutoSlots; ++i) {
-    const uint64_t eid = row[i].id;
-    if (eid == 0) break;
-    if (eid != id) continue;
-    const uint64_t base = row[i].peer_base, size = row[i].size;
-    if (addr >= base && addr + bytes <= base + size) return reinterpret_cast<char*>(row[i].local_base + (addr - base));
-    return nullptr;
-  }
-  return nullptr;
-}
-
 // The peer-to-peer two-shot AllReduce on ORDINARY device buffers (one type, any operator).  Planned
 // as the staged kernel (P.args: copy_in = copy_out = 1, staging views, passes of chunk_shard_vecs).
-// Before the first pass the ranks find out, inside the kernel, whether every rank can reach every
-// rank's buffers of this call directly (see AutoCtl); if so the same core runs once over the user
-// buffers themselves: no copy-in, no copy-out, no passes.  Two extra barriers per call.
+// Before the first pass the ranks find out, inside the kernel and with one extra barrier, whether
+// every rank can reach every rank's buffers of this call directly (see AutoDesc); if so the same core
+// runs once over the user buffers themselves: no copy-in, no copy-out, no passes.  All blocks of a
+// rank decide alike, because everything the decision rests on travels by value with the launch.
 template <typename T, int OP>
 __device__ __forceinline__ void twoshot_auto_body(const KParams& P, int blk, int nblk, BlockCtl& ctl) {
   __shared__ CollArgs direct;
-  __shared__ int s_have[kMaxRanks];
+  __shared__ AutoDesc s_desc[kAutoRanks];
   const CommDev& c = P.comm;
   const CollArgs& a = P.args;
   const int t = threadIdx.x, N = c.nranks, me = c.rank;
-  const uint64_t bytes = a.count * sizeof(typename Elem<T>::Raw);
   block_begin(c, blk, ctl);
-  const volatile AutoCtl* mine = reinterpret_cast<const volatile AutoCtl*>(c.ctrl[me] + c.off_auto);
+  const AutoCtl* mine = reinterpret_cast<const AutoCtl*>(c.ctrl[me] + c.off_auto);
   if (t < N && t != me) {
-    uint64_t* d = reinterpret_cast<AutoCtl*>(c.ctrl[t] + c.off_auto)->desc[blk][me];
-    d[0] = a.auto_send_id;
-    d[1] = reinterpret_cast<uint64_t>(a.send);
-    d[2] = a.auto_recv_id;
-    d[3] = reinterpret_cast<uint64_t>(a.recv);
+    // 48 bytes as three 16-byte stores; the same thread releases this peer's barrier flag afterwards
+    uint4* dst = reinterpret_cast<uint4*>(&reinterpret_cast<AutoCtl*>(c.ctrl[t] + c.off_auto)->desc[blk][me]);
+    const uint4* src = reinterpret_cast<const uint4*>(&a.auto_desc);
+    dst[0] = src[0];
+    dst[1] = src[1];
+    dst[2] = src[2];
   }
   if (t == 0) direct = a;
-  bool ok = block_barrier(c, blk, ctl);   // the same thread that wrote a peer's row releases that peer's flag
+  bool ok = block_barrier(c, blk, ctl);
   bool agreed = false;
-  if (ok) {
+  if (ok && N <= kAutoRanks && c.auto_map != nullptr) {
     if (t < N) {
-      char* in = static_cast<char*>(const_cast<void*>(a.send));
-      char* out = static_cast<char*>(a.recv);
-      int have = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0 ? 1 : 0;
-      if (t != me) {
-        const volatile uint64_t* d = mine->desc[blk][t];
-        in = auto_lookup(c, t, d[0], d[1], bytes);
-        out = auto_lookup(c, t, d[2], d[3], bytes);
-        have = (in != nullptr && out != nullptr) ? 1 : 0;
+      if (t == me) {
+        s_desc[t] = a.auto_desc;
+      } else {
+        const uint4* src = reinterpret_cast<const uint4*>(&mine->desc[blk][t]);
+        uint4* dst = reinterpret_cast<uint4*>(&s_desc[t]);
+        dst[0] = __ldcg(src);
+        dst[1] = __ldcg(src + 1);
+        dst[2] = __ldcg(src + 2);
       }
-      direct.in_peer[t] = in;
-      direct.out_peer[t] = out;
-      s_have[t] = have;
     }
     __syncthreads();
-    int have_all = 1;
-    for (int r = 0; r < N; ++r) have_all &= s_have[r];
-    if (t < N && t != me) reinterpret_cast<AutoCtl*>(c.ctrl[t] + c.off_auto)->vote[blk][me] = static_cast<uint32_t>(have_all);
-    ok = block_barrier(c, blk, ctl);
-    if (ok) {
-      agreed = have_all != 0;
-      for (int r = 0; r < N; ++r)
-        if (r != me && mine->vote[blk][r] == 0u) agreed = false;
+    // every rank evaluates the same words: rank q must have the slots of rank r's two buffers
+    agreed = true;
+    for (int r = 0; r < N; ++r) {
+      const uint32_t sl = s_desc[r].slots;
+      if (((sl >> 16) & 1u) == 0u) {
+        agreed = false;
+        break;
+      }
+      const uint32_t need = (1u << (sl & 15u)) | (1u << ((sl >> 8) & 15u));
+      for (int q = 0; q < N; ++q)
+        if (q != r && (s_desc[q].mask[r] & need) != need) agreed = false;
     }
-  }
-  if (ok) {
     if (agreed) {
-      if (t == 0) {
+      // warp 0 resolves the peers' send buffers, warp 1 their recv buffers
+      const int role = t >> 5, r = t & 31;
+      if (role < 2 && r < N) {
+        char* p = role == 0 ? static_cast<char*>(const_cast<void*>(a.send)) : static_cast<char*>(a.recv);
+        if (r != me) {
+          const uint32_t slot = (s_desc[r].slots >> (8 * role)) & 0xffu;
+          const uint64_t addr = role == 0 ? s_desc[r].send_addr : s_desc[r].recv_addr;
+          const uint4* e = reinterpret_cast<const uint4*>(c.auto_map + r * kAutoSlots + slot);
+          const uint4 lo = __ldcg(e), hi = __ldcg(e + 1);
+          const uint64_t base = (uint64_t(lo.w) << 32) | lo.z;
+          const uint64_t local = (uint64_t(hi.w) << 32) | hi.z;
+          p = reinterpret_cast<char*>(local + (addr - base));
+        }
+        if (role == 0) direct.in_peer[r] = p; else direct.out_peer[r] = p;
+      }
+      if (t == 64) {
         direct.copy_in = 0;
         direct.copy_out = 0;
         direct.in_mc = nullptr;
         direct.out_mc = nullptr;
-        direct.chunk_shard_vecs = (a.shard_elems + (16 / sizeof(typename Elem<T>::Raw)) - 1) / (16 / sizeof(typename Elem<T>::Raw));
+        constexpr uint64_t VW = 16 / sizeof(typename Elem<T>::Raw);
+        direct.chunk_shard_vecs = (a.shard_elems + VW - 1) / VW;
       }
-      __syncthreads();
-      if (blk == 0 && t == 0) {   // calls that ran on the user buffers directly (statistics)
+      if (blk == 0 && t == 96) {   // calls that ran on the user buffers directly (statistics)
         const uint32_t n = atomicAdd(&local_state(c)->pad[0], 1u) + 1u;
         if (c.host_progress) c.host_progress[6] = n;
       }
+      __syncthreads();
     }
-    twoshot_core<T, T, T, OP, false, kAllReduce>(c, agreed ? direct : a, blk, blk, nblk, ctl);
   }
+  if (ok) twoshot_core<T, T, T, OP, false, kAllReduce>(c, agreed ? direct : a, blk, blk, nblk, ctl);
   block_end(c, blk, nblk, ctl);
 }
-
 
 // -------------------------------------------------------------------- pipelined (ordinary buffers)
 // AllReduce of buffers that are NOT in symmetric memory, as ONE kernel whose blocks take three

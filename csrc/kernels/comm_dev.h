@@ -62,24 +62,35 @@ struct PipeCtl {
 };
 
 // Lazy direct access to ordinary device buffers (coll_kernels.cuh, twoshot_auto_body).  A rank exports
-// the allocations its buffers live in (CUDA IPC) and maps what its peers have exported; which peer
-// allocation is mapped where is listed in a table in host-mapped memory, one row per peer.  Inside
-// the kernel every rank tells every peer which buffers it passed to THIS call (allocation id and
-// address, pushed into the peer's AutoCtl before a barrier), looks the peers' buffers up in its
-// table, and tells the peers whether it found them all; only when every rank did, the kernel reads
-// and writes the user buffers directly, otherwise it stages as before.  No host-side agreement is
-// needed and a rank that has not mapped a peer's buffer yet merely delays the switch.
+// the allocations its buffers live in (CUDA IPC; export slots 0..kAutoSlots-1, never reused) and maps
+// what its peers have exported; row [peer][slot] of a table in device memory says where that peer's
+// slot is mapped here.  With every launch the host passes, by value, which slots of which peer it had
+// mapped when it launched (a bit mask per peer) and which of its own slots hold this call's buffers.
+// Inside the kernel every rank pushes that, with the buffers' addresses, into every peer's AutoCtl
+// before ONE barrier; afterwards every rank holds every rank's word and all of them evaluate the same
+// condition: "every rank has the slots of every other rank's buffers mapped".  Only then the kernel
+// reads and writes the user buffers directly, otherwise it stages as before.  Nothing is agreed on
+// the host, a rank that has not mapped a peer's buffer yet merely delays the switch, and what the
+// host maps while a kernel runs cannot split that kernel's blocks (the masks travel by value).
 constexpr int kAutoSlots = 16;        // exported allocations per rank
+constexpr int kAutoRanks = 8;         // ranks the masks of one descriptor cover
 constexpr int kAutoBlocks = 128;      // grid cap of the kernel (rows of AutoCtl)
 struct AutoMapEntry {
-  uint64_t id;          // allocation id in the exporting process (0: empty; written last)
+  uint64_t id;          // allocation id in the exporting process (informative)
   uint64_t peer_base;   // its address range in the exporting process
   uint64_t size;
   uint64_t local_base;  // where this process mapped it
 };
+// What a rank tells every peer about one call.
+struct alignas(16) AutoDesc {
+  uint64_t send_addr, recv_addr;   // in the sender's address space
+  uint32_t slots;                  // send slot | recv slot << 8 | usable << 16 (exported, in range, 16-byte aligned)
+  uint32_t pad;
+  uint16_t mask[kAutoRanks];       // mask[r]: export slots of rank r that the sender has mapped
+  uint64_t pad2;
+};
 struct AutoCtl {
-  uint64_t desc[kAutoBlocks][kMaxRanks][4];   // from every peer: send id, send address, recv id, recv address
-  uint32_t vote[kAutoBlocks][kMaxRanks];      // from every peer: 1 = it can reach every rank's buffers
+  AutoDesc desc[kAutoBlocks][kMaxRanks];   // [block][source rank], written by the peers
 };
 
 struct CommDev {
@@ -94,7 +105,7 @@ struct CommDev {
   uint64_t off_pipe;              // PipeCtl
   uint64_t ll_slot_bytes, inbox_slot_bytes, stage_bytes;
   uint64_t off_auto;              // AutoCtl
-  const AutoMapEntry* auto_map;   // [kMaxRanks][kAutoSlots] in host-mapped memory, or null
+  const AutoMapEntry* auto_map;   // [kMaxRanks][kAutoSlots] in device memory, or null
 };
 
 // Arguments of one AllReduce / ReduceScatter / AllGather launch.
@@ -115,8 +126,7 @@ struct CollArgs {
   int32_t copy_out;          // 1: outputs are copied from stage_b to `recv`
   int32_t pipe_ramp;         // pipelined kernel: number of small first chunks (CE / 2^R ... CE / 2), see pipe_chunk_geom
   int32_t pad0;
-  uint64_t auto_send_id;     // twoshot_auto_body: allocation ids of `send` and `recv` (0: not exported)
-  uint64_t auto_recv_id;
+  AutoDesc auto_desc;        // twoshot_auto_body: what this rank tells its peers about the call
 };
 
 struct KParams {
