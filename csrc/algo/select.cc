@@ -119,7 +119,14 @@ Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
     // than the stream pipeline on two GPUs (800 against 605 us), so two ranks and the other operators
     // keep that one.
     const bool pipe_auto = caps.nvls && N > 2 && nvls_types;
-    if (ordinary && pipe_auto && !in.host_memory && cfg.pipe_min_bytes != 0 && wire_bytes >= cfg.pipe_min_bytes) algo = Algo::Pipe;
+    // Four GPUs, ordinary device buffers: the peer-to-peer two-shot kernel running on the user buffers
+    // directly (lazy direct access) measured ahead of the staged switch kernel and of the pipelined
+    // kernel from 8 MB to 128 MB (16 MB: 71 against 81 us; 32 MB: 109 against 146; 128 MB: 349 against
+    // 367; NCCL 71 / 120 / 354) and behind the pipelined kernel at 256 MB (663 against 655).
+    const bool direct_auto = ordinary && in.auto_eligible && !in.host_memory && N > 2 && N <= 4 &&
+                             wire_bytes >= (8u << 20) && wire_bytes < (192u << 20);
+    if (direct_auto) algo = Algo::TwoShot;
+    else if (ordinary && pipe_auto && !in.host_memory && cfg.pipe_min_bytes != 0 && wire_bytes >= cfg.pipe_min_bytes) algo = Algo::Pipe;
     else if (wire_bytes <= th.ll_max && wire_bytes * 2 <= caps.ll_slot_bytes) algo = Algo::LL;
     else if (wire_bytes <= th.oneshot_max && wire_bytes <= caps.inbox_slot_bytes) algo = Algo::OneShot;
     else if (nvls_usable && wire_bytes >= th.nvls_min) algo = Algo::Nvls;

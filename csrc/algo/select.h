@@ -47,6 +47,8 @@ struct PlanInput {
   bool out_symmetric = false;  // recv buffer lies in symmetric memory (16-byte aligned)
   bool in_has_mc = false, out_has_mc = false;  // those segments have multicast mappings
   bool host_memory = false;     // a buffer is pinned host memory (never taken by the pipelined kernel)
+  bool auto_eligible = false;  // both buffers are ordinary device memory of one type and lazy direct access is on:
+                               // the two-shot kernel can run on them directly once every rank has mapped them
   Algo forced = Algo::Auto;
 };
 

@@ -689,6 +689,8 @@ void Comm::launch(Mode mode, const void* send, DType send_t, void* recv, DType r
   if (send_kind == MemKind::PlainHost || recv_kind == MemKind::PlainHost)
     fail(Result::InvalidArgument, "buffers must be device memory or pinned host memory on the GPU data plane");
   pi.host_memory = send_kind == MemKind::PinnedHost || recv_kind == MemKind::PinnedHost;
+  pi.auto_eligible = auto_shm_ != nullptr && cfg_.auto_map && mode == Mode::AllReduce && size_ > 1 && !in_seg && !out_seg &&
+                     send_t == wire_t && recv_t == wire_t && send_kind == MemKind::Device && recv_kind == MemKind::Device;
   Plan plan = make_plan(pi, caps_, cfg_);
   if (!plan.valid) fail(Result::InvalidArgument, std::string("no kernel for this request: ") + plan.reason);
   if (!kernel_exists(plan.spec)) fail(Result::InvalidArgument, "no kernel for this type / operator combination");
@@ -1364,6 +1366,7 @@ Algo Comm::query_algo(size_t bytes, DType t, RedOp op, bool registered) {
   pi.op = op;
   pi.in_symmetric = pi.out_symmetric = registered;
   pi.in_has_mc = pi.out_has_mc = registered && caps_.nvls;
+  pi.auto_eligible = !registered && auto_shm_ != nullptr && cfg_.auto_map;   // as for ordinary device buffers
   pi.forced = parse_algo(cfg_.algo);
   if (pi.forced == Algo::Ring) pi.forced = Algo::Auto;
   Plan p = make_plan(pi, caps_, cfg_);

@@ -321,10 +321,11 @@ MNCCL_EXPORT int mnccl_test_plan(int nranks, int mode, uint64_t count, int in_t,
   pi.wire = static_cast<DType>(wire_t);
   pi.out = static_cast<DType>(out_t);
   pi.op = static_cast<RedOp>(op);
-  pi.in_symmetric = in_sym;
-  pi.out_symmetric = out_sym;
-  pi.in_has_mc = in_sym && nvls;
-  pi.out_has_mc = out_sym && nvls;
+  pi.in_symmetric = (in_sym & 1) != 0;
+  pi.out_symmetric = (out_sym & 1) != 0;
+  pi.auto_eligible = (in_sym & 2) != 0;   // bit 1 of in_sym: ordinary device buffers with lazy direct access on
+  pi.in_has_mc = pi.in_symmetric && nvls;
+  pi.out_has_mc = pi.out_symmetric && nvls;
   pi.forced = static_cast<Algo>(forced);
   Plan p = make_plan(pi, caps, cfg);
   if (!p.valid) return 1;
