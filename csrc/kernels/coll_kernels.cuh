@@ -250,8 +250,13 @@ __device__ __forceinline__ void oneshot_body(const KParams& P, int blk, int nblk
 // for the cross-rank barrier, (`blk`, `nblk`) its place among the blocks that share this message.
 // They differ when one kernel serves two messages with two groups of blocks (the NVLS + peer-to-peer
 // split of k_nvls.cu).
+//
+// `synced`: the caller has just passed a cross-rank barrier of its own and nothing is staged, so the
+// first pass needs no barrier 1 (every rank's kernel has started: its inputs are in place; the previous
+// call ended with a barrier).
 template <typename InT, typename WireT, typename OutT, int OP, bool NVLS, int MODE, int kUnroll = 4>
-__device__ __forceinline__ void twoshot_core(const CommDev& c, const CollArgs& a, int sig_blk, int blk, int nblk, BlockCtl& ctl) {
+__device__ __forceinline__ void twoshot_core(const CommDev& c, const CollArgs& a, int sig_blk, int blk, int nblk, BlockCtl& ctl,
+                                             bool synced = false) {
   using Acc = typename Elem<WireT>::Acc;
   using OAcc = typename Elem<OutT>::Acc;
   constexpr int VW = 16 / sizeof(typename Elem<WireT>::Raw);
@@ -300,8 +305,10 @@ __device__ __forceinline__ void twoshot_core(const CommDev& c, const CollArgs& a
     }
     // Barrier 1: every rank's inputs are in place, and every rank has left the
     // previous pass (so its staging / receive buffers may be written again).
-    ok = block_barrier(c, sig_blk, ctl);
-    if (!ok) break;
+    if (!(synced && v0 == 0 && !staged_in)) {
+      ok = block_barrier(c, sig_blk, ctl);
+      if (!ok) break;
+    }
 
     // ---- phase B: reduce my shard and hand the result out (AllGather: push my shard)
     if (MODE == kAllGather) {
@@ -540,7 +547,8 @@ __device__ __forceinline__ void twoshot_auto_body(const KParams& P, int blk, int
       __syncthreads();
     }
   }
-  if (ok) twoshot_core<T, T, T, OP, false, kAllReduce>(c, agreed ? direct : a, blk, blk, nblk, ctl);
+  // direct: the agreement's barrier stands in for the core's first one
+  if (ok) twoshot_core<T, T, T, OP, false, kAllReduce>(c, agreed ? direct : a, blk, blk, nblk, ctl, agreed);
   block_end(c, blk, nblk, ctl);
 }
 

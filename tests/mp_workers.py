@@ -205,7 +205,10 @@ def gpu_battery(rank, n, kw):
     torch.cuda.synchronize()
     err = float(np.abs(big_out.cpu().numpy() - want).max())
     assert err <= (1e-5 * n if res["nvls"] else 0.0), f"pipelined AllReduce: err {err}"
-    assert comm.stats()["pipelined_calls"] >= 1
+    # ... which is, by rank count and what the machine offers: the two-shot kernel with lazy direct access,
+    # the pipelined kernel, or copy kernels on side streams around the collective
+    st_big = comm.stats()
+    assert (st_big["pipelined_calls"] >= 1 or st_big["algo"].get("pipe", 0) >= 1 or st_big["auto_map"]["exports"] >= 1), st_big
     gp = torch.cuda.CUDAGraph()
     sp = torch.cuda.Stream()
     sp.wait_stream(torch.cuda.current_stream())
@@ -231,7 +234,7 @@ def gpu_battery(rank, n, kw):
     torch.cuda.synchronize()
     assert np.array_equal(reg.cpu().numpy(), want), "registered buffer: mismatch"
     st = comm.stats()
-    assert st["zero_copy_in"] == zc0 + 1 and st["ipc_cache"]["open"] == n - 1
+    assert st["zero_copy_in"] == zc0 + 1 and st["ipc_cache"]["open"] >= n - 1   # lazy direct access may hold mappings too
     view = reg[1024:1024 + 4096]            # a view inside the same allocation hits the handle cache
     comm.register(view)
     assert comm.stats()["ipc_cache"]["hits"] >= 0
