@@ -121,10 +121,11 @@ Plan make_plan(const PlanInput& in, const CommCaps& caps, const Config& cfg) {
     const bool pipe_auto = caps.nvls && N > 2 && nvls_types;
     // Four GPUs, ordinary device buffers: the peer-to-peer two-shot kernel running on the user buffers
     // directly (lazy direct access) measured ahead of the staged switch kernel and of the pipelined
-    // kernel from 8 MB to 128 MB (16 MB: 71 against 81 us; 32 MB: 109 against 146; 128 MB: 349 against
-    // 367; NCCL 71 / 120 / 354) and behind the pipelined kernel at 256 MB (663 against 655).
+    // kernel from 4 MB to 128 MB (4 MB: 36.7 against 40.6 us; 16 MB: 67 against 81; 32 MB: 104 against
+    // 146; 128 MB: 349 against 367; NCCL 35.2 / 70.6 / 119 / 354) and behind the pipelined kernel at
+    // 256 MB (663 against 655); at 2 MB the one-shot kernel is faster (25.9 against 32.7).
     const bool direct_auto = ordinary && in.auto_eligible && !in.host_memory && N > 2 && N <= 4 &&
-                             wire_bytes >= (8u << 20) && wire_bytes < (192u << 20);
+                             wire_bytes >= (4u << 20) && wire_bytes < (192u << 20);
     if (direct_auto) algo = Algo::TwoShot;
     else if (ordinary && pipe_auto && !in.host_memory && cfg.pipe_min_bytes != 0 && wire_bytes >= cfg.pipe_min_bytes) algo = Algo::Pipe;
     else if (wire_bytes <= th.ll_max && wire_bytes * 2 <= caps.ll_slot_bytes) algo = Algo::LL;

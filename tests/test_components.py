@@ -133,13 +133,15 @@ def plan(lib, n, count, dtype=_lib.FLOAT32, op=_lib.SUM, mode=0, in_sym=0, out_s
 
 def test_planner_direct_two_shot_for_ordinary_buffers_on_four_gpus(lib):
     """Ordinary device buffers with lazy direct access on (bit 1 of in_sym): four GPUs take the peer-to-peer
-    two-shot kernel from 8 MB to below 192 MB, where it measured ahead of the staged switch kernel and of
+    two-shot kernel from 4 MB to below 192 MB, where it measured ahead of the staged switch kernel and of
     the pipelined kernel; other rank counts, sizes and ineligible buffers keep their choice.  The choice
     never depends on what has been mapped so far."""
     mb = 1 << 18  # fp32 elements per MB
     assert plan(lib, 4, 16 * mb, nvls=1, in_sym=2)["algo"] == "twoshot"
     assert plan(lib, 4, 128 * mb, nvls=1, in_sym=2)["algo"] == "twoshot"
-    assert plan(lib, 4, 4 * mb, nvls=1, in_sym=2)["algo"] == "nvls"
+    assert plan(lib, 4, 4 * mb, nvls=1, in_sym=2)["algo"] == "twoshot"
+    assert plan(lib, 4, 3 * mb, nvls=1, in_sym=2)["algo"] == "nvls"
+    assert plan(lib, 4, 2 * mb, nvls=1, in_sym=2)["algo"] == "oneshot"
     assert plan(lib, 4, 256 * mb, nvls=1, in_sym=2)["algo"] == "pipe"
     assert plan(lib, 4, 16 * mb, nvls=1, in_sym=0)["algo"] == "nvls"
     assert plan(lib, 8, 16 * mb, nvls=1, in_sym=2)["algo"] == "nvls"

@@ -72,12 +72,14 @@ def test_hera_bootstrap_and_stall_bounded_failure(free_port, lib):
 
 
 @pytest.mark.multigpu(2)
+@pytest.mark.parametrize("M", [1024, 256])
 @pytest.mark.parametrize("in_switch", [1, 0])
-def test_fused_tensor_parallel_kernels(free_port, in_switch):
+def test_fused_tensor_parallel_kernels(free_port, in_switch, M):
     """Both forms of GEMM -> reduce-scatter: partial tiles summed by the switch (where it can), or pushed
-    to their owner and summed there."""
+    to their owner and summed there.  M = 1024: 512 rows per rank, CTA pairs; M = 256: 128 rows per rank,
+    single-CTA tiles (with their own communication CTAs in the switch form)."""
     n = 2
-    res = run_ranks("gpu_tp", n, {"M": 1024, "N": 1024, "K": 512},
+    res = run_ranks("gpu_tp", n, {"M": M, "N": 1024, "K": 512},
                     {"MINI_NCCL_BOOTSTRAP_PORT": free_port, "MINI_NCCL_RS_SWITCH": in_switch}, timeout=300)
     assert len(res) == n and all(r["worst"] < 3e-2 for r in res)
     if not in_switch:
