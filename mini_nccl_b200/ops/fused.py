@@ -3,8 +3,9 @@
 ``GemmReduceScatter``: ``out[M/R, N] = reduce_scatter(A_r[M, K_r] @ B_r[N, K_r].T)`` -- one kernel.
 Where the NVSwitch can reduce (NVLS), the partial tiles stay on their rank and the owner of a row block
 sums all ranks' copies in the switch (``multimem.ld_reduce``) while the remaining tiles are computed;
-otherwise (two GPUs without a multicast mapping, ``MINI_NCCL_NVLS_ENABLE=0``, ``MINI_NCCL_RS_SWITCH=0``)
-tiles are pushed to their owner over NVLink and summed there in rank order.
+otherwise (no multicast mapping, ``MINI_NCCL_NVLS_ENABLE=0``, ``MINI_NCCL_RS_SWITCH=0``, or more than four
+ranks unless ``MINI_NCCL_RS_SWITCH=1``: that size has not been measured) tiles are pushed to their owner
+over NVLink and summed there in rank order.
 ``AllGatherGemm``: ``C[M, N_r] = all_gather(X_r)[M, K] @ B_r[N_r, K].T`` -- one kernel; a few CTAs push
 the local shard to the peers while the others already compute on the local rows.
 
@@ -78,9 +79,12 @@ class GemmReduceScatter:
         self._stage_peers = _peers(comm, self.stage)
         self._flag_peers = _peers(comm, self.flags)
         self._handle = comm.device_handle_bytes()
-        # multicast address of the staging: the in-switch sum needs it (0: peer-to-peer kernel)
+        # multicast address of the staging: the in-switch sum needs it (0: peer-to-peer kernel).  The
+        # in-switch form is the default on up to four ranks, where it has been measured (TP=4: 116.8
+        # against 121.4 us); with more ranks it has to be asked for (MINI_NCCL_RS_SWITCH=1).
         self._mc = 0
-        if R > 1 and os.environ.get("MINI_NCCL_RS_SWITCH", "1") != "0" and hasattr(L, "mncclGemmReduceScatterBf16Switch"):
+        want = os.environ.get("MINI_NCCL_RS_SWITCH", "1" if R <= 4 else "0")
+        if R > 1 and want != "0" and hasattr(L, "mncclGemmReduceScatterBf16Switch"):
             self._mc = comm.peer_pointers(self.stage)[1]
         # CTAs that only sum finished tiles in the switch form (0: the kernel's default of 16)
         self.n_comm_ctas = int(os.environ.get("MINI_NCCL_RS_COMM_CTAS", "0"))

@@ -310,7 +310,7 @@ def test_ll_calls_with_changing_block_counts(worlds):
         assert w.last_plan() == ("ll", nb)
 
 
-@pytest.mark.parametrize("n", [2, 4])
+@pytest.mark.parametrize("n", [2, 4, 8])
 def test_lazy_direct_access_agrees_inside_the_kernel(lib, n):
     """The two-shot kernel on ordinary buffers goes direct only when EVERY rank has EVERY rank's buffers
     in its table; one missing row on one rank keeps all ranks on the staged path.  Bit-exact either way,
