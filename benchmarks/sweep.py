@@ -52,8 +52,26 @@ def _time_loop(fn, iters, warmup, world, repeats=1):
     return sorted(seen)[(len(seen) - 1) // 2]
 
 
+def nccl_registered_buffer(numel, dtype):
+    """A tensor from NCCL's own allocator (ncclMemAlloc through ``torch.cuda.MemPool``), registered with the
+    process group's communicator, so that NCCL can use it in place (and through the switch): the
+    like-for-like partner of this library's symmetric buffers.  Returns (tensor, pool) or (None, reason)."""
+    import torch
+    import torch.distributed as dist
+
+    try:
+        backend = dist.group.WORLD._get_backend(torch.device("cuda"))
+        pool = torch.cuda.MemPool(backend.mem_allocator)
+        with torch.cuda.use_mem_pool(pool):
+            t = torch.empty(numel, dtype=dtype, device="cuda")
+        backend.register_mem_pool(pool)
+        return t, pool
+    except Exception as e:  # an older torch, an NCCL without the allocator, ...
+        return None, f"{type(e).__name__}: {e}"[:120]
+
+
 def run_sweep(comm, world, rank, max_bytes=1 << 30, min_bytes=8 << 10, quick=False, dtypes=("fp32", "bf16"),
-              algos=("auto",), with_nccl=True, graphs=True):
+              algos=("auto",), with_nccl=True, graphs=True, nccl_registered=False):
     import torch
     import torch.distributed as dist
 
@@ -73,6 +91,9 @@ def run_sweep(comm, world, rank, max_bytes=1 << 30, min_bytes=8 << 10, quick=Fal
         if world > 1:
             sym[dt_name] = comm.empty(sym_cap // esz, dt)
         plain = torch.empty(sym_cap // esz, dtype=dt, device="cuda")
+        reg, reg_pool = (None, None)
+        if nccl_registered and with_nccl and world > 1:
+            reg, reg_pool = nccl_registered_buffer(sym_cap // esz, dt)
         gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
         init = torch.randn(min(sym_cap // esz, 1 << 24), generator=gen, device="cuda").to(dt)
         for nbytes in sizes:
@@ -150,6 +171,15 @@ def run_sweep(comm, world, rank, max_bytes=1 << 30, min_bytes=8 << 10, quick=Fal
                     except Exception as e:
                         row["nccl_graph_err"] = str(e)[:80]
                 q.zero_()
+                if reg is not None:
+                    # NCCL on a buffer from its own registered pool: the partner of "ours, symmetric buffers"
+                    qr = reg[:n]
+                    qr.zero_()
+                    ms = _time_loop(lambda: dist.all_reduce(qr), iters, warm, world, reps)
+                    row["nccl_registered_us"] = round(ms * 1e3, 2)
+                    row["nccl_registered_busbw"] = round(bus_bandwidth_gbs(nbytes, ms, world)[1], 2)
+                elif nccl_registered and isinstance(reg_pool, str):
+                    row["nccl_registered_err"] = reg_pool
             rows.append(row)
         del plain
     for t in sym.values():
@@ -170,6 +200,8 @@ def main():
     ap.add_argument("--dtypes", default="fp32,bf16")
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--no-nccl", action="store_true")
+    ap.add_argument("--nccl-registered", action="store_true",
+                    help="also time NCCL on a buffer from its own registered pool (ncclMemAlloc through torch.cuda.MemPool)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -184,7 +216,8 @@ def main():
 
     comm = mn.Communicator(world, rank, os.environ["MASTER_ADDR"])
     res = run_sweep(comm, world, rank, max_bytes=args.max_bytes, min_bytes=args.min_bytes, quick=args.quick,
-                    dtypes=tuple(args.dtypes.split(",")), algos=tuple(args.algos.split(",")), with_nccl=not args.no_nccl)
+                    dtypes=tuple(args.dtypes.split(",")), algos=tuple(args.algos.split(",")), with_nccl=not args.no_nccl,
+                    nccl_registered=args.nccl_registered)
     res["stats"] = comm.stats()
     if rank == 0:
         text = json.dumps(res)
