@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Headline benchmark: AllReduce bus bandwidth (the metric BASELINE.json names).
+"""Headline benchmark: AllReduce bus bandwidth, the reference benchmark's own metric (reference: tests/perf_test.cpp:140-143).
 
 One "step" is one fp32 sum AllReduce of 256 MiB per rank through the library's
 public Python API (Communicator.all_reduce on a tensor from Communicator.empty),
