@@ -32,7 +32,7 @@ def main():
     from mini_nccl_b200 import _lib
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("--target", required=True, choices=["gemm", "gemm_pair", "copy", "twoshot", "oneshot", "gemm_rs", "ag_gemm", "swiglu", "ll", "pipe", "noalloc"])
+    ap.add_argument("--target", required=True, choices=["gemm", "gemm_pair", "copy", "twoshot", "oneshot", "gemm_rs", "ag_gemm", "swiglu", "ll", "pipe", "noalloc", "auto_direct"])
     ap.add_argument("--launches", type=int, default=4)
     args = ap.parse_args()
     torch.cuda.set_device(0)
@@ -114,6 +114,26 @@ def main():
         torch.cuda.synchronize()
         st = (C.c_uint32 * n)()
         assert lib.mncclEmuStatus(world, st, None) == 0 and list(st) == [0] * n
+        lib.mncclEmuDestroy(world)
+    elif args.target == "auto_direct":
+        # four virtual ranks, ORDINARY buffers (plain device tensors), every rank's table complete: the
+        # two-shot kernel with lazy direct access agrees inside the kernel and runs on the buffers directly
+        n = 4
+        world = C.c_void_p()
+        assert lib.mncclEmuCreate(n, 8 << 20, C.byref(world)) == 0
+        count = 16 << 20                                     # 64 MiB fp32 per rank, far above the 8 MiB staging
+        bufs = [torch.randn(count, device="cuda") for _ in range(n)]
+        ptrs = (C.c_void_p * n)(*[b.data_ptr() for b in bufs])
+        assert lib.mncclEmuSetAutoMap(world, (C.c_int * (n * n))(*([1] * (n * n)))) == 0
+        for _ in range(args.launches):
+            rc = lib.mncclEmuCollective(world, 0, ptrs, ptrs, count, _lib.FLOAT32, _lib.FLOAT32, _lib.FLOAT32, _lib.SUM,
+                                        0.25, _lib.ALGO_TWOSHOT, 0, None)
+            assert rc == 0, rc
+        torch.cuda.synchronize()
+        st = (C.c_uint32 * n)()
+        assert lib.mncclEmuStatus(world, st, None) == 0 and list(st) == [0] * n
+        direct = (C.c_uint32 * n)()
+        assert lib.mncclEmuDirectCalls(world, direct) == 0 and list(direct) == [args.launches] * n, list(direct)
         lib.mncclEmuDestroy(world)
     elif args.target == "copy":
         comm = mn.Communicator(1, 0)
