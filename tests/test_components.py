@@ -412,3 +412,23 @@ def test_soft_provider_rejects_bad_key_and_range(lib, free_port, cma):
     if rc == -1:
         pytest.skip("cross-memory attach is not permitted on this machine")
     assert rc == 0, f"check {rc} failed"
+
+
+def test_switch_tie_rule_accepts_only_true_ties():
+    """The oracle check of the in-switch GEMM -> reduce-scatter: the other bf16 neighbour is accepted exactly
+    where the exact sum lies halfway between two bf16 values, nowhere else."""
+    import numpy as np
+
+    from mini_nccl_b200.utils import oracle as O
+    from mini_nccl_b200.utils.verify import switch_ties
+
+    exact = np.array([257.0, 258.0, 259.0, 513.0, 514.0, 100.0, -257.0], dtype=np.float32)
+    want = O.f32_to_bf16_bits(exact)                       # nearest-even: 256, 258, 260, 512, 512, 100, -256
+    assert list(O.bf16_bits_to_f32(want)) == [256.0, 258.0, 260.0, 512.0, 512.0, 100.0, -256.0]
+    other = O.f32_to_bf16_bits(np.array([258.0, 258.0, 258.0, 516.0, 516.0, 100.0, -258.0], dtype=np.float32))
+    tie = switch_ties(other, want, exact)
+    # 257, 259 and -257 are ties between their neighbours; 513 is not (512 is nearer than 516); 514 is a tie
+    assert list(tie) == [True, False, True, False, True, False, True]
+    wrong = want.copy()
+    wrong[5] = O.f32_to_bf16_bits(np.array([100.5], dtype=np.float32))[0]
+    assert not switch_ties(wrong, want, exact).any(), "an ordinary mismatch is never excused"
