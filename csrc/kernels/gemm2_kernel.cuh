@@ -71,7 +71,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     __syncthreads();
     if (threadIdx.x == 0) {
       report_failure(g, s_abort);
-      finish_epoch(g, s_epoch);
+      if (finish_epoch(g, s_epoch)) epi.last_cta_out(g, s_epoch);
     }
     return;
   }
@@ -306,7 +306,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   }
   if (threadIdx.x == 0) {
     report_failure(g, ctl->abort);
-    finish_epoch(g, epoch);
+    if (finish_epoch(g, epoch)) epi.last_cta_out(g, epoch);
   }
 }
 

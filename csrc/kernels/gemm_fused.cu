@@ -313,6 +313,7 @@ struct RsEpilogue {
                                            volatile uint32_t* abort_flag, uint8_t*, uint32_t) const {
     if (mc_stage != nullptr) reduce_switch<kThreads, true>(g, epoch, static_cast<int>(threadIdx.x), abort_flag);
   }
+  __device__ __forceinline__ void last_cta_out(const GemmArgs&, uint32_t) const {}
 };
 
 // ------------------------------------------------------------------ all-gather -> GEMM
@@ -323,7 +324,8 @@ struct AgEpilogue {
   int lda;                           // row stride of the gather buffers, elements
   char* xg[kMaxTpRanks];             // every rank's gather buffer [M, K] bf16
   uint32_t* ready[kMaxTpRanks];      // every rank's chunk counters [M / 128]
-  uint32_t* bar[kMaxTpRanks];        // every rank's barrier words [n_comm][nranks]
+  uint32_t* bar[kMaxTpRanks];        // every rank's barrier words [n_comm][nranks] (unused since the done words)
+  int done_base;                     // ready[r] + done_base + s: rank s has left its call number (value); see last_cta_out
   StoreEpilogue<false> plain;
 
   int swiglu;                        // 1: the store applies SwiGLU (see store_swiglu); C is [M, N / 2]
@@ -386,8 +388,17 @@ struct AgEpilogue {
   __device__ __forceinline__ void tile_done(const GemmArgs&, uint32_t, int, int, int, int, uint8_t*) const {}
   __device__ __forceinline__ void after_tiles(const GemmArgs&, uint32_t, int, int, int, int, volatile uint32_t*, uint8_t*) const {}
 
-  // A communication CTA: barrier with the same CTA of every peer (everyone has left the previous
-  // use of the gather buffers), then push the local shard to every peer with the TMA engine:
+  // The last CTA of the kernel (every tile done, every row of the gather buffer read): tell every peer
+  // that this rank's gather buffer is free for the pushes of the next call.
+  __device__ __forceinline__ void last_cta_out(const GemmArgs&, uint32_t epoch) const {
+    if (nranks <= 1 || ready[rank] == nullptr) return;
+    __threadfence_system();
+    for (int p = 0; p < nranks; ++p)
+      if (p != rank) st_release_sys_u32(ready[p] + done_base + rank, epoch);
+  }
+
+  // A communication CTA: wait until every peer has left the previous use of its gather buffer, then
+  // push the local shard to every peer with the TMA engine:
   // bulk copies local memory -> shared memory -> peer memory, a ring of row-sized slots, driven by
   // one thread.  Work items are (peer, chunk of 128 rows, quarter of the chunk), dealt round-robin
   // to the communication CTAs in the order the peers will need them; each finished quarter adds
@@ -396,10 +407,12 @@ struct AgEpilogue {
                                            volatile uint32_t* abort_flag, uint8_t* smem, uint32_t smem_base) const {
     __shared__ uint64_t s_full[kAgSlots];
     const int t = threadIdx.x;
-    if (t < nranks && t != rank) {
-      st_release_sys_u32(bar[t] + cta * nranks + rank, epoch);
-      wait_flag_sys(bar[rank] + cta * nranks + t, epoch, abort_flag, g);
-    }
+    // A peer's gather buffer may be written again once that peer has LEFT its previous call (it reads
+    // the rows until then).  Every rank says so when its kernel ends (last_cta_out), so in a steady
+    // sequence of calls this wait finds its word already there: the pushes start at once and do not
+    // wait for the peers to start their kernels, as a barrier here would (and did).
+    (void)cta;
+    if (t < nranks && t != rank) wait_flag_sys(ready[rank] + done_base + t, epoch - 1u, abort_flag, g);
     if (t == 0) {
       for (int i = 0; i < kAgSlots; ++i) mbar_init(smem_u32(&s_full[i]), 1);
       fence_barrier_init();
@@ -504,7 +517,8 @@ MNCCL_EXPORT size_t mncclGemmRsStageBytes(int M, int N, int /*nranks*/) {
 MNCCL_EXPORT size_t mncclGemmRsFlagWords(int M, int N, int nranks) {
   return size_t(nranks) * (M / nranks / kBM) * ((N + 127) / 128);  // sized for the narrowest tile
 }
-MNCCL_EXPORT size_t mncclAgGemmReadyWords(int M) { return size_t(M) / kBM; }
+// chunk counters [M / 128], then one "has left call number ..." word per source rank
+MNCCL_EXPORT size_t mncclAgGemmReadyWords(int M) { return size_t(M) / kBM + kMaxTpRanks; }
 MNCCL_EXPORT size_t mncclAgGemmBarWords(int nranks, int n_comm) { return size_t(nranks) * n_comm; }
 
 // out[M/nranks, N] (rows of this rank) = sum over ranks of A_r[M, K] * B_r[N, K]^T, bf16.
@@ -684,6 +698,7 @@ static int ag_gemm_launch(void* const* xg_peers, const void* B, void* C, int M, 
   epi.lda = lda;
   epi.swiglu = swiglu ? 1 : 0;
   epi.chunks_per_tile = bn / 32;
+  epi.done_base = M / kBM;
   for (int r = 0; r < nranks; ++r) {
     epi.xg[r] = static_cast<char*>(xg_peers[r]);
     epi.ready[r] = nranks > 1 ? static_cast<uint32_t*>(ready_peers[r]) : nullptr;

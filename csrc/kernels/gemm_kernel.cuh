@@ -45,9 +45,10 @@ __device__ __forceinline__ void report_failure(const GemmArgs& g, uint32_t code)
   }
 }
 
-// Last CTA out publishes the new epoch of a fused op (see GemmArgs::epoch_ptr).
-__device__ __forceinline__ void finish_epoch(const GemmArgs& g, uint32_t epoch) {
-  if (g.epoch_ptr == nullptr) return;
+// Last CTA out publishes the new epoch of a fused op (see GemmArgs::epoch_ptr).  Returns true in
+// that CTA, whose caller then gives the epilogue its say (Epilogue::last_cta_out).
+__device__ __forceinline__ bool finish_epoch(const GemmArgs& g, uint32_t epoch) {
+  if (g.epoch_ptr == nullptr) return false;
   __threadfence();
   const uint32_t t = atomicAdd(g.ticket_ptr, 1u);
   if (t == gridDim.x - 1) {
@@ -59,7 +60,9 @@ __device__ __forceinline__ void finish_epoch(const GemmArgs& g, uint32_t epoch) 
       const uint32_t d = atomicAdd(g.err + 2, 1u) + 1u;
       st_volatile_sys_u32(g.comm_progress + 5, d);
     }
+    return true;
   }
+  return false;
 }
 
 // True when the communicator's abort word is set (polled by every wait on a peer).
@@ -108,7 +111,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     __syncthreads();
     if (threadIdx.x == 0) {
       report_failure(g, s_abort);
-      finish_epoch(g, s_epoch);
+      if (finish_epoch(g, s_epoch)) epi.last_cta_out(g, s_epoch);
     }
     return;
   }
@@ -274,7 +277,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   }
   if (threadIdx.x == 0) {
     report_failure(g, ctl->abort);
-    finish_epoch(g, epoch);
+    if (finish_epoch(g, epoch)) epi.last_cta_out(g, epoch);
   }
 }
 

@@ -191,6 +191,7 @@ struct StoreEpilogue {
   __device__ __forceinline__ void tile_done(const GemmArgs&, uint32_t, int, int, int, int, uint8_t*) const {}
   __device__ __forceinline__ void after_tiles(const GemmArgs&, uint32_t, int, int, int, int, volatile uint32_t*, uint8_t*) const {}
   __device__ __forceinline__ void comm_cta(const GemmArgs&, uint32_t, int, int, volatile uint32_t*, uint8_t*, uint32_t) const {}
+  __device__ __forceinline__ void last_cta_out(const GemmArgs&, uint32_t) const {}
 };
 
 bool make_tensor_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_elems,
