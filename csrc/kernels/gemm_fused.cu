@@ -12,7 +12,7 @@
 //
 //   all-gather -> GEMM.  X is sharded by rows; every rank needs all of X times its own
 //   weight slice.  The local shard already sits at its place inside the gather buffer.
-//   A few CTAs of the grid do no math: after a cross-rank barrier they push the local
+//   A few CTAs of the grid do no math: once every peer has left its previous call they push the local
 //   shard into every peer's gather buffer (peer stores), chunk of 128 rows by chunk,
 //   and count each finished chunk into the peer's ready counters (red.release.sys).
 //   The GEMM CTAs start on the local rows at once; their TMA producer waits (bounded)
