@@ -9,6 +9,12 @@
 //   CTA has no tiles left, its epilogue warps turn to the rows this rank owns: they
 //   wait (bounded) for the flags of all ranks, add the partial tiles in rank order in
 //   fp32 and write the bf16 result.  Deterministic; nothing is reduced in the switch.
+//   Second form, where the staging has an NVSwitch multicast mapping (RsEpilogue::mc_stage):
+//   the bf16 tiles stay in the rank's OWN staging, every rank walks the tiles in the same
+//   order, the flag still goes to the owner, and a few CTAs of the owner (joined by the
+//   others as they run out of tiles) read the sum of all ranks' copies with
+//   multimem.ld_reduce while the remaining tiles are computed: the owner receives M / R
+//   reduced rows instead of R - 1 partial copies; the switch orders the sum.
 //
 //   all-gather -> GEMM.  X is sharded by rows; every rank needs all of X times its own
 //   weight slice.  The local shard already sits at its place inside the gather buffer.
