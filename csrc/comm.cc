@@ -1399,7 +1399,7 @@ std::string Comm::stats_json() {
   if (transport_) {
     TransportStats& t = transport_->stats();
     o << ",\"transport\":{\"writes\":" << t.writes.load() << ",\"flag_writes\":" << t.flag_writes.load() << ",\"bytes\":"
-      << t.bytes_written.load() << ",\"signaled\":" << t.signaled.load() << ",\"direct_writes\":" << t.direct_writes.load() << ",\"reg_hits\":" << t.reg_hits.load()
+      << t.bytes_written.load() << ",\"signaled\":" << t.signaled.load() << ",\"direct_writes\":" << t.direct_writes.load() << ",\"direct_flags\":" << t.direct_flags.load() << ",\"reg_hits\":" << t.reg_hits.load()
       << ",\"reg_misses\":" << t.reg_misses.load() << ",\"completion_errors\":" << t.completion_errors.load() << "}";
   }
   if (ring_) {

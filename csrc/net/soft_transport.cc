@@ -3,7 +3,9 @@
 #include <chrono>
 #include <cstdlib>
 #include <cstring>
+#include <fcntl.h>
 #include <poll.h>
+#include <sys/mman.h>
 #include <sys/uio.h>
 #include <unistd.h>
 
@@ -41,7 +43,17 @@ struct CmaInfo {      // what a rank tells the others about its address space
   uint64_t table_addr;
   int32_t pid;
   int32_t enabled;
+  uint64_t flags_addr;   // the flag array in the owner's address space, and its key
+  uint32_t flags_rkey;
+  uint32_t flags_shared; // 1: the array is the shared-memory object flags_name
+  char flags_name[48];
 };
+constexpr size_t kFlagPageBytes = 2 * 4096;            // flags, then a page with the header below
+struct FlagPageHeader {
+  uint64_t magic;
+  int32_t rank, pid;
+};
+constexpr uint64_t kFlagPageMagic = 0x4d4e43434c464c47ull;
 
 uint64_t cma_host_id() {
   std::string key;
@@ -63,8 +75,31 @@ SoftTransport::Region::~Region() {
 
 SoftTransport::SoftTransport(int rank, int size) : rank_(rank), size_(size) {
   timeout_ms_ = Config::get().socket_timeout_ms;
-  flags_.reset(new uint32_t[kNumFlags]);
-  memset(flags_.get(), 0, sizeof(uint32_t) * kNumFlags);
+  static_assert(sizeof(uint32_t) * kNumFlags <= 4096, "the flag array fits the first page");
+  // The flag array: a shared-memory page that same-host peers can map (see the header), else heap memory.
+  snprintf(flags_name_, sizeof(flags_name_), "/mnccl-fl-%d-%d-%08x", static_cast<int>(getpid()), rank,
+           static_cast<unsigned>(std::chrono::steady_clock::now().time_since_epoch().count()));
+  int fd = shm_open(flags_name_, O_CREAT | O_EXCL | O_RDWR, 0600);
+  if (fd >= 0) {
+    void* m = ftruncate(fd, kFlagPageBytes) == 0 ? mmap(nullptr, kFlagPageBytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0) : MAP_FAILED;
+    close(fd);
+    if (m != MAP_FAILED) {
+      flags_ = static_cast<uint32_t*>(m);
+      flags_shm_ = true;
+      memset(m, 0, kFlagPageBytes);
+      FlagPageHeader* h = reinterpret_cast<FlagPageHeader*>(static_cast<char*>(m) + 4096);
+      h->rank = rank;
+      h->pid = static_cast<int32_t>(getpid());
+      __atomic_store_n(&h->magic, kFlagPageMagic, __ATOMIC_RELEASE);
+    } else {
+      shm_unlink(flags_name_);
+    }
+  }
+  if (!flags_shm_) {
+    flags_name_[0] = 0;
+    flags_ = new uint32_t[kNumFlags];
+    memset(flags_, 0, sizeof(uint32_t) * kNumFlags);
+  }
   table_.reset(new KeyTable());
   memset(table_.get(), 0, sizeof(KeyTable));
   if (const char* e = std::getenv("MINI_NCCL_SOFT_DROP_FLAG_AT")) drop_at_.store(std::strtoull(e, nullptr, 10));
@@ -75,6 +110,14 @@ SoftTransport::~SoftTransport() {
   if (nic_.joinable()) nic_.join();
   flags_mr_.reset();
   cache_.clear();
+  for (uint32_t* p : peer_flags_)
+    if (p) munmap(p, kFlagPageBytes);
+  if (flags_shm_) {
+    if (flags_name_[0]) shm_unlink(flags_name_);
+    munmap(flags_, kFlagPageBytes);
+  } else {
+    delete[] flags_;
+  }
 }
 
 void SoftTransport::connect(BootstrapStore& store) {
@@ -83,8 +126,8 @@ void SoftTransport::connect(BootstrapStore& store) {
   for (auto& m : send_mu_) m.reset(new std::mutex);
   dead_ = std::vector<std::atomic<bool>>(size_);
   for (auto& d : dead_) d.store(false);
-  flags_mr_ = register_memory(flags_.get(), sizeof(uint32_t) * kNumFlags);
-  flags_remote_.addr = reinterpret_cast<uint64_t>(flags_.get());
+  flags_mr_ = register_memory(flags_, sizeof(uint32_t) * kNumFlags);
+  flags_remote_.addr = reinterpret_cast<uint64_t>(flags_);
   flags_remote_.rkey = flags_mr_->rkey;
   if (size_ > 1) {
     TcpListener lis;
@@ -109,11 +152,20 @@ void SoftTransport::connect(BootstrapStore& store) {
     }
     // Same-host fast path: who shares this host's memory, and may we touch it?
     const char* env = std::getenv("MINI_NCCL_SOFT_CMA");
-    CmaInfo mine{cma_host_id(), reinterpret_cast<uint64_t>(table_.get()), static_cast<int32_t>(getpid()),
-                 (env && env[0] == '0') ? 0 : 1};
+    CmaInfo mine{};
+    mine.host_id = cma_host_id();
+    mine.table_addr = reinterpret_cast<uint64_t>(table_.get());
+    mine.pid = static_cast<int32_t>(getpid());
+    mine.enabled = (env && env[0] == '0') ? 0 : 1;
+    mine.flags_addr = flags_remote_.addr;
+    mine.flags_rkey = flags_remote_.rkey;
+    mine.flags_shared = flags_shm_ ? 1 : 0;
+    memcpy(mine.flags_name, flags_name_, sizeof(mine.flags_name));
     std::vector<CmaInfo> infos(size_);
     store.all_gather(&mine, infos.data(), sizeof(mine));
     cma_.assign(size_, CmaPeer());
+    peer_flags_.assign(size_, nullptr);
+    peer_flags_remote_.assign(size_, RemoteBuffer());
     int n_cma = 0;
     for (int p = 0; p < size_; ++p) {
       if (p == rank_ || !mine.enabled || !infos[p].enabled || infos[p].host_id != mine.host_id) continue;
@@ -122,9 +174,34 @@ void SoftTransport::connect(BootstrapStore& store) {
       cma_[p].ok = true;
       if (!cma_refresh(cma_[p])) cma_[p].ok = false;  // the probe: not permitted here (ptrace policy) -> sockets
       if (cma_[p].ok) ++n_cma;
+      // the peer's flag page: only together with the payload fast path (a flag must never overtake a
+      // payload that is still in a socket)
+      if (cma_[p].ok && infos[p].flags_shared) {
+        infos[p].flags_name[sizeof(infos[p].flags_name) - 1] = 0;
+        int pfd = shm_open(infos[p].flags_name, O_RDWR, 0600);
+        if (pfd >= 0) {
+          void* m = mmap(nullptr, kFlagPageBytes, PROT_READ | PROT_WRITE, MAP_SHARED, pfd, 0);
+          close(pfd);
+          if (m != MAP_FAILED) {
+            const FlagPageHeader* h = reinterpret_cast<const FlagPageHeader*>(static_cast<const char*>(m) + 4096);
+            if (__atomic_load_n(&h->magic, __ATOMIC_ACQUIRE) == kFlagPageMagic && h->rank == p && h->pid == infos[p].pid) {
+              peer_flags_[p] = static_cast<uint32_t*>(m);
+              peer_flags_remote_[p].addr = infos[p].flags_addr;
+              peer_flags_remote_[p].rkey = infos[p].flags_rkey;
+            } else {
+              munmap(m, kFlagPageBytes);
+            }
+          }
+        }
+      }
     }
     if (n_cma) MNCCL_INFO("Mini-NCCL", "soft transport: cross-memory attach to %d same-host peer(s)", n_cma);
     store.barrier();
+    // every peer that wanted the page has mapped it: the name can go
+    if (flags_shm_ && flags_name_[0]) {
+      shm_unlink(flags_name_);
+      flags_name_[0] = 0;
+    }
   }
   run_.store(true);
   nic_ = std::thread([this] { nic_loop(); });
@@ -300,7 +377,14 @@ Request* SoftTransport::write_flag(int peer, RemoteBuffer remote_flags, uint32_t
   uint64_t nth = flag_posts_.fetch_add(1) + 1;
   const bool drop = drop_at_.load() != 0 && nth >= drop_at_.load();
   try {
-    if (!drop) send_frame(peer, kFlag, remote_flags.rkey, value, remote_flags.addr + 4ull * index, nullptr, 4);
+    // Same-host peer whose payloads go straight into its memory: so does the flag, with one release
+    // store (every payload posted before it was copied by a system call that has returned).
+    uint32_t* page = (!drop && peer >= 0 && peer < static_cast<int>(peer_flags_.size()) && cma_[peer].ok) ? peer_flags_[peer] : nullptr;
+    if (page && remote_flags.addr == peer_flags_remote_[peer].addr && remote_flags.rkey == peer_flags_remote_[peer].rkey) {
+      if (aborted()) fail(Result::InternalError, "transport aborted");
+      __atomic_store_n(page + index, value, __ATOMIC_RELEASE);
+      stats_.direct_flags++;
+    } else if (!drop) send_frame(peer, kFlag, remote_flags.rkey, value, remote_flags.addr + 4ull * index, nullptr, 4);
     else MNCCL_INFO("Mini-NCCL", "soft transport: dropping flag write #%llu (fault injection)", (unsigned long long)nth);
   } catch (...) {
     if (req) pool_.release(req);

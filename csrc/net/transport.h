@@ -42,6 +42,7 @@ struct TransportStats {
   std::atomic<uint64_t> writes{0}, flag_writes{0}, bytes_written{0}, signaled{0};
   std::atomic<uint64_t> reg_hits{0}, reg_misses{0}, completion_errors{0};
   std::atomic<uint64_t> direct_writes{0};  // payloads that went straight into a same-host peer's memory
+  std::atomic<uint64_t> direct_flags{0};   // flags stored straight into a same-host peer's flag page
 };
 
 class OneSidedTransport {

@@ -31,10 +31,12 @@ def test_plumbing_config_two_ranks(free_port, cma):
         assert st["transport"]["reg_hits"] >= 2
         assert "[Config] Loaded: SLICE_SIZE=131072 B, WINDOW=64, BATCH=16" in r["_stderr"]
         if cma == 0:
-            assert st["transport"]["direct_writes"] == 0
+            assert st["transport"]["direct_writes"] == 0 and st["transport"]["direct_flags"] == 0
         elif "cross-memory attach to 1 same-host peer" in r["_stderr"]:
-            # the kernel allowed it: every payload went straight into the peer's memory
+            # the kernel allowed it: every payload went straight into the peer's memory, and every flag
+            # (one per slice sent, one credit per slice received) was one store into the peer's flag page
             assert st["transport"]["direct_writes"] == st["transport"]["writes"] == 16 * 2 * 3
+            assert st["transport"]["direct_flags"] == 2 * 16 * 2 * 3
         else:
             assert st["transport"]["direct_writes"] == 0   # not permitted here: sockets, same results
 
