@@ -432,3 +432,21 @@ def test_switch_tie_rule_accepts_only_true_ties():
     wrong = want.copy()
     wrong[5] = O.f32_to_bf16_bits(np.array([100.5], dtype=np.float32))[0]
     assert not switch_ties(wrong, want, exact).any(), "an ordinary mismatch is never excused"
+
+
+def test_nccl_registered_buffer_degrades_without_a_process_group():
+    """benchmarks/sweep.py --nccl-registered: without NCCL (no GPU, no process group) the helper reports why
+    instead of raising, so a sweep simply has no such column."""
+    import os
+    import sys
+
+    import torch
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if root not in sys.path:
+        sys.path.insert(0, root)
+    from benchmarks.sweep import nccl_registered_buffer
+
+    t, why = nccl_registered_buffer(1024, torch.float32)
+    if t is None:
+        assert isinstance(why, str) and why
