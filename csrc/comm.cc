@@ -1405,7 +1405,7 @@ std::string Comm::stats_json() {
   if (ring_) {
     const RingStats& r = ring_->stats();
     o << ",\"ring\":{\"calls\":" << r.calls << ",\"slices_sent\":" << r.slices_sent << ",\"credit_stalls\":" << r.credit_stalls
-      << ",\"window_stalls\":" << r.window_stalls << ",\"slice_bytes\":" << ring_->slice_bytes() << ",\"slots\":" << ring_->slots() << "}";
+      << ",\"window_stalls\":" << r.window_stalls << ",\"threaded_calls\":" << r.threaded_calls << ",\"slice_bytes\":" << ring_->slice_bytes() << ",\"slots\":" << ring_->slots() << "}";
   }
   o << ",\"aborted\":" << (aborted_.load() ? "true" : "false") << "}";
   return o.str();

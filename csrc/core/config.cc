@@ -109,6 +109,7 @@ Config Config::from_getter(Getter get, void* ctx) {
   r.boolean("MINI_NCCL_PIPELINE_COPY_ENGINE", c.pipeline_copy_engine);
   r.boolean("MINI_NCCL_PIPELINE_TAPER", c.pipeline_taper);
   r.boolean("MINI_NCCL_AUTO_MAP", c.auto_map);
+  r.boolean("MINI_NCCL_RING_SENDER_THREAD", c.ring_sender_thread);
   r.boolean("MINI_NCCL_AUTO_DEVICE", c.auto_device);
   r.str("MINI_NCCL_TUNING_FILE", c.tuning_file);
 

@@ -42,6 +42,7 @@ struct Config {
   size_t host_pipeline_min_bytes = 4u << 20;  // MINI_NCCL_HOST_PIPELINE_MIN_BYTES: pinned-host buffers of at least this size are moved by the copy engines in chunks that overlap the collective (0 = never)
   size_t host_chunk_bytes = 8u << 20;  // MINI_NCCL_HOST_CHUNK_BYTES: chunk of that pipeline
   bool auto_map = true;         // MINI_NCCL_AUTO_MAP: ordinary device buffers of the peer-to-peer two-shot AllReduce are exported over CUDA IPC when first seen and used directly once every rank has mapped them
+  bool ring_sender_thread = true;  // MINI_NCCL_RING_SENDER_THREAD: the host ring sends from a second thread while the caller's thread receives and reduces (messages of 4 MB and more, providers that allow it)
   bool pipeline_taper = false;  // MINI_NCCL_PIPELINE_TAPER: small first and last chunk, large chunks between (device buffers of 128 MB and more)
   bool pipeline_copy_engine = false;  // MINI_NCCL_PIPELINE_COPY_ENGINE: the chunk pipeline moves ordinary DEVICE buffers with the copy engines too (off: copy kernels)
   size_t pipeline_min_bytes = 48u << 20;  // MINI_NCCL_PIPELINE_MIN_BYTES: ordinary buffers of at least this size go through the chunk pipeline (0 = never)

@@ -4,7 +4,9 @@
 #include <chrono>
 #include <cstdlib>
 #include <cstring>
+#include <exception>
 #include <thread>
+#include <vector>
 
 #include "bootstrap/store.h"
 #include "core/error.h"
@@ -57,6 +59,7 @@ void RingAllReduce::wait_flag(uint32_t index, uint32_t target, const char* what)
   auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(cfg_.watchdog_timeout_ms);
   unsigned spins = 0;
   while (!reached()) {
+    if (cancel_.load(std::memory_order_relaxed)) fail(Result::InternalError, std::string("the call's other thread failed while waiting for ") + what);
     if (abort_word_ && *abort_word_) fail(Result::InternalError, std::string("aborted while waiting for ") + what);
     if (t_->aborted()) fail(Result::InternalError, std::string("transport aborted while waiting for ") + what);
     if ((++spins & 0x3f) == 0) {
@@ -131,6 +134,11 @@ void RingAllReduce::run(void* data, size_t count, DType dtype, RedOp op) {
   auto chunk_len = [&](int c) { return base + (size_t(c) < rem ? 1 : 0); };
   char* bytes = static_cast<char*>(data);
   std::shared_ptr<MemoryRegion> mr = t_->register_memory(data, count * esz);
+  if (cfg_.ring_sender_thread && t_->concurrent_posting() && count * esz >= (size_t(4) << 20)) {
+    run_threaded(bytes, count, esz, slice_elems, dtype, op, *mr);
+    if (op == RedOp::Avg) host_avg_finalize(dtype, data, count, n);
+    return;
+  }
 
   for (int step = 0; step < 2 * (n - 1); ++step) {
     const bool phase1 = step < n - 1;
@@ -163,6 +171,82 @@ void RingAllReduce::run(void* data, size_t count, DType dtype, RedOp op) {
     if (step == n - 2 || step == 2 * (n - 1) - 1) drain();  // end of each phase, as the reference does
   }
   if (op == RedOp::Avg) host_avg_finalize(dtype, data, count, n);
+}
+
+// The same schedule with the two halves of the work in two threads.  The chunk a rank sends in step s
+// is the chunk it received (and, in phase 1, reduced) in step s - 1, cut into the same slices, so slice
+// k of step s may go as soon as slice k of step s - 1 has been consumed: the sender thread waits for
+// the receiver's counter to reach that slice and otherwise runs freely (credits and the window bound
+// it as before).  The sender owns sent_total_, pending_ and the send counters, the receiver owns
+// recv_total_; they share the counter and cancel_.
+void RingAllReduce::run_threaded(char* bytes, size_t count, size_t esz, size_t slice_elems, DType dtype, RedOp op,
+                                 const MemoryRegion& mr) {
+  const int n = size_;
+  const size_t base = count / n, rem = count % n;
+  auto chunk_off = [&](int c) { return size_t(c) * base + std::min<size_t>(c, rem); };
+  auto chunk_len = [&](int c) { return base + (size_t(c) < rem ? 1 : 0); };
+  auto slices_of = [&](size_t len) { return (len + slice_elems - 1) / slice_elems; };
+  const int steps = 2 * (n - 1);
+  auto send_chunk_of = [&](int step) { return step < n - 1 ? (rank_ - step + n) % n : (rank_ + 1 - (step - (n - 1)) + n) % n; };
+  auto recv_chunk_of = [&](int step) { return step < n - 1 ? (rank_ - step - 1 + 2 * n) % n : (rank_ - (step - (n - 1)) + n) % n; };
+  // slices this rank has received before each step
+  std::vector<uint64_t> recv_before(steps + 1, 0);
+  for (int s = 0; s < steps; ++s) recv_before[s + 1] = recv_before[s] + slices_of(chunk_len(recv_chunk_of(s)));
+
+  std::atomic<uint64_t> received{0};
+  std::exception_ptr sender_error;
+  bool sender_first = false;   // the sender failed first (the receiver's error is then only the echo); read after join
+  cancel_.store(false);
+  ++stats_.threaded_calls;
+  std::thread sender([&] {
+    try {
+      for (int step = 0; step < steps; ++step) {
+        const int c = send_chunk_of(step);
+        const size_t len = chunk_len(c), ns = slices_of(len);
+        for (size_t k = 0; k < ns; ++k) {
+          if (step > 0) {
+            const uint64_t need = recv_before[step - 1] + k + 1;
+            unsigned spins = 0;
+            while (received.load(std::memory_order_acquire) < need) {
+              if (cancel_.load(std::memory_order_relaxed)) fail(Result::InternalError, "the receiving thread of the call failed");
+              if ((++spins & 0x3ff) == 0) {
+                if ((abort_word_ && *abort_word_) || t_->aborted()) fail(Result::InternalError, "aborted while waiting for a slice to forward");
+                std::this_thread::yield();
+              }
+            }
+          }
+          const size_t off = k * slice_elems;
+          const size_t ne = std::min(slice_elems, len - off);
+          const bool signaled = (k % static_cast<size_t>(cfg_.signal_batch) == 0) || (k + 1 == ns);
+          send_slice(bytes + (chunk_off(c) + off) * esz, mr, ne * esz, signaled);
+        }
+        if (step == n - 2 || step == steps - 1) drain();  // end of each phase, as the reference does
+      }
+    } catch (...) {
+      sender_error = std::current_exception();
+      if (!cancel_.exchange(true)) sender_first = true;
+    }
+  });
+  std::exception_ptr receiver_error;
+  try {
+    for (int step = 0; step < steps; ++step) {
+      const int c = recv_chunk_of(step);
+      const size_t len = chunk_len(c), ns = slices_of(len);
+      for (size_t k = 0; k < ns; ++k) {
+        const size_t off = k * slice_elems;
+        const size_t ne = std::min(slice_elems, len - off);
+        recv_slice(bytes + (chunk_off(c) + off) * esz, ne, dtype, op, step < n - 1);
+        received.fetch_add(1, std::memory_order_release);
+      }
+    }
+  } catch (...) {
+    receiver_error = std::current_exception();
+    cancel_.store(true);
+  }
+  sender.join();
+  cancel_.store(false);
+  if (sender_error && (sender_first || !receiver_error)) std::rethrow_exception(sender_error);
+  if (receiver_error) std::rethrow_exception(receiver_error);
 }
 
 }  // namespace mnccl

@@ -16,7 +16,11 @@
 //  * count need not divide by the rank count (the reference drops count % N
 //    trailing elements) and may be smaller than it;
 //  * both phases land in scratch, so no buffer address is exchanged per call;
-//  * every wait is bounded and observes the abort word.
+//  * every wait is bounded and observes the abort word;
+//  * for messages of 4 MB and more (and a provider that allows posting from two threads) the sends of
+//    a call run in a second thread while the caller's thread receives, reduces and returns credits:
+//    a slice is sent as soon as the slice it forwards has been received, so copying out and reducing
+//    in overlap instead of taking turns (MINI_NCCL_RING_SENDER_THREAD=0: one thread, as before).
 #pragma once
 #include <atomic>
 #include <cstdint>
@@ -34,6 +38,7 @@ class BootstrapStore;
 struct RingStats {
   uint64_t calls = 0, slices_sent = 0, slices_received = 0, bytes_sent = 0;
   uint64_t credit_stalls = 0, window_stalls = 0;
+  uint64_t threaded_calls = 0;   // calls whose sends ran in the second thread
 };
 
 class RingAllReduce {
@@ -56,6 +61,8 @@ class RingAllReduce {
   void recv_slice(char* dst, size_t elems, DType dtype, RedOp op, bool reduce);
   void wait_flag(uint32_t index, uint32_t target, const char* what);
   void drain();
+  void run_threaded(char* bytes, size_t count, size_t esz, size_t slice_elems, DType dtype, RedOp op, const MemoryRegion& mr);
+  std::atomic<bool> cancel_{false};   // set when one of the two threads of a call failed: the other one's waits give up
 
   int rank_, size_, next_, prev_;
   OneSidedTransport* t_;

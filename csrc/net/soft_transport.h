@@ -51,6 +51,7 @@ class SoftTransport : public OneSidedTransport {
   volatile uint32_t* flags() override { return flags_; }
   RemoteBuffer flags_remote() const override { return flags_remote_; }
   int max_outstanding() const override { return 1024; }
+  bool concurrent_posting() const override { return true; }  // per-peer send lock, atomic counters, flags are atomic stores
 
   // Host-side fault injection for tests: from the n-th flag write posted by
   // this rank on (1-based) every flag write is dropped silently, as if the

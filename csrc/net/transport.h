@@ -80,6 +80,9 @@ class OneSidedTransport {
 
   // Upper bound of posted-but-unreaped work requests per peer.
   virtual int max_outstanding() const = 0;
+  // True when one thread may post writes and wait for their completions while another thread posts
+  // unsignalled flag writes and polls (the ring's sender thread, net/ring.cc).
+  virtual bool concurrent_posting() const { return false; }
 
   // Makes every blocked wait in this transport return (sticky).
   void abort() { aborted_.store(true, std::memory_order_release); }

@@ -122,7 +122,7 @@ def cpu_ring_fault(rank, n, kw):
     from mini_nccl_b200 import _lib
 
     comm = mn.Communicator(n, rank, "127.0.0.1")
-    x = np.ones(1 << 16, np.float32)
+    x = np.ones(kw.get("count", 1 << 16), np.float32)
     t0 = time.time()
     rc = mn.lib().ncclAllReduce(x.ctypes.data, x.ctypes.data, x.size, _lib.FLOAT32, _lib.SUM, comm.handle, None)
     dt = time.time() - t0

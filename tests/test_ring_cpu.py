@@ -97,3 +97,34 @@ def test_dropped_flag_write_fails_bounded(free_port):
         assert r["rc2"] == _lib.INTERNAL_ERROR, "the failure is sticky"
         assert r["seconds"] < 5.0, "bounded"
     assert any("Watchdog" in r["_stderr"] and "TIMEOUT" in r["_stderr"] for r in res)
+
+
+@pytest.mark.parametrize("n", [2, 3, 4])
+@pytest.mark.parametrize("threaded", [1, 0])
+def test_large_messages_send_from_a_second_thread(free_port, n, threaded):
+    """Messages of 4 MB and more: the sends of a call run in a second thread while the caller's thread
+    receives and reduces (MINI_NCCL_RING_SENDER_THREAD=0: one thread).  Same results either way, with
+    counts the rank count does not divide, few scratch slots (credit stalls) and repeated calls."""
+    env = {"MINI_NCCL_BOOTSTRAP_PORT": free_port, "MINI_NCCL_RING_SENDER_THREAD": threaded, "MINI_NCCL_WINDOW_SIZE": 4}
+    cases = [{"dtype": _lib.FLOAT32, "op": _lib.SUM, "count": (1 << 20) + 7, "in_place": True, "repeat": 2},
+             {"dtype": _lib.FLOAT32, "op": _lib.MAX, "count": (3 << 19) + 1},
+             {"dtype": _lib.BFLOAT16, "op": _lib.AVG, "count": (1 << 21) + 5},
+             {"dtype": _lib.INT32, "op": _lib.SUM, "count": 1 << 20, "in_place": True},
+             {"dtype": _lib.FLOAT32, "op": _lib.SUM, "count": 1000}]          # a small one in between: one thread
+    res = run_ranks("cpu_ring", n, {"cases": cases}, env, timeout=240)
+    for r in res:
+        assert r["cases"] == len(cases)
+        assert r["stats"]["ring"]["threaded_calls"] == (5 if threaded else 0)
+        assert r["stats"]["transport"]["completion_errors"] == 0
+
+
+def test_dropped_flag_in_a_threaded_call_fails_bounded(free_port):
+    """The host-made fault of the test above in a call whose sends run in the second thread: both threads
+    of both ranks give up within the bound, the threads are joined, the failure is sticky."""
+    env = {"MINI_NCCL_BOOTSTRAP_PORT": free_port, "MINI_NCCL_WATCHDOG_TIMEOUT_MS": 400, "MINI_NCCL_SOCKET_TIMEOUT_MS": 3000}
+    res = run_ranks("cpu_ring_fault", 2, {"count": 1 << 21}, env, per_rank_env={0: {"MINI_NCCL_SOFT_DROP_FLAG_AT": 9}})
+    for r in res:
+        assert r["rc"] == _lib.INTERNAL_ERROR, r
+        assert r["rc2"] == _lib.INTERNAL_ERROR, "the failure is sticky"
+        assert r["seconds"] < 5.0, "bounded"
+    assert any("Watchdog" in r["_stderr"] and "TIMEOUT" in r["_stderr"] for r in res)
