@@ -41,9 +41,10 @@ static int g_fail = 0;
     }                                                                \
   } while (0)
 
-static void ring_threads(int port) {
+// count: 200003 elements run in one thread per rank; 1100003 (4.4 MB) take the ring's second thread,
+// so that the thread sanitizer sees the sender, the receiver and the provider's threads together.
+static void ring_threads(int port, size_t count, int iters) {
   const int n = 3;
-  const size_t count = 200003;
   std::vector<std::vector<float>> data(n, std::vector<float>(count));
   for (int r = 0; r < n; ++r)
     for (size_t i = 0; i < count; ++i) data[r][i] = static_cast<float>((i * 7 + r * 13) % 101) * 0.25f;
@@ -63,12 +64,13 @@ static void ring_threads(int port) {
         SoftTransport t(r, n);
         t.connect(store);
         RingAllReduce ring(r, n, &t, &store, cfg, nullptr);
-        for (int it = 0; it < 3; ++it) {
+        for (int it = 0; it < iters; ++it) {
           std::vector<float> buf = data[r];
           ring.run(buf.data(), count, DType::Float32, RedOp::Sum);
           for (size_t i = 0; i < count; ++i)
             if (std::fabs(buf[i] - want[i]) > 1e-3f) { errors++; break; }
         }
+        if (count * sizeof(float) >= (size_t(4) << 20) && ring.stats().threaded_calls != static_cast<uint64_t>(iters)) errors++;
         store.barrier();
       } catch (const std::exception& e) {
         fprintf(stderr, "rank %d: %s\n", r, e.what());
@@ -107,7 +109,8 @@ int main(int argc, char** argv) {
     CHECK(mnccl_hera_master_registered(m) == 4);
     mnccl_hera_master_stop(m);
   }
-  ring_threads(port);
+  ring_threads(port, 200003, 3);
+  ring_threads(port + 7, 1100003, 2);
   printf(g_fail ? "[FAIL] host self-test: %d check(s) failed\n" : "[PASS] host self-test\n", g_fail);
   return g_fail ? 1 : 0;
 }
